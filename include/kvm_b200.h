@@ -1,0 +1,119 @@
+/* libkvm_b200.so: C ABI of the B200 executor for Magni VM task bundles (ABI v2).
+ *
+ * The reference has no FFI: its executor is a header-level C++ class (MvmExec, mvm_exec.cu:492-1677) driven by a CLI that
+ * reads a bundle directory.  Each entry point below flattens one member of that class (cited beside it), with plain
+ * pointers and sizes, so the CLI, a ctypes / cgo / JNI stub or a C++ host can bind it.  Return value: 0 = ok, negative =
+ * host-side error (KVM_E_*), positive = device error code (executor codes 1..20 as in the reference's MVM_ERRORS,
+ * include/mvm_exec.cuh:147-164; op codes 1001..1007 as in MVM_GPT_ERRORS, include/mvm_ops_gpt.cuh:181-194).
+ * No exception crosses the boundary; kvm_last_error() gives the text of the last failure on a handle.
+ */
+#ifndef KVM_B200_H
+#define KVM_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVM_ABI_VERSION 2
+#define KVM_NO_VAR (-1)
+
+/* Task descriptor: sixteen int32 words, field for field the reference's MvmTaskDesc (include/mvm_task_abi.h:11-29). */
+typedef struct KvmTaskDesc {
+    int32_t op_id, succ_off, succ_cnt, indegree, priority, deadline_us, args_off, args_words;
+    int32_t wait_var, wait_ver, pub_var, pub_ver, workload_id, flags, reserved0, reserved1;
+} KvmTaskDesc;
+
+enum { KVM_F32 = 0, KVM_I32 = 1, KVM_BF16 = 2 };            /* buffer dtypes, MvmBuf.dtype (include/mvm_task_abi.h:33-38) */
+enum { KVM_INIT_FILL = 0, KVM_INIT_VALUES = 1, KVM_INIT_SEEDED = 2, KVM_INIT_NONE = 3 };
+
+/* Host-side error codes (negative). */
+enum { KVM_E_ARG = -1, KVM_E_CUDA = -2, KVM_E_BUNDLE = -3, KVM_E_STATE = -4, KVM_E_NOMEM = -5, KVM_E_IO = -6 };
+
+typedef struct KvmConfig {
+    int32_t device;        /* CUDA device ordinal */
+    int32_t workers;       /* worker CTAs; 0 = one per SM */
+    int32_t trace;         /* 1 = record per-task start/end timestamps and SM id */
+    int32_t timeout_ms;    /* device-side stall limit; 0 = default (20000) */
+    int32_t num_vars;      /* version variables; 0 = default (64) */
+    int32_t flags;         /* KVM_CFG_* */
+} KvmConfig;
+enum { KVM_CFG_NO_TENSOR_CORES = 1 /* run every GEMM on the SIMT reference path (debugging / bit-exact f32) */ };
+
+/* Buffer initial value (mvm_exec.cu:1915-1929 buffer init kinds; `file` inits are read by the caller and passed as VALUES). */
+typedef struct KvmInit {
+    int32_t kind;          /* KVM_INIT_* */
+    int32_t draws;         /* SEEDED: draws per element (1 uniform, 4 normal) */
+    double  fill;          /* FILL: the value (integers for i32 buffers) */
+    const void* data;      /* VALUES: rows*cols elements in the buffer's storage type (f32 / i32 / raw bf16) */
+    uint64_t seed;         /* SEEDED */
+    float   bias, coef;    /* SEEDED: value = (acc - bias) * coef */
+} KvmInit;
+
+typedef struct KvmResult {
+    int32_t status;        /* 0 or the first device error code */
+    int32_t done;          /* tasks finished */
+    int32_t admitted;      /* tasks submitted */
+    int32_t err_task;      /* task index of the first error, -1 if none */
+    int32_t err_a, err_b;  /* two words of detail */
+    float   ms;            /* device time of the persistent kernel (CUDA events) */
+    float   busy_frac;     /* with trace: sum(end - start) / (workers * span); else 0 */
+} KvmResult;
+
+typedef struct KvmExec KvmExec;
+
+/* MvmExec::MvmExec(cfg) (mvm_exec.cu:494-569): create the context, size the pools. */
+int kvm_create(const KvmConfig* cfg, KvmExec** out);
+/* ~MvmExec (mvm_exec.cu:570-578): frees every device buffer the handle allocated. */
+void kvm_destroy(KvmExec* h);
+/* MvmExec::add_buffer (mvm_exec.cu:582-591,1621-1651): allocate rows x cols of dtype, initialise on the device; returns the
+ * buffer-table index (>= 0) or a negative error. */
+int kvm_add_buffer(KvmExec* h, int32_t rows, int32_t cols, int32_t dtype, const KvmInit* init);
+/* Same table entry over memory the caller owns (a device pointer, ld in elements): how an NCCL / framework tensor becomes a
+ * task operand.  No reference counterpart (its buffers are always owned). */
+int kvm_bind_buffer(KvmExec* h, void* dev_ptr, int32_t rows, int32_t cols, int32_t ld, int32_t dtype);
+/* Device address of buffer idx (NULL on a bad index). */
+void* kvm_buffer_ptr(KvmExec* h, int32_t idx);
+/* Raw host -> device / device -> host copies of [offset, offset+bytes) of a buffer's storage. */
+int kvm_write_buffer(KvmExec* h, int32_t idx, const void* host, size_t bytes, size_t offset);
+int kvm_read_buffer_raw(KvmExec* h, int32_t idx, void* host, size_t bytes, size_t offset);
+/* MvmExec::read_buffer (mvm_exec.cu:1541-1554): n elements widened to float32 (i32 converted, bf16 widened exactly). */
+int kvm_read_buffer(KvmExec* h, int32_t idx, float* out, size_t n);
+/* Version variables (include/mvm_task_abi.h:20-23): base version before a run / value after it. */
+int kvm_set_version(KvmExec* h, int32_t var, int32_t version);
+int kvm_get_version(KvmExec* h, int32_t var, int32_t* version);
+/* MvmBundle::validate + MvmExec::submit (mvm_exec.cu:141-208,742-793): append one compiled batch; successor indices are
+ * batch-local.  The bundle is checked (op ids, arities, ranges, buffer indices, indegree == in-edges, acyclic) before any
+ * of it reaches the device. */
+int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na);
+/* Read tasks.bin / successors.bin / args.bin of a bundle directory (FRAMEWORK.md:62-71) and submit them; buffers must have
+ * been added in metadata.json's order by the caller. */
+int kvm_submit_bundle_dir(KvmExec* h, const char* dir);
+/* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over everything submitted since the last run.
+ * kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
+int kvm_start(KvmExec* h);
+int kvm_finish(KvmExec* h, KvmResult* res);
+int kvm_run(KvmExec* h, KvmResult* res);
+/* Re-arm the submitted tasks (dependency counters, queue, per-task records) so the same program runs again on the current
+ * buffer contents and versions: the reference re-admits a one-step template per window (FRONTEND.md:201-213). */
+int kvm_rearm(KvmExec* h);
+/* Drop all submitted tasks (buffers and versions stay). */
+int kvm_clear_tasks(KvmExec* h);
+/* Per task of the last run: times executed and predecessor completions observed (the exactly-once witness and dependency
+ * count the reference keeps in MvmTrace.exec_count, include/mvm_exec.cuh:167-176,733-736). Either pointer may be NULL. */
+int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t n);
+/* With trace on: per task start / end (ns, %globaltimer) and SM id (MvmTrace, include/mvm_exec.cuh:167-176). */
+int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32_t* smid, int32_t n);
+/* Launch geometry of the persistent kernel: worker CTAs, threads per CTA, dynamic shared memory bytes. */
+int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes);
+const char* kvm_last_error(KvmExec* h);
+const char* kvm_err_name(int32_t code);
+/* Registry lookups (include/kvm_ops.def): arity of op id, or -1; name or NULL. */
+int kvm_op_arity(int32_t op_id);
+const char* kvm_op_name(int32_t op_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,151 @@
+// libkvm_b200.so: host side of the executor (bundle validation, device tables, launch, results) and the C ABI of
+// include/kvm_b200.h.  Mirrors what the reference's MvmExec does around its persistent kernel (mvm_exec.cu:492-1677):
+// own the device buffers, check a batch before it reaches the device, launch one persistent kernel, read back counters.
+// Build: nvcc -gencode arch=compute_100a,code=sm_100a -shared (see kvm_b200/build.py).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "kvm_dev.cuh"
+#include "kvm_ops_flat.cuh"
+#include "kvm_ops_rows.cuh"
+#include "kvm_ops_mm.cuh"
+#include "kvm_ops_attn.cuh"
+#include "kvm_ops_decode.cuh"
+#include "kvm_gemm_tc.cuh"
+#include "kvm_sched.cuh"
+
+// ---------------------------------------------------------------------------------------------------------------- registry
+struct KvmOpInfo { const char* name; int id; const char* sig; int arity; unsigned char types[KVM_MAX_ARGS]; };   // type 0 i32, 1 f32, 2 buf, 3 buf?
+static std::vector<KvmOpInfo> g_ops;
+static const KvmOpInfo* kvm_find_op(int id) {
+  if (g_ops.empty()) {
+    const struct { const char* n; int id; const char* s; } raw[] = {
+#define KVM_OP(name, id, sig) {#name, id, sig},
+#include "../../include/kvm_ops.def"
+#undef KVM_OP
+    };
+    for (auto& r : raw) {
+      KvmOpInfo o{r.n, r.id, r.s, 0, {}};
+      const char* p = r.s;
+      while (*p) {
+        const char* colon = strchr(p, ':');
+        if (!colon) break;
+        const char* end = strchr(colon, ',');
+        std::string ty(colon + 1, end ? end - colon - 1 : strlen(colon + 1));
+        o.types[o.arity++] = ty == "i32" ? 0 : ty == "f32" ? 1 : ty == "buf" ? 2 : 3;
+        if (!end) break;
+        p = end + 1;
+      }
+      g_ops.push_back(o);
+    }
+  }
+  for (auto& o : g_ops) if (o.id == id) return &o;
+  return nullptr;
+}
+
+// ---------------------------------------------------------------------------------------------------------------- dispatch
+__device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* a, const int4& aux) {
+  switch (op) {
+    case 1: kvm_op_copy(c, a); break;
+    case 2: kvm_op_add(c, a); break;
+    case 3: kvm_op_scale(c, a); break;
+    case 4: kvm_op_relu(c, a); break;
+    case 5: kvm_op_sgd(c, a); break;
+    case 6: kvm_op_predict(c, a); break;
+    case 7: kvm_op_mse_grad(c, a); break;
+    case 8: kvm_op_matmul(c, a); break;
+    case 9: kvm_op_fill(c, a); break;
+    case 10: kvm_op_spin(c, a); break;
+    case 32: kvm_op_embedding_fwd(c, a); break;
+    case 33: kvm_op_embedding_bwd(c, a); break;
+    case 34: kvm_op_matmul_tile(c, a); break;
+    case 35: kvm_op_layernorm_fwd(c, a); break;
+    case 36: kvm_op_rmsnorm_fwd(c, a); break;
+    case 37: kvm_op_layernorm_bwd_dx(c, a); break;
+    case 38: kvm_op_rmsnorm_bwd_dx(c, a); break;
+    case 39: kvm_op_norm_bwd_params(c, a); break;
+    case 40: kvm_op_gelu_fwd(c, a); break;
+    case 41: kvm_op_gelu_bwd(c, a); break;
+    case 42: kvm_op_residual_add(c, a); break;
+    case 43: kvm_op_rope_fwd(c, a); break;
+    case 44: kvm_op_rope_bwd(c, a); break;
+    case 45: kvm_op_attn_fwd(c, a); break;
+    case 46: kvm_op_attn_bwd_delta(c, a); break;
+    case 47: kvm_op_attn_bwd_dq(c, a); break;
+    case 48: kvm_op_attn_bwd_dkv(c, a); break;
+    case 49: kvm_op_kv_append(c, a); break;
+    case 50: kvm_op_attn_decode(c, a); break;
+    case 51: kvm_op_softmax_ce_fwd(c, a); break;
+    case 52: kvm_op_softmax_ce_reduce(c, a); break;
+    case 53: kvm_op_softmax_ce_bwd(c, a); break;
+    case 54: kvm_op_adamw(c, a); break;
+    case 55: kvm_op_gradnorm_partial(c, a); break;
+    case 56: kvm_op_gradnorm_finish(c, a); break;
+    case 57: kvm_op_sample(c, a); break;
+    case 58: kvm_op_argmax(c, a); break;
+    case 59: kvm_op_zero_buf(c, a); break;
+    case 60: kvm_op_counter_inc(c, a); break;
+    case 61: kvm_op_colsum(c, a); break;
+    case 62: kvm_op_select_window(c, a); break;
+    case 63: kvm_op_gather_rows(c, a); break;
+    case 96: kvm_op_act_fwd(c, a); break;
+    case 97: kvm_op_act_bwd(c, a); break;
+    case 98: kvm_op_silu_mul_fwd(c, a); break;
+    case 113: kvm_op_round_bf16(c, a); break;
+    case 114: kvm_op_matmul_tile_bf16(c, a); break;
+    case 115: kvm_op_adamw_lr(c, a); break;
+    case 116: kvm_op_lr_schedule(c, a); break;
+    case 117: kvm_op_scale_flat(c, a); break;
+    case 118: kvm_op_add_rowtile(c, a); break;
+    case 122: kvm_op_matmul_mma_bf16(c, a, aux); break;
+    case 123: kvm_op_sgd_range(c, a); break;
+    case 126: kvm_op_round_tf32(c, a); break;
+    case 127: kvm_op_softmax_ce_fused(c, a); break;
+    case 134: kvm_op_gemv_bf16(c, a); break;
+    case 135: kvm_op_attn_decode_part(c, a); break;
+    case 136: kvm_op_attn_decode_merge(c, a); break;
+    default: c.fail(KVM_ERR_BAD_OP, op); break;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- init kernels
+// Seeded init: SplitMix64 at counter i*draws+d, u = (z >> 40) * 2^-24, every step one rounded float32 operation
+// (reference: runtime/initgen.py:1-58, device twin include/mvm_exec.cuh:1089-1115).  Bit-exact requirement.
+__device__ __forceinline__ float kvm_seeded_u(unsigned long long seed, unsigned long long j) {
+  unsigned long long z = seed + (j + 1ull) * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return __fmul_rn((float)(z >> 40), 1.0f / 16777216.0f);
+}
+__global__ void kvm_seeded_kernel(float* p, size_t n, unsigned long long seed, int draws, float bias, float coef) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float acc;
+    if (draws == 1) acc = kvm_seeded_u(seed, i);
+    else {
+      const unsigned long long j = i * (unsigned long long)draws;
+      acc = __fadd_rn(__fadd_rn(kvm_seeded_u(seed, j), kvm_seeded_u(seed, j + 1)), __fadd_rn(kvm_seeded_u(seed, j + 2), kvm_seeded_u(seed, j + 3)));
+    }
+    p[i] = __fmul_rn(__fsub_rn(acc, bias), coef);
+  }
+}
+__global__ void kvm_fill_kernel(void* p, size_t n, int dtype, double value) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    if (dtype == KVM_I32) ((int*)p)[i] = (int)value;
+    else if (dtype == KVM_BF16) ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn((float)value);
+    else ((float*)p)[i] = (float)value;
+  }
+}
+__global__ void kvm_widen_kernel(const void* p, float* out, size_t n, int dtype) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = dtype == KVM_I32 ? (float)((const int*)p)[i] : dtype == KVM_BF16 ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------- host state
+#include "kvm_host.inl"

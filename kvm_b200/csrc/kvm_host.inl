@@ -1,0 +1,437 @@
+// Host state and the C entry points (included by kvm_exec.cu).
+
+#define KVM_CUDA(call)                                                                         \
+  do {                                                                                         \
+    cudaError_t e_ = (call);                                                                   \
+    if (e_ != cudaSuccess) { h->error = std::string(#call) + ": " + cudaGetErrorString(e_); return KVM_E_CUDA; } \
+  } while (0)
+
+struct KvmOwned { void* p; size_t bytes; };
+
+struct KvmExec {
+  KvmConfig cfg{};
+  int device = 0, sms = 0, workers = 0, smem_bytes = 0, nvars = 64;
+  std::string error;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // buffer table
+  std::vector<KvmBuf> bufs;
+  std::vector<KvmOwned> owned;
+  KvmBuf* d_bufs = nullptr; size_t d_bufs_cap = 0; bool bufs_dirty = true;
+  // tasks (all submitted batches, successor indices already global)
+  std::vector<KvmTaskDesc> tasks;
+  std::vector<int32_t> succ, args;
+  std::vector<int4> aux;
+  std::vector<CUtensorMap> tmaps;
+  bool tasks_dirty = true;
+  KvmTaskDesc* d_tasks = nullptr; int32_t* d_succ = nullptr; int32_t* d_args = nullptr; int4* d_aux = nullptr; void* d_tmaps = nullptr;
+  int *d_indeg = nullptr, *d_exec = nullptr, *d_ring = nullptr, *d_park_next = nullptr, *d_tsmid = nullptr;
+  unsigned long long *d_tstart = nullptr, *d_tend = nullptr;
+  size_t task_cap = 0;
+  // control words
+  int* d_ctl = nullptr;          // [0] head [1] tail [2] done
+  int* d_versions = nullptr; int* d_park_head = nullptr;
+  KvmErrRec* d_err = nullptr;
+  bool started = false, armed = false;
+  KvmResult last{};
+};
+
+static void kvm_free_tasks(KvmExec* h) {
+  for (void* p : {(void*)h->d_tasks, (void*)h->d_succ, (void*)h->d_args, (void*)h->d_aux, (void*)h->d_tmaps, (void*)h->d_indeg, (void*)h->d_exec, (void*)h->d_ring,
+                  (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend})
+    if (p) cudaFree(p);
+  h->d_tasks = nullptr; h->d_succ = nullptr; h->d_args = nullptr; h->d_aux = nullptr; h->d_tmaps = nullptr; h->d_indeg = h->d_exec = h->d_ring = h->d_park_next = h->d_tsmid = nullptr;
+  h->d_tstart = h->d_tend = nullptr; h->task_cap = 0;
+}
+
+extern "C" const char* kvm_err_name(int32_t code) {
+  static const char* names[] = {
+#define E(n) #n,
+      KVM_ERRORS(E)
+#undef E
+  };
+  if (code >= 0 && code < KVM_ERR_COUNT) return names[code];
+  switch (code) {
+    case KVM_OPE_BUF: return "E_BUF"; case KVM_OPE_DTYPE: return "E_DTYPE"; case KVM_OPE_RANGE: return "E_RANGE"; case KVM_OPE_SHAPE: return "E_SHAPE";
+    case KVM_OPE_TOKEN: return "E_TOKEN"; case KVM_OPE_KVLEN: return "E_KVLEN"; case KVM_OPE_SMEM: return "E_SMEM";
+    case KVM_E_ARG: return "KVM_E_ARG"; case KVM_E_CUDA: return "KVM_E_CUDA"; case KVM_E_BUNDLE: return "KVM_E_BUNDLE"; case KVM_E_STATE: return "KVM_E_STATE";
+    case KVM_E_NOMEM: return "KVM_E_NOMEM"; case KVM_E_IO: return "KVM_E_IO";
+  }
+  return "UNKNOWN";
+}
+extern "C" int kvm_op_arity(int32_t op_id) { const KvmOpInfo* o = kvm_find_op(op_id); return o ? o->arity : -1; }
+extern "C" const char* kvm_op_name(int32_t op_id) { const KvmOpInfo* o = kvm_find_op(op_id); return o ? o->name : nullptr; }
+extern "C" const char* kvm_last_error(KvmExec* h) { return h ? h->error.c_str() : "null handle"; }
+
+extern "C" int kvm_create(const KvmConfig* cfg, KvmExec** out) {
+  if (!out) return KVM_E_ARG;
+  *out = nullptr;
+  KvmExec* h = new KvmExec();
+  if (cfg) h->cfg = *cfg;
+  h->device = h->cfg.device;
+  auto fail = [&](const char* what, cudaError_t e) { fprintf(stderr, "kvm_create: %s: %s\n", what, cudaGetErrorString(e)); delete h; return KVM_E_CUDA; };
+  cudaError_t e;
+  if ((e = cudaSetDevice(h->device)) != cudaSuccess) return fail("cudaSetDevice", e);
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, h->device)) != cudaSuccess) return fail("cudaGetDeviceProperties", e);
+  if (prop.major != 10) { fprintf(stderr, "kvm_create: device %d is sm_%d%d; this library holds sm_100a code only\n", h->device, prop.major, prop.minor); delete h; return KVM_E_CUDA; }
+  h->sms = prop.multiProcessorCount;
+  h->workers = h->cfg.workers > 0 ? h->cfg.workers : h->sms;
+  if (h->workers > h->sms) h->workers = h->sms;      // one CTA per SM: more could not be co-resident, and waiting CTAs need their peers running
+  h->smem_bytes = (int)prop.sharedMemPerBlockOptin;
+  h->nvars = h->cfg.num_vars > 0 ? h->cfg.num_vars : 64;
+  if ((e = cudaFuncSetAttribute(kvm_exec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_bytes)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
+  cudaEventCreate(&h->ev0); cudaEventCreate(&h->ev1);
+  if ((e = cudaMalloc(&h->d_ctl, 64 * sizeof(int))) != cudaSuccess) return fail("cudaMalloc", e);
+  cudaMalloc(&h->d_versions, h->nvars * sizeof(int)); cudaMalloc(&h->d_park_head, h->nvars * sizeof(int)); cudaMalloc(&h->d_err, sizeof(KvmErrRec));
+  cudaMemset(h->d_versions, 0, h->nvars * sizeof(int)); cudaMemset(h->d_err, 0, sizeof(KvmErrRec)); cudaMemset(h->d_ctl, 0, 64 * sizeof(int));
+  if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail("init", e);
+  *out = h;
+  return 0;
+}
+
+extern "C" void kvm_destroy(KvmExec* h) {
+  if (!h) return;
+  cudaSetDevice(h->device);
+  cudaStreamSynchronize(h->stream);
+  for (auto& o : h->owned) cudaFree(o.p);
+  kvm_free_tasks(h);
+  for (void* p : {(void*)h->d_bufs, (void*)h->d_ctl, (void*)h->d_versions, (void*)h->d_park_head, (void*)h->d_err}) if (p) cudaFree(p);
+  if (h->ev0) cudaEventDestroy(h->ev0);
+  if (h->ev1) cudaEventDestroy(h->ev1);
+  if (h->stream) cudaStreamDestroy(h->stream);
+  delete h;
+}
+
+static size_t kvm_elem_bytes(int dtype) { return dtype == KVM_BF16 ? 2 : 4; }
+
+extern "C" int kvm_add_buffer(KvmExec* h, int32_t rows, int32_t cols, int32_t dtype, const KvmInit* init) {
+  if (!h) return KVM_E_ARG;
+  if (rows < 1 || cols < 1 || dtype < 0 || dtype > 2 || (long long)rows * cols > 2147483647LL) { h->error = "kvm_add_buffer: bad shape or dtype"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  const size_t n = (size_t)rows * cols, bytes = n * kvm_elem_bytes(dtype);
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes < 256 ? 256 : bytes) != cudaSuccess) { cudaGetLastError(); h->error = "kvm_add_buffer: out of device memory"; return KVM_E_NOMEM; }
+  const int kind = init ? init->kind : KVM_INIT_FILL;
+  const int blocks = (int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
+  if (kind == KVM_INIT_FILL) kvm_fill_kernel<<<blocks, 256, 0, h->stream>>>(p, n, dtype, init ? init->fill : 0.0);
+  else if (kind == KVM_INIT_VALUES) {
+    if (!init->data) { cudaFree(p); h->error = "kvm_add_buffer: VALUES init without data"; return KVM_E_ARG; }
+    KVM_CUDA(cudaMemcpyAsync(p, init->data, bytes, cudaMemcpyHostToDevice, h->stream));
+    KVM_CUDA(cudaStreamSynchronize(h->stream));
+  } else if (kind == KVM_INIT_SEEDED) {
+    if (dtype != KVM_F32 || (init->draws != 1 && init->draws != 4)) { cudaFree(p); h->error = "kvm_add_buffer: seeded init needs f32 and draws 1 or 4"; return KVM_E_ARG; }
+    kvm_seeded_kernel<<<blocks, 256, 0, h->stream>>>((float*)p, n, init->seed, init->draws, init->bias, init->coef);
+  } else if (kind != KVM_INIT_NONE) { cudaFree(p); h->error = "kvm_add_buffer: unknown init kind"; return KVM_E_ARG; }
+  KVM_CUDA(cudaGetLastError());
+  KvmBuf b{p, rows, cols, cols, dtype, {0, 0}};
+  h->bufs.push_back(b);
+  h->owned.push_back({p, bytes});
+  h->bufs_dirty = true;
+  return (int)h->bufs.size() - 1;
+}
+
+extern "C" int kvm_bind_buffer(KvmExec* h, void* dev_ptr, int32_t rows, int32_t cols, int32_t ld, int32_t dtype) {
+  if (!h || !dev_ptr || rows < 1 || cols < 1 || ld < cols || dtype < 0 || dtype > 2) { if (h) h->error = "kvm_bind_buffer: bad argument"; return KVM_E_ARG; }
+  KvmBuf b{dev_ptr, rows, cols, ld, dtype, {0, 0}};
+  h->bufs.push_back(b);
+  h->bufs_dirty = true;
+  return (int)h->bufs.size() - 1;
+}
+
+extern "C" void* kvm_buffer_ptr(KvmExec* h, int32_t idx) { return (h && idx >= 0 && idx < (int)h->bufs.size()) ? h->bufs[idx].p : nullptr; }
+
+static int kvm_buf_span(KvmExec* h, int idx, size_t bytes, size_t offset) {
+  if (!h || idx < 0 || idx >= (int)h->bufs.size()) { if (h) h->error = "buffer index out of range"; return KVM_E_ARG; }
+  const KvmBuf& b = h->bufs[idx];
+  if (offset + bytes > (size_t)b.rows * b.ld * kvm_elem_bytes(b.dtype)) { h->error = "buffer copy out of range"; return KVM_E_ARG; }
+  return 0;
+}
+extern "C" int kvm_write_buffer(KvmExec* h, int32_t idx, const void* host, size_t bytes, size_t offset) {
+  if (int r = kvm_buf_span(h, idx, bytes, offset)) return r;
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaMemcpyAsync((char*)h->bufs[idx].p + offset, host, bytes, cudaMemcpyHostToDevice, h->stream));
+  return 0;     // ordered before the next launch on the same stream; the source must stay valid until then (pinned) or is staged by CUDA (pageable)
+}
+extern "C" int kvm_read_buffer_raw(KvmExec* h, int32_t idx, void* host, size_t bytes, size_t offset) {
+  if (int r = kvm_buf_span(h, idx, bytes, offset)) return r;
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaMemcpyAsync(host, (const char*)h->bufs[idx].p + offset, bytes, cudaMemcpyDeviceToHost, h->stream));
+  KVM_CUDA(cudaStreamSynchronize(h->stream));
+  return 0;
+}
+extern "C" int kvm_read_buffer(KvmExec* h, int32_t idx, float* out, size_t n) {
+  if (!h || idx < 0 || idx >= (int)h->bufs.size() || !out) { if (h) h->error = "kvm_read_buffer: bad argument"; return KVM_E_ARG; }
+  const KvmBuf& b = h->bufs[idx];
+  if (b.ld != b.cols || n > (size_t)b.rows * b.cols) { h->error = "kvm_read_buffer: range"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  if (b.dtype == KVM_F32) { KVM_CUDA(cudaMemcpyAsync(out, b.p, n * 4, cudaMemcpyDeviceToHost, h->stream)); KVM_CUDA(cudaStreamSynchronize(h->stream)); return 0; }
+  float* tmp = nullptr;
+  KVM_CUDA(cudaMalloc(&tmp, n * 4));
+  kvm_widen_kernel<<<(int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048), 256, 0, h->stream>>>(b.p, tmp, n, b.dtype);
+  cudaError_t e = cudaMemcpyAsync(out, tmp, n * 4, cudaMemcpyDeviceToHost, h->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  cudaFree(tmp);
+  KVM_CUDA(e);
+  return 0;
+}
+
+extern "C" int kvm_set_version(KvmExec* h, int32_t var, int32_t version) {
+  if (!h || var < 0 || var >= h->nvars || version < 0) { if (h) h->error = "kvm_set_version: bad variable"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaMemcpyAsync(h->d_versions + var, &version, 4, cudaMemcpyHostToDevice, h->stream));
+  KVM_CUDA(cudaStreamSynchronize(h->stream));
+  return 0;
+}
+extern "C" int kvm_get_version(KvmExec* h, int32_t var, int32_t* version) {
+  if (!h || var < 0 || var >= h->nvars || !version) { if (h) h->error = "kvm_get_version: bad variable"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaMemcpyAsync(version, h->d_versions + var, 4, cudaMemcpyDeviceToHost, h->stream));
+  KVM_CUDA(cudaStreamSynchronize(h->stream));
+  return 0;
+}
+
+// The host check of MvmBundle::validate (mvm_exec.cu:141-208): first problem as text, "" if well formed.
+static std::string kvm_validate(const KvmTaskDesc* t, int nt, const int32_t* succ, int ne, const int32_t* args, int na, int nbufs, int nvars) {
+  char m[256];
+  if (nt <= 0) return "empty bundle";
+  std::vector<int> in(nt, 0);
+  for (int i = 0; i < nt; ++i) {
+    const KvmTaskDesc& d = t[i];
+    const KvmOpInfo* op = kvm_find_op(d.op_id);
+    if (!op) { snprintf(m, sizeof m, "task %d: bad op_id %d", i, d.op_id); return m; }
+    if (d.args_words != op->arity) { snprintf(m, sizeof m, "task %d: %s takes %d args, got %d", i, op->name, op->arity, d.args_words); return m; }
+    if (d.args_off < 0 || (long long)d.args_off + d.args_words > na) { snprintf(m, sizeof m, "task %d: args range", i); return m; }
+    if (d.succ_off < 0 || d.succ_cnt < 0 || (long long)d.succ_off + d.succ_cnt > ne) { snprintf(m, sizeof m, "task %d: successor range", i); return m; }
+    if (d.priority < 0 || d.priority >= 32) { snprintf(m, sizeof m, "task %d: priority %d outside [0,31]", i, d.priority); return m; }
+    if (d.deadline_us < -1) { snprintf(m, sizeof m, "task %d: deadline_us", i); return m; }
+    for (int v : {d.wait_var, d.pub_var}) if (v < -1 || v >= nvars) { snprintf(m, sizeof m, "task %d: version variable %d out of range", i, v); return m; }
+    if ((d.wait_var >= 0 && d.wait_ver < 0) || (d.pub_var >= 0 && d.pub_ver < 1)) { snprintf(m, sizeof m, "task %d: wait_ver >= 0 and pub_ver >= 1 (0 is the initial state)", i); return m; }
+    for (int j = 0; j < op->arity; ++j)
+      if (op->types[j] >= 2) {
+        const int b = args[d.args_off + j];
+        if ((b == -1 && op->types[j] == 2) || b < -1 || b >= nbufs) { snprintf(m, sizeof m, "task %d: %s arg %d buffer index %d out of range", i, op->name, j, b); return m; }
+      }
+    for (int k = 0; k < d.succ_cnt; ++k) {
+      const int s = succ[d.succ_off + k];
+      if (s < 0 || s >= nt || s == i) { snprintf(m, sizeof m, "task %d: successor %d out of range", i, s); return m; }
+      ++in[s];
+    }
+  }
+  for (int i = 0; i < nt; ++i) if (in[i] != t[i].indegree) { snprintf(m, sizeof m, "task %d: indegree %d != in-edges %d", i, t[i].indegree, in[i]); return m; }
+  std::vector<int> q, rem = in;
+  q.reserve(nt);
+  for (int i = 0; i < nt; ++i) if (!rem[i]) q.push_back(i);
+  for (size_t x = 0; x < q.size(); ++x) {
+    const KvmTaskDesc& d = t[q[x]];
+    for (int k = 0; k < d.succ_cnt; ++k) if (--rem[succ[d.succ_off + k]] == 0) q.push_back(succ[d.succ_off + k]);
+  }
+  if ((int)q.size() != nt) return "dependency cycle";
+  // version waits decidable inside the batch: publisher -> waiter edges must keep the graph acyclic
+  std::vector<std::pair<int, int>> extra;
+  for (int i = 0; i < nt; ++i) if (t[i].wait_var >= 0)
+    for (int p = 0; p < nt; ++p) if (t[p].pub_var == t[i].wait_var && t[p].pub_ver <= t[i].wait_ver) {
+      if (p == i) { snprintf(m, sizeof m, "task %d: waits for version %d of variable %d that it publishes itself", i, t[i].wait_ver, t[i].wait_var); return m; }
+      extra.push_back({p, i});
+    }
+  if (!extra.empty()) {
+    std::vector<int> deg = in;
+    std::vector<std::vector<int>> xs(nt);
+    for (auto& e : extra) { ++deg[e.second]; xs[e.first].push_back(e.second); }
+    std::vector<int> st;
+    int seen = 0;
+    for (int i = 0; i < nt; ++i) if (!deg[i]) st.push_back(i);
+    while (!st.empty()) {
+      const int u = st.back(); st.pop_back(); ++seen;
+      for (int k = 0; k < t[u].succ_cnt; ++k) { const int v = succ[t[u].succ_off + k]; if (--deg[v] == 0) st.push_back(v); }
+      for (int v : xs[u]) if (--deg[v] == 0) st.push_back(v);
+    }
+    if (seen != nt) return "version-wait cycle: a task waits for a version that only a task depending on it can publish";
+  }
+  return "";
+}
+
+static int kvm_plan_tc(KvmExec* h, int first_task);   // kvm_gemm_host.inl: tensor maps of the tensor-core tasks
+
+extern "C" int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na) {
+  if (!h || !tasks || nt <= 0 || ne < 0 || na < 0 || (ne && !succ) || (na && !args)) { if (h) h->error = "kvm_submit: bad argument"; return KVM_E_ARG; }
+  if (h->started) { h->error = "kvm_submit: a run is in flight"; return KVM_E_STATE; }
+  const std::string problem = kvm_validate(tasks, nt, succ, ne, args, na, (int)h->bufs.size(), h->nvars);
+  if (!problem.empty()) { h->error = problem; return KVM_E_BUNDLE; }
+  const int tbase = (int)h->tasks.size(), sbase = (int)h->succ.size(), abase = (int)h->args.size();
+  for (int i = 0; i < nt; ++i) { KvmTaskDesc d = tasks[i]; d.succ_off += sbase; d.args_off += abase; h->tasks.push_back(d); }
+  for (int i = 0; i < ne; ++i) h->succ.push_back(succ[i] + tbase);
+  h->args.insert(h->args.end(), args, args + na);
+  h->aux.resize(h->tasks.size(), make_int4(0, 0, 0, 0));
+  h->tasks_dirty = true; h->armed = false;
+  return kvm_plan_tc(h, tbase);
+}
+
+static bool kvm_read_file(const std::string& path, std::vector<char>& out) {
+  FILE* f = fopen(path.c_str(), "rb");
+  if (!f) return false;
+  fseek(f, 0, SEEK_END); long n = ftell(f); fseek(f, 0, SEEK_SET);
+  out.resize(n > 0 ? n : 0);
+  const bool ok = n <= 0 || fread(out.data(), 1, n, f) == (size_t)n;
+  fclose(f);
+  return ok;
+}
+extern "C" int kvm_submit_bundle_dir(KvmExec* h, const char* dir) {
+  if (!h || !dir) return KVM_E_ARG;
+  std::vector<char> t, s, a;
+  const std::string d(dir);
+  if (!kvm_read_file(d + "/tasks.bin", t) || !kvm_read_file(d + "/successors.bin", s) || !kvm_read_file(d + "/args.bin", a)) { h->error = "cannot read bundle files in " + d; return KVM_E_IO; }
+  if (t.size() % sizeof(KvmTaskDesc) || s.size() % 4 || a.size() % 4) { h->error = "bundle file sizes are not whole records"; return KVM_E_BUNDLE; }
+  return kvm_submit(h, (const KvmTaskDesc*)t.data(), (int)(t.size() / sizeof(KvmTaskDesc)), (const int32_t*)s.data(), (int)(s.size() / 4), (const int32_t*)a.data(), (int)(a.size() / 4));
+}
+
+extern "C" int kvm_clear_tasks(KvmExec* h) {
+  if (!h) return KVM_E_ARG;
+  if (h->started) { h->error = "kvm_clear_tasks: a run is in flight"; return KVM_E_STATE; }
+  h->tasks.clear(); h->succ.clear(); h->args.clear(); h->aux.clear(); h->tmaps.clear();
+  h->tasks_dirty = true; h->armed = false;
+  return 0;
+}
+
+static KvmDevState kvm_dev_state(KvmExec* h) {
+  KvmDevState S{};
+  S.tasks = h->d_tasks; S.succ = h->d_succ; S.args = h->d_args; S.nt = (int)h->tasks.size();
+  S.indeg = h->d_indeg; S.exec_count = h->d_exec; S.ring = h->d_ring;
+  S.head = (unsigned*)h->d_ctl; S.tail = (unsigned*)h->d_ctl + 1; S.done = h->d_ctl + 2;
+  S.bufs = h->d_bufs; S.nbufs = (int)h->bufs.size();
+  S.versions = h->d_versions; S.nvars = h->nvars; S.park_head = h->d_park_head; S.park_next = h->d_park_next;
+  S.err = h->d_err;
+  S.t_start = h->d_tstart; S.t_end = h->d_tend; S.t_smid = h->d_tsmid; S.trace = h->cfg.trace;
+  S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
+  S.cfg_flags = h->cfg.flags;
+  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux;
+  return S;
+}
+
+// Upload whatever changed since the last run, arm the counters and enqueue the roots.
+static int kvm_prepare(KvmExec* h) {
+  cudaSetDevice(h->device);
+  const size_t nt = h->tasks.size();
+  if (nt == 0) { h->error = "nothing submitted"; return KVM_E_STATE; }
+  if (h->bufs_dirty) {
+    if (h->bufs.size() > h->d_bufs_cap) {
+      if (h->d_bufs) cudaFree(h->d_bufs);
+      h->d_bufs_cap = h->bufs.size() * 2 + 16;
+      KVM_CUDA(cudaMalloc(&h->d_bufs, h->d_bufs_cap * sizeof(KvmBuf)));
+    }
+    KVM_CUDA(cudaMemcpyAsync(h->d_bufs, h->bufs.data(), h->bufs.size() * sizeof(KvmBuf), cudaMemcpyHostToDevice, h->stream));
+    h->bufs_dirty = false;
+  }
+  if (h->tasks_dirty) {
+    kvm_free_tasks(h);
+    KVM_CUDA(cudaMalloc(&h->d_tasks, nt * sizeof(KvmTaskDesc)));
+    KVM_CUDA(cudaMalloc(&h->d_succ, (h->succ.size() + 1) * 4));
+    KVM_CUDA(cudaMalloc(&h->d_args, (h->args.size() + 1) * 4));
+    KVM_CUDA(cudaMalloc(&h->d_aux, nt * sizeof(int4)));
+    KVM_CUDA(cudaMalloc(&h->d_tmaps, (h->tmaps.size() + 1) * sizeof(CUtensorMap)));
+    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4));
+    if (h->cfg.trace) { KVM_CUDA(cudaMalloc(&h->d_tstart, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tend, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tsmid, nt * 4)); }
+    KVM_CUDA(cudaMemcpyAsync(h->d_tasks, h->tasks.data(), nt * sizeof(KvmTaskDesc), cudaMemcpyHostToDevice, h->stream));
+    if (!h->succ.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_succ, h->succ.data(), h->succ.size() * 4, cudaMemcpyHostToDevice, h->stream));
+    if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
+    KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
+    if (!h->tmaps.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_tmaps, h->tmaps.data(), h->tmaps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+    h->tasks_dirty = false; h->task_cap = nt;
+  }
+  KvmDevState S = kvm_dev_state(h);
+  KVM_CUDA(cudaMemsetAsync(h->d_ctl, 0, 64 * sizeof(int), h->stream));
+  KVM_CUDA(cudaMemsetAsync(h->d_err, 0, sizeof(KvmErrRec), h->stream));
+  if (h->cfg.trace) { cudaMemsetAsync(h->d_tstart, 0, nt * 8, h->stream); cudaMemsetAsync(h->d_tend, 0, nt * 8, h->stream); }
+  const int blocks = (int)((nt > (size_t)h->nvars ? nt : (size_t)h->nvars) + 255) / 256;
+  kvm_arm_kernel<<<blocks, 256, 0, h->stream>>>(S);
+  kvm_roots_kernel<<<blocks, 256, 0, h->stream>>>(S);
+  KVM_CUDA(cudaGetLastError());
+  h->armed = true;
+  return 0;
+}
+
+extern "C" int kvm_rearm(KvmExec* h) {
+  if (!h) return KVM_E_ARG;
+  if (h->started) { h->error = "kvm_rearm: a run is in flight"; return KVM_E_STATE; }
+  return kvm_prepare(h);
+}
+
+extern "C" int kvm_start(KvmExec* h) {
+  if (!h) return KVM_E_ARG;
+  if (h->started) { h->error = "kvm_start: already started"; return KVM_E_STATE; }
+  if (!h->armed) if (int r = kvm_prepare(h)) return r;
+  KvmDevState S = kvm_dev_state(h);
+  KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
+  kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);
+  KVM_CUDA(cudaGetLastError());
+  KVM_CUDA(cudaEventRecord(h->ev1, h->stream));
+  h->started = true; h->armed = false;
+  return 0;
+}
+
+extern "C" int kvm_finish(KvmExec* h, KvmResult* res) {
+  if (!h) return KVM_E_ARG;
+  if (!h->started) { h->error = "kvm_finish: nothing started"; return KVM_E_STATE; }
+  h->started = false;
+  KVM_CUDA(cudaStreamSynchronize(h->stream));
+  int ctl[4]; KvmErrRec er;
+  KVM_CUDA(cudaMemcpy(ctl, h->d_ctl, sizeof ctl, cudaMemcpyDeviceToHost));
+  KVM_CUDA(cudaMemcpy(&er, h->d_err, sizeof er, cudaMemcpyDeviceToHost));
+  KvmResult r{};
+  r.status = er.code; r.done = ctl[2]; r.admitted = (int)h->tasks.size();
+  r.err_task = er.code ? er.task : -1; r.err_a = er.a; r.err_b = er.b;
+  cudaEventElapsedTime(&r.ms, h->ev0, h->ev1);
+  if (h->cfg.trace && !h->tasks.empty()) {
+    const size_t nt = h->tasks.size();
+    std::vector<unsigned long long> s(nt), e(nt);
+    cudaMemcpy(s.data(), h->d_tstart, nt * 8, cudaMemcpyDeviceToHost); cudaMemcpy(e.data(), h->d_tend, nt * 8, cudaMemcpyDeviceToHost);
+    unsigned long long lo = ~0ull, hi = 0; double busy = 0;
+    for (size_t i = 0; i < nt; ++i) if (e[i] > s[i] && s[i]) { busy += (double)(e[i] - s[i]); if (s[i] < lo) lo = s[i]; if (e[i] > hi) hi = e[i]; }
+    if (hi > lo) r.busy_frac = (float)(busy / ((double)h->workers * (double)(hi - lo)));
+  }
+  if (er.code) {
+    char m[200];
+    snprintf(m, sizeof m, "device error %d (%s) at task %d, detail %d %d; %d/%d tasks done", er.code, kvm_err_name(er.code), er.task, er.a, er.b, r.done, r.admitted);
+    h->error = m;
+  } else if (r.done != r.admitted) {
+    r.status = KVM_ERR_TIMEOUT; h->error = "run ended with unfinished tasks";
+  }
+  h->last = r;
+  if (res) *res = r;
+  return r.status;
+}
+
+extern "C" int kvm_run(KvmExec* h, KvmResult* res) {
+  if (int r = kvm_start(h)) { if (res) { *res = KvmResult{}; res->status = r; } return r; }
+  return kvm_finish(h, res);
+}
+
+extern "C" int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t n) {
+  if (!h || n < 0 || n > (int)h->tasks.size() || !h->d_exec) { if (h) h->error = "kvm_task_counts: bad argument or no run yet"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  if (exec_count) KVM_CUDA(cudaMemcpy(exec_count, h->d_exec, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  if (observed) {
+    std::vector<int> rem(n);
+    KVM_CUDA(cudaMemcpy(rem.data(), h->d_indeg, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; ++i) observed[i] = h->tasks[i].indegree - rem[i];
+  }
+  return 0;
+}
+extern "C" int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32_t* smid, int32_t n) {
+  if (!h || !h->cfg.trace || n < 0 || n > (int)h->tasks.size() || !h->d_tstart) { if (h) h->error = "kvm_trace: tracing is off or no run yet"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  if (start_ns) KVM_CUDA(cudaMemcpy(start_ns, h->d_tstart, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  if (end_ns) KVM_CUDA(cudaMemcpy(end_ns, h->d_tend, (size_t)n * 8, cudaMemcpyDeviceToHost));
+  if (smid) KVM_CUDA(cudaMemcpy(smid, h->d_tsmid, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  return 0;
+}
+extern "C" int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes) {
+  if (!h) return KVM_E_ARG;
+  if (workers) *workers = h->workers;
+  if (threads) *threads = KVM_NT + 32;
+  if (smem_bytes) *smem_bytes = h->smem_bytes;
+  return 0;
+}
+
+#include "kvm_gemm_host.inl"

@@ -1,0 +1,293 @@
+// Decode (serving) ops: KV-cache append, one-row attention over the cache (whole and split-context flash-decoding with
+// optional fused RoPE + append), the bf16 weight-streaming GEMV with RMSNorm / SwiGLU prologue, and token sampling.
+// Reference semantics: runtime/ref_gpt.py:367-410,485-545, runtime/ref_extra.py:398-498; layouts from
+// include/mvm_ops_gpt.def:19-20 (cache [B*Hkv*Tmax, hd], row (b*Hkv+kvh)*Tmax+t) and include/mvm_ops_extra.def:79-95.
+#pragma once
+#include "kvm_dev.cuh"
+#include "kvm_ops_flat.cuh"
+#include "kvm_ops_rows.cuh"
+
+#define KVM_ATTN_EMPTY_M (-3.4028234663852886e38f)
+
+__device__ void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
+  KvmBuf kn, vn, kc, vc, lens;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, kn) || !kvm_buf(c, a[1], KVM_M_FLT, vn) || !kvm_buf(c, a[2], KVM_M_FLT, kc) || !kvm_buf(c, a[3], KVM_M_FLT, vc) ||
+      !kvm_buf(c, a[4], KVM_M_I32, lens)) return;
+  const int b0 = a[5], b1 = a[6], nn = a[7], Hkv = a[8], hd = a[9], Tmax = a[10];
+  if (b0 < 0 || b1 < b0 || nn <= 0 || Hkv <= 0 || hd <= 0 || Tmax <= 0 || !kvm_mat_ok(c, kn, (long long)b1 * nn, Hkv * hd) || !kvm_mat_ok(c, vn, (long long)b1 * nn, Hkv * hd) ||
+      !kvm_mat_ok(c, kc, (long long)b1 * Hkv * Tmax, hd) || !kvm_mat_ok(c, vc, (long long)b1 * Hkv * Tmax, hd) || !kvm_flat_ok(c, lens, b1)) { c.fail(KVM_OPE_RANGE, b0, b1); return; }
+  for (int bb = b0; bb < b1; ++bb) { const int L = ((const int*)lens.p)[bb]; if (L < 0 || L + nn > Tmax) { c.fail(KVM_OPE_KVLEN, bb, L); return; } }
+  const long long per = (long long)nn * Hkv * hd;
+  for (long long e = threadIdx.x; e < (long long)(b1 - b0) * per; e += KVM_NT) {
+    const int bb = b0 + (int)(e / per), t = (int)((e % per) / (Hkv * hd)), h = (int)((e % (Hkv * hd)) / hd), cc = (int)(e % hd);
+    const size_t row = (size_t)(bb * Hkv + h) * Tmax + ((const int*)lens.p)[bb] + t;
+    kvm_st(kc, row * kc.ld + cc, kvm_ld(kn, (size_t)(bb * nn + t) * kn.ld + h * hd + cc));
+    kvm_st(vc, row * vc.ld + cc, kvm_ld(vn, (size_t)(bb * nn + t) * vn.ld + h * hd + cc));
+  }
+}
+
+// Partial attention of one GQA group (G <= 8 query heads sharing one kv head) over cache rows [j0,j1) of `base`.
+// Warps take keys j0+warp, j0+warp+16, ...; lanes hold hd/32 (<= 4) columns.  Results (m, l, acc[hd]) per head are merged over
+// the 16 warps in warp order through shared memory, then handed to `emit(g, m, l, acc_of_column)` per head.
+//   qs: G*hd floats in shared memory (the query rows, already rotated)       ws: scratch of 16*G*(hd+2) floats
+template <class Emit>
+__device__ void kvm_decode_group(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nc = (hd + 31) / 32;
+  float m[8], l[8], acc[8][4];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) { m[g] = KVM_ATTN_EMPTY_M; l[g] = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) acc[g][t] = 0.0f; }
+  for (int j = j0 + warp; j < j1; j += KVM_NWARPS) {
+    float kr[4], vr[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int cc = lane + 32 * t;
+      kr[t] = (t < nc && cc < hd) ? kvm_ld(kc, (base + j) * kc.ld + cc) : 0.0f;
+      vr[t] = (t < nc && cc < hd) ? kvm_ld(vc, (base + j) * vc.ld + cc) : 0.0f;
+    }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) if (g < G) {
+      float s = 0.0f;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) if (t < nc && lane + 32 * t < hd) s += qs[g * hd + lane + 32 * t] * kr[t];
+      s = kvm_warp_sum(s) * sc;
+      const float mn = fmaxf(m[g], s), corr = __expf(m[g] - mn), p = __expf(s - mn);
+      l[g] = l[g] * corr + p;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) acc[g][t] = acc[g][t] * corr + p * vr[t];
+      m[g] = mn;
+    }
+  }
+  const int stride = hd + 2;
+  kvm_sync();
+#pragma unroll
+  for (int g = 0; g < 8; ++g) if (g < G) {
+    float* w = ws + (size_t)(warp * G + g) * stride;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) if (t < nc && lane + 32 * t < hd) w[lane + 32 * t] = acc[g][t];
+    if (lane == 0) { w[hd] = m[g]; w[hd + 1] = l[g]; }
+  }
+  kvm_sync();
+  // merge over warps: thread (g, column)
+  for (int e = threadIdx.x; e < G * hd; e += KVM_NT) {
+    const int g = e / hd, cc = e % hd;
+    float M = KVM_ATTN_EMPTY_M;
+    for (int w = 0; w < KVM_NWARPS; ++w) if (ws[(size_t)(w * G + g) * stride + hd + 1] > 0.0f) M = fmaxf(M, ws[(size_t)(w * G + g) * stride + hd]);
+    float L = 0.0f, A = 0.0f;
+    for (int w = 0; w < KVM_NWARPS; ++w) {
+      const float* r = ws + (size_t)(w * G + g) * stride;
+      if (r[hd + 1] > 0.0f) { const float e2 = __expf(r[hd] - M); L += e2 * r[hd + 1]; A += e2 * r[cc]; }
+    }
+    emit(g, cc, M, L, A);
+  }
+}
+
+__device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
+  KvmBuf q, kc, vc, lens, o;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
+      !kvm_buf(c, a[4], KVM_M_FLT, o)) return;
+  const int b = a[5], h = a[6], H = a[7], Hkv = a[8], hd = a[9], Tmax = a[10];
+  const float sc = kvm_bits_f32(a[11]);
+  if (b < 0 || h < 0 || h >= H || Hkv <= 0 || H % Hkv || hd <= 0 || hd > 128 || Tmax <= 0) { c.fail(KVM_OPE_SHAPE, h, hd); return; }
+  if (!kvm_mat_ok(c, q, b + 1, H * hd) || !kvm_mat_ok(c, o, b + 1, H * hd) || !kvm_mat_ok(c, kc, (long long)(b + 1) * Hkv * Tmax, hd) ||
+      !kvm_mat_ok(c, vc, (long long)(b + 1) * Hkv * Tmax, hd) || !kvm_flat_ok(c, lens, b + 1)) return;
+  const int L = ((const int*)lens.p)[b], n = L + 1;
+  if (L < 0 || n > Tmax) { c.fail(KVM_OPE_KVLEN, b, L); return; }
+  float* qs = (float*)c.smem;
+  float* ws = qs + 128;
+  kvm_sync();
+  for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) qs[cc] = kvm_ld(q, (size_t)b * q.ld + h * hd + cc);
+  kvm_sync();
+  const size_t base = (size_t)(b * Hkv + h / (H / Hkv)) * Tmax;
+  kvm_decode_group(kc, vc, base, 0, n, 1, hd, sc, qs, ws, [&](int, int cc, float, float Lsum, float A) { kvm_st(o, (size_t)b * o.ld + h * hd + cc, A / Lsum); });
+}
+
+__device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
+  KvmBuf q, kc, vc, lens, part, kn, vn;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
+      !kvm_buf(c, a[4], KVM_M_F32, part) || !kvm_buf(c, a[5], KVM_M_FLT, kn, true) || !kvm_buf(c, a[6], KVM_M_FLT, vn, true)) return;
+  const int b = a[7], kvh = a[8], s = a[9], S = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
+  const float sc = kvm_bits_f32(a[15]), theta = kvm_bits_f32(a[16]);
+  if (b < 0 || Hkv <= 0 || H % Hkv || kvh < 0 || kvh >= Hkv || s < 0 || s >= S || Tmax <= 0 || hd <= 0 || hd > 128 || (hd & 7) || H / Hkv > 8 ||
+      !(fl == 0 || fl == 1 || fl == 3) || ((fl & 1) && (!kn.p || !vn.p))) { c.fail(KVM_OPE_SHAPE, hd, fl); return; }
+  const int G = H / Hkv;
+  if (!kvm_mat_ok(c, q, b + 1, H * hd) || !kvm_mat_ok(c, kc, (long long)(b + 1) * Hkv * Tmax, hd) || !kvm_mat_ok(c, vc, (long long)(b + 1) * Hkv * Tmax, hd) ||
+      !kvm_flat_ok(c, lens, b + 1) || !kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) || !kvm_mat_ok(c, kn, b + 1, Hkv * hd) || !kvm_mat_ok(c, vn, b + 1, Hkv * hd)) return;
+  const int p0 = ((const int*)lens.p)[b], n = p0 + 1;
+  if (p0 < 0 || n > Tmax) { c.fail(KVM_OPE_KVLEN, b, p0); return; }
+  const int chunk = (n + S - 1) / S, j0 = s * chunk, j1 = min(n, s * chunk + chunk), half = hd / 2;
+  const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
+  float* qs = (float*)c.smem;                 // G*hd
+  float* inv = qs + 8 * 128;                  // hd/2 inverse frequencies
+  float* ws = inv + 64;
+  kvm_sync();
+  if (fl & 1) for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
+  kvm_sync();
+  if ((fl & 1) && j0 <= n - 1 && n - 1 < j1) {   // this split appends the new key / value (rotated key), rounded to the cache dtype
+    for (int i = threadIdx.x; i < half; i += KVM_NT) {
+      float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+      const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
+      kvm_st(kc, (base + n - 1) * kc.ld + i, x1 * co - x2 * sn);
+      kvm_st(kc, (base + n - 1) * kc.ld + i + half, x1 * sn + x2 * co);
+    }
+    for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) kvm_st(vc, (base + n - 1) * vc.ld + cc, kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc));
+    __threadfence_block();
+  }
+  for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
+    const int g = e / half, i = e % half, h = kvh * G + g;
+    float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
+    if (fl & 1) {
+      float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+      const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+      x1 = y1; x2 = y2;
+      if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
+    }
+    qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
+  }
+  kvm_sync();
+  float* pp = (float*)part.p;
+  kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, [&](int g, int cc, float M, float Lsum, float A) {
+    const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
+    pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
+    if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M; pp[row + hd + 1] = Lsum; }
+  });
+}
+
+__device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
+  KvmBuf part, o;
+  if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
+  const int b = a[2], h0 = a[3], h1 = a[4], S = a[5], H = a[6], hd = a[7];
+  if (b < 0 || h0 < 0 || h1 <= h0 || h1 > H || S <= 0 || hd <= 0 || !kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) || !kvm_mat_ok(c, o, b + 1, H * hd)) {
+    c.fail(KVM_OPE_RANGE, h0, h1); return; }
+  const float* pp = (const float*)part.p;
+  for (int e = threadIdx.x; e < (h1 - h0) * hd; e += KVM_NT) {
+    const int h = h0 + e / hd, cc = e % hd;
+    float M = KVM_ATTN_EMPTY_M;
+    for (int s = 0; s < S; ++s) { const float* r = pp + ((size_t)(b * S + s) * H + h) * part.ld; if (r[hd + 1] > 0.0f) M = fmaxf(M, r[hd]); }
+    float L = 0.0f, A = 0.0f;
+    for (int s = 0; s < S; ++s) {
+      const float* r = pp + ((size_t)(b * S + s) * H + h) * part.ld;
+      if (r[hd + 1] > 0.0f) { const float e2 = __expf(r[hd] - M); L += e2 * r[hd + 1]; A += e2 * r[cc]; }
+    }
+    kvm_st(o, (size_t)b * o.ld + h * hd + cc, A / L);
+  }
+}
+
+// out[0,n] = sum_k v[k] w[n,k] (+ res[0,n]), v = bf16(prologue(x)); w bf16 [>=n1, K], rows contiguous in K.
+// The activation row is staged once per task in shared memory (as float); each warp then streams four weight rows at a
+// time with 16-byte loads, two k-steps in flight, float32 accumulation in a fixed order, warp-shuffle reduction.
+__device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
+  KvmBuf x, x2, gm, w, out, res;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, x2, true) || !kvm_buf(c, a[2], KVM_M_F32, gm, true) || !kvm_buf(c, a[3], KVM_M_BF16, w) ||
+      !kvm_buf(c, a[4], KVM_M_FLT, out) || !kvm_buf(c, a[5], KVM_M_FLT, res, true)) return;
+  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
+  const float eps = kvm_bits_f32(a[10]);
+  if (n0 < 0 || n1 <= n0 || K <= 0 || (K & 7) || pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || (w.ld & 7) || !kvm_vec_ok(w) ||
+      K * 4 + 256 > c.smem_bytes) { c.fail(KVM_OPE_SHAPE, K, pro); return; }
+  if (!kvm_mat_ok(c, w, n1, K) || !kvm_mat_ok(c, x, 1, K) || !kvm_mat_ok(c, x2, 1, K) || !kvm_flat_ok(c, gm, K) || !kvm_mat_ok(c, out, 1, n1) || !kvm_mat_ok(c, res, 1, n1)) return;
+  float* vs = (float*)c.smem;
+  float* red = vs + K;
+  float rs = 1.0f;
+  if (pro == 1) {
+    float q = 0.0f;
+    for (int k = threadIdx.x; k < K; k += KVM_NT) { const float t = kvm_ld(x, k); q += t * t; }
+    q = kvm_block_sum(q, red);
+    rs = 1.0f / sqrtf(q / K + eps);
+  }
+  kvm_sync();
+  for (int k = threadIdx.x; k < K; k += KVM_NT) {
+    const float t = kvm_ld(x, k);
+    vs[k] = kvm_bf16_round(pro == 1 ? t * rs * ((const float*)gm.p)[k] : pro == 2 ? kvm_silu(t) * kvm_ld(x2, k) : t);
+  }
+  kvm_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p;
+  for (int nb = n0 + warp * 4; nb < n1; nb += KVM_NWARPS * 4) {
+    float acc[4] = {0, 0, 0, 0};
+    const int nr = min(4, n1 - nb);
+    for (int k = lane * 8; k < K; k += 512) {
+      uint4 u[4][2];
+      const bool two = k + 256 < K;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const __nv_bfloat16* row = wp + (size_t)(nb + (r < nr ? r : 0)) * w.ld;
+        u[r][0] = __ldcs((const uint4*)(row + k));
+        u[r][1] = two ? __ldcs((const uint4*)(row + k + 256)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int hstep = 0; hstep < 2; ++hstep) {
+        if (hstep == 1 && !two) break;
+        const float* vv = vs + k + hstep * 256;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const __nv_bfloat162* hh = (const __nv_bfloat162*)&u[r][hstep];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hh[j]); acc[r] = fmaf(vv[2 * j], f.x, acc[r]); acc[r] = fmaf(vv[2 * j + 1], f.y, acc[r]); }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float s = kvm_warp_sum(acc[r]);
+      if (lane == 0 && r < nr) {
+        const int n = nb + r;
+        kvm_st(out, n, res.p ? __fadd_rn(s, kvm_ld(res, n)) : s);
+      }
+    }
+  }
+}
+
+// ---- sampling: Philox-4x32-10 counter (row, ctr, 0, 0), key (seed, 0x9E3779B9) (runtime/ref_gpt.py:488-506) --------------------------
+__device__ __forceinline__ float kvm_philox_uniform(unsigned seed, unsigned ctr, unsigned row) {
+  unsigned c0 = row, c1 = ctr, c2 = 0, c3 = 0, k0 = seed, k1 = 0x9E3779B9u;
+  for (int i = 0; i < 10; ++i) {
+    const unsigned long long p0 = 0xD2511F53ull * c0, p1 = 0xCD9E8D57ull * c2;
+    const unsigned n0 = (unsigned)(p1 >> 32) ^ c1 ^ k0, n1 = (unsigned)p1, n2 = (unsigned)(p0 >> 32) ^ c3 ^ k1, n3 = (unsigned)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return (float)(c0 >> 8) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ unsigned kvm_order_key(float x) { const unsigned b = __float_as_uint(x); return (b >> 31) ? ~b : (b ^ 0x80000000u); }
+
+// temp <= 0: argmax. Otherwise inverse-CDF over softmax(logits/temp) restricted to the topk largest (ties kept), weights and
+// running sum in double in index order by one thread (the reference's order; rows are short-lived serving rows).
+__device__ void kvm_op_sample(const KvmCtx& c, const int32_t* a) {
+  KvmBuf lg, out, ctr;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, out) || !kvm_buf(c, a[2], KVM_M_I32, ctr, true)) return;
+  const int r0 = a[3], r1 = a[4], V = a[5], topk = a[7];
+  const float temp = kvm_bits_f32(a[6]);
+  if (r0 < 0 || r1 < r0 || V <= 0 || !kvm_mat_ok(c, lg, r1, V) || !kvm_flat_ok(c, out, r1)) { c.fail(KVM_OPE_RANGE, r0, r1); return; }
+  if (temp <= 0.0f) { kvm_argmax_rows(c, lg, out, r0, r1, V); return; }
+  const unsigned cv = ctr.p ? (unsigned)((const int*)ctr.p)[0] : 0u;
+  unsigned* sh = (unsigned*)c.smem;
+  for (int r = r0; r < r1; ++r) {
+    // threshold key = topk-th largest order key, by bitwise binary search on the count of keys >= candidate (block-parallel counts)
+    unsigned thr = 0;
+    if (topk > 0 && topk < V) {
+      for (int bit = 31; bit >= 0; --bit) {
+        const unsigned cand = thr | (1u << bit);
+        int cnt = 0;
+        for (int k = threadIdx.x; k < V; k += KVM_NT) cnt += kvm_order_key(kvm_ld(lg, (size_t)r * lg.ld + k)) >= cand;
+        const float tot = kvm_block_sum((float)cnt, (float*)sh);
+        if ((int)tot >= topk) thr = cand;
+      }
+    }
+    float mx = -INFINITY;
+    for (int k = threadIdx.x; k < V; k += KVM_NT) { const float v = kvm_ld(lg, (size_t)r * lg.ld + k); if (v == v) mx = fmaxf(mx, v); }
+    mx = kvm_block_max(mx, (float*)sh);
+    if (threadIdx.x == 0) {
+      double total = 0.0;
+      for (int k = 0; k < V; ++k) { const float v = kvm_ld(lg, (size_t)r * lg.ld + k); if (v == v && kvm_order_key(v) >= thr) total += exp((double)__fsub_rn(v, mx) / (double)temp); }
+      const double target = (double)kvm_philox_uniform((unsigned)a[8], cv, (unsigned)r) * total;
+      double run = 0.0; int pick = -1, last = -1;
+      for (int k = 0; k < V; ++k) {
+        const float v = kvm_ld(lg, (size_t)r * lg.ld + k);
+        if (v == v && kvm_order_key(v) >= thr) { run += exp((double)__fsub_rn(v, mx) / (double)temp); last = k; if (run > target) { pick = k; break; } }
+      }
+      ((int*)out.p)[r] = pick >= 0 ? pick : (last > 0 ? last : 0);
+    }
+    kvm_sync();
+  }
+}

@@ -1,0 +1,292 @@
+// The persistent executor kernel: one worker CTA per SM, each made of a scheduler warp and KVM_NT compute threads.
+//
+//   scheduler warp   claims ready-queue tickets, fetches the 16-word descriptor and the argument words of the next task into a
+//                    two-entry shared-memory slot ring (so the next task is staged while the current one computes), and, when
+//                    the compute group reports a task finished, publishes its version, decrements the dependency counters
+//                    of its successors (lanes in parallel) and enqueues or parks the ones that reach zero.
+//   compute group    waits for a full slot, dispatches the op body (SIMT ops use all 16 warps; tcgen05 GEMM / attention tasks
+//                    split them into TMA-producer, MMA-issuer and epilogue roles), fences, and hands the slot back.
+//
+// What it implements of the reference (include/mvm_exec.cuh, include/mvm_sched.cuh): mvm_worker / mvm_run_task / mvm_post_task
+// (:614-801), the successor release with continuation (:690-713), mvm_publish / park lists (:523-565), the ready queue
+// (mvm_sched.cuh:107-246, here a ticketed ring: one atomic per push and per pop) and first-error-wins failure (:260-266).
+// Admission differs by design: the whole batch is resident in HBM before launch (descriptor table, CSR successors, args),
+// dependency counters are armed by a tiny kernel, so no admitter CTA is needed.
+// Every wait has a time limit after which the kernel records KVM_ERR_TIMEOUT and all workers leave.
+#pragma once
+#include "kvm_dev.cuh"
+
+struct KvmDevState {
+  const KvmTaskDesc* tasks;
+  const int32_t* succ;
+  const int32_t* args;
+  int nt;
+  int* indeg;                 // remaining predecessors per task
+  int* exec_count;            // times executed (exactly-once witness)
+  int* ring;                  // ready ring: ring[ticket] = task + 1 once filled
+  unsigned* head;             // next pop ticket
+  unsigned* tail;             // next push ticket
+  int* done;                  // tasks finished
+  const KvmBuf* bufs;
+  int nbufs;
+  int* versions;
+  int nvars;
+  int* park_head;             // per variable: head of the parked list (-1 empty)
+  int* park_next;             // per task
+  KvmErrRec* err;
+  unsigned long long* t_start;  // trace (optional)
+  unsigned long long* t_end;
+  int* t_smid;
+  int trace;
+  unsigned long long timeout_ns;
+  int cfg_flags;
+  const void* tmaps;          // CUtensorMap table for tensor-core tasks
+  const int4* task_aux;       // per task: tensor-map indices / path selector
+};
+
+struct KvmSlot {
+  int task;                   // -1 = leave
+  int state;                  // 0 free, 1 full, 2 finished (awaiting release)
+  int pad[2];
+  int32_t desc[16];
+  int32_t args[KVM_MAX_ARGS];
+  int4 aux;
+};
+
+__device__ __forceinline__ int kvm_ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void kvm_st_release(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int kvm_ld_volatile_shared(const int* p) { return *(volatile const int*)p; }
+
+__device__ __forceinline__ void kvm_dev_fail(const KvmDevState& S, int code, int task, int a = 0, int b = 0) {
+  if (atomicCAS(&S.err->code, 0, code) == 0) { S.err->task = task; S.err->a = a; S.err->b = b; __threadfence_system(); }
+}
+
+__device__ __forceinline__ void kvm_push_ready(const KvmDevState& S, int task) {
+  unsigned t = atomicAdd(S.tail, 1u);
+  if (t >= (unsigned)S.nt) { kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, task, (int)t); return; }
+  kvm_st_release(&S.ring[t], task + 1);
+}
+
+// Push `task` onto the parked list of `var` (lock-free stack).
+__device__ __forceinline__ void kvm_park_push(const KvmDevState& S, int task, int var) {
+  int old = *(volatile int*)&S.park_head[var];
+  while (true) {
+    S.park_next[task] = old;
+    __threadfence();
+    const int prev = atomicCAS(&S.park_head[var], old, task);
+    if (prev == old) break;
+    old = prev;
+  }
+}
+// Re-examine the tasks parked on `var`: the list is detached atomically (so each waiter is in exactly one scanner's hands),
+// satisfied waiters are enqueued, the rest pushed back; if the version moved meanwhile, look again.
+__device__ void kvm_scan_parked(const KvmDevState& S, int var) {
+  for (int round = 0; round < 1024; ++round) {
+    const int v0 = kvm_ld_acquire(&S.versions[var]);
+    int list = atomicExch(&S.park_head[var], -1);
+    bool reparked = false;
+    while (list != -1) {
+      const int nxt = S.park_next[list];
+      if (v0 >= S.tasks[list].wait_ver) kvm_push_ready(S, list);
+      else { kvm_park_push(S, list, var); reparked = true; }
+      list = nxt;
+    }
+    __threadfence();
+    if (!reparked || kvm_ld_acquire(&S.versions[var]) == v0) return;
+  }
+}
+// Park, then look again: a publish that landed between the caller's check and the push is not lost (the Dekker pattern of
+// the reference's mvm_release_task, include/mvm_exec.cuh:544-556).
+__device__ __forceinline__ void kvm_park(const KvmDevState& S, int task, int var, int ver) {
+  kvm_park_push(S, task, var);
+  __threadfence();
+  if (kvm_ld_acquire(&S.versions[var]) >= ver) kvm_scan_parked(S, var);
+}
+// A task whose predecessors have all finished: enqueue it, or park it on its version wait.
+__device__ __forceinline__ void kvm_release_task(const KvmDevState& S, int task) {
+  const int wv = S.tasks[task].wait_var;
+  if (wv >= 0) {
+    if (wv >= S.nvars) { kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, wv); return; }
+    const int want = S.tasks[task].wait_ver;
+    if (kvm_ld_acquire(&S.versions[wv]) < want) { kvm_park(S, task, wv, want); return; }
+  }
+  kvm_push_ready(S, task);
+}
+
+// Arm kernel: dependency counters from the descriptors, roots into the ring, counters cleared.
+__global__ void kvm_arm_kernel(KvmDevState S) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < S.nt) {
+    S.indeg[i] = S.tasks[i].indegree;
+    S.exec_count[i] = 0;
+    S.ring[i] = 0;
+    S.park_next[i] = -1;
+  }
+  if (i < S.nvars) S.park_head[i] = -1;
+}
+__global__ void kvm_roots_kernel(KvmDevState S) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < S.nt && S.tasks[i].indegree == 0) kvm_release_task(S, i);
+}
+
+__device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* args, const int4& aux);
+
+#define KVM_EXEC_SMEM_HDR 1024     // slots + control words at the start of dynamic shared memory
+
+// The scheduler warp's share of finishing `task` (descriptor words in `desc`): publish, release successors.
+// Returns a continuation task (>= 0) when exactly the caller may run one directly, else -1.
+__device__ int kvm_finish_task(const KvmDevState& S, const int32_t* desc, int task, bool want_cont) {
+  const int lane = threadIdx.x & 31;
+  __threadfence();             // pairs with the compute group's fence before it flagged the slot finished
+  const int pv = desc[10];
+  if (pv >= 0) {
+    if (lane == 0) {
+      if (pv >= S.nvars) kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, pv);
+      else {
+        __threadfence();
+        const int ver = desc[11];
+        if (atomicCAS(&S.versions[pv], ver - 1, ver) != ver - 1) kvm_dev_fail(S, KVM_ERR_VERSION_GAP, task, pv, ver);
+        __threadfence();
+        kvm_scan_parked(S, pv);
+      }
+    }
+    __syncwarp();
+  }
+  const int so = desc[1], sc = desc[2];
+  int cont = -1;
+  for (int k0 = 0; k0 < sc; k0 += 32) {
+    const int k = k0 + lane;
+    int rdy = -1;
+    if (k < sc) {
+      const int s = S.succ[so + k];
+      const int old = atomicSub(&S.indeg[s], 1);
+      if (old == 1) rdy = s;
+      else if (old <= 0) kvm_dev_fail(S, KVM_ERR_BAD_TASK, s, old);
+    }
+    // The first ready successor without a version wait may become the continuation (no queue hop).
+    unsigned m = __ballot_sync(0xffffffffu, rdy >= 0 && want_cont && cont < 0 && S.tasks[rdy >= 0 ? rdy : 0].wait_var < 0);
+    int take = -1;
+    if (m) { take = __ffs(m) - 1; cont = __shfl_sync(0xffffffffu, rdy, take); }
+    if (rdy >= 0 && lane != take) kvm_release_task(S, rdy);
+  }
+  if (lane == 0) atomicAdd(S.done, 1);
+  return cont;
+}
+
+__global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S) {
+  extern __shared__ __align__(1024) unsigned char kvm_smem[];
+  KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
+  int* ctl = (int*)(kvm_smem + 2 * sizeof(KvmSlot));   // ctl[0] = TMEM base, ctl[1..] scratch
+  static_assert(2 * sizeof(KvmSlot) + 64 <= KVM_EXEC_SMEM_HDR, "header too small");
+  const int tid = threadIdx.x;
+  const bool is_sched = tid >= KVM_NT;
+  if (tid < 2) { slots[tid].state = 0; slots[tid].task = -1; }
+  unsigned dyn;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+  kvm_tc_init(ctl, kvm_smem);                          // TMEM allocation + mbarrier init (whole CTA)
+  __syncthreads();
+  const unsigned long long t_begin = kvm_globaltimer();
+
+  if (is_sched) {
+    const int lane = tid & 31;
+    int fill = 0;              // slot to fill next
+    int drain = 0;             // slot whose completion is due next (tasks finish in slot order)
+    int inflight = 0;          // slots handed to the compute group and not yet released
+    int ticket = -1;           // claimed, unfilled ticket
+    int cont = -1;             // continuation ready to be staged
+    bool stop = false;
+    unsigned polls = 0;
+    while (true) {
+      bool progressed = false;
+      // 1. a finished task?
+      if (inflight > 0 && kvm_ld_volatile_shared(&slots[drain].state) == 2) {
+        __syncwarp();
+        const int c2 = kvm_finish_task(S, slots[drain].desc, slots[drain].task, cont < 0 && ticket < 0 && !stop);
+        if (c2 >= 0) cont = c2;
+        __syncwarp();
+        if (lane == 0) slots[drain].state = 0;
+        __syncwarp();
+        drain ^= 1; --inflight; progressed = true;
+      }
+      // 2. stage the next task if a slot is free
+      if (!stop && inflight < 2) {
+        int task = -1;
+        if (cont >= 0) { task = cont; cont = -1; }
+        else {
+          if (ticket < 0) { int t = 0; if (lane == 0) t = (int)atomicAdd(S.head, 1u); ticket = __shfl_sync(0xffffffffu, t, 0); }
+          int v = 0;
+          if (lane == 0 && ticket < S.nt) v = kvm_ld_acquire(&S.ring[ticket]);
+          v = __shfl_sync(0xffffffffu, v, 0);
+          if (v > 0) { task = v - 1; ticket = -1; }
+        }
+        if (task >= 0) {
+          KvmSlot& sl = slots[fill];
+          if (lane < 16) sl.desc[lane] = ((const int32_t*)&S.tasks[task])[lane];
+          __syncwarp();
+          const int ao = sl.desc[6], aw = sl.desc[7];
+          if (lane < aw && lane < KVM_MAX_ARGS) sl.args[lane] = S.args[ao + lane];
+          if (lane == 31) { sl.task = task; sl.aux = S.task_aux ? S.task_aux[task] : make_int4(0, 0, 0, 0); }
+          __threadfence();       // gpu scope: the predecessors' data must be visible to this CTA's compute group
+          __syncwarp();
+          if (lane == 0) sl.state = 1;
+          fill ^= 1; ++inflight; progressed = true;
+        }
+      }
+      // 3. termination / failure / stall
+      if (!progressed) {
+        int d = 0, e = 0;
+        if (lane == 0) { d = kvm_ld_acquire(S.done); e = *(volatile int*)&S.err->code; }
+        d = __shfl_sync(0xffffffffu, d, 0); e = __shfl_sync(0xffffffffu, e, 0);
+        if (d >= S.nt || e != 0) stop = true;
+        if (stop && inflight == 0) break;
+        if ((++polls & 63u) == 0) {
+          if (kvm_globaltimer() - t_begin > S.timeout_ns) { if (lane == 0) kvm_dev_fail(S, KVM_ERR_TIMEOUT, ticket, d, inflight); stop = true; if (inflight == 0) break; }
+          __nanosleep(64);
+        }
+      } else polls = 0;
+    }
+    // tell the compute group to leave: it consumes slots in order, `fill` is the next one it looks at
+    if (lane == 0) { slots[fill].task = -1; __threadfence_block(); slots[fill].state = 1; }
+  } else {
+    KvmCtx c;
+    c.bufs = S.bufs; c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps;
+    c.smem = kvm_smem + KVM_EXEC_SMEM_HDR; c.smem_bytes = (int)dyn - KVM_EXEC_SMEM_HDR;
+    int cur = 0;
+    while (true) {
+      KvmSlot& sl = slots[cur];
+      if (tid == 0) {
+        unsigned polls = 0;
+        while (kvm_ld_volatile_shared(&sl.state) != 1) {
+          if ((++polls & 1023u) == 0 && kvm_globaltimer() - t_begin > 2 * S.timeout_ns) break;   // the scheduler always answers first
+        }
+      }
+      kvm_sync();
+      if (kvm_ld_volatile_shared(&sl.state) != 1) break;
+      const int task = sl.task;
+      if (task < 0) break;
+      c.task = task;
+      if (tid == 0) {
+        if (atomicAdd(&S.exec_count[task], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, task);
+        const int wv = sl.desc[8];
+        if (wv >= 0 && wv < S.nvars && kvm_ld_acquire(&S.versions[wv]) < sl.desc[9]) kvm_dev_fail(S, KVM_ERR_WAIT_VIOLATION, task, wv);
+        if (S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
+      }
+      const int op = sl.desc[0];
+      if (op != 0 && *(volatile int*)&S.err->code == 0) kvm_dispatch(c, op, sl.args, sl.aux);
+      __threadfence();
+      kvm_sync();
+      if (tid == 0) {
+        if (S.trace) S.t_end[task] = kvm_globaltimer();
+        __threadfence();
+        sl.state = 2;
+      }
+      cur ^= 1;
+    }
+  }
+  __syncthreads();
+  kvm_tc_fini(ctl);
+}
