@@ -98,6 +98,10 @@ int kvm_run(KvmExec* h, KvmResult* res);
 /* Re-arm the submitted tasks (dependency counters, queue, per-task records) so the same program runs again on the current
  * buffer contents and versions: the reference re-admits a one-step template per window (FRONTEND.md:201-213). */
 int kvm_rearm(KvmExec* h);
+/* Run the submitted program `steps` times back to back: re-arm + launch per step on the executor's stream with no host
+ * synchronisation in between; res->ms is the device time of the whole sequence (CUDA events on that stream) and the
+ * counters are those of the last step.  A device error in any step stops the following ones (they see the error word). */
+int kvm_run_steps(KvmExec* h, int32_t steps, KvmResult* res);
 /* Drop all submitted tasks (buffers and versions stay). */
 int kvm_clear_tasks(KvmExec* h);
 /* Per task of the last run: times executed and predecessor completions observed (the exactly-once witness and dependency
@@ -107,6 +111,8 @@ int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t 
 int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32_t* smid, int32_t n);
 /* Launch geometry of the persistent kernel: worker CTAs, threads per CTA, dynamic shared memory bytes. */
 int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes);
+/* Number of submitted tasks the host planned onto the tcgen05 / TMA path (the rest run SIMT bodies). */
+int kvm_tc_task_count(KvmExec* h);
 const char* kvm_last_error(KvmExec* h);
 const char* kvm_err_name(int32_t code);
 /* Registry lookups (include/kvm_ops.def): arity of op id, or -1; name or NULL. */

@@ -1,2 +1,61 @@
-// Host planning of the tensor-core tasks (placeholder).
-static int kvm_plan_tc(KvmExec* h, int first_task) { (void)h; (void)first_task; return 0; }
+// Host planning of the tensor-core tasks: for every matmul_mma_bf16 task whose operands TMA can address (bf16 storage,
+// 16-byte aligned base, row stride a multiple of 16 bytes, tile origin on an 8-element boundary) encode the two tensor maps
+// (deduplicated per GEMM) and mark the task for the tcgen05 path; everything else keeps the SIMT path.
+#include <map>
+#include <tuple>
+
+typedef CUresult (*KvmEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static KvmEncodeTiled kvm_encode_fn() {
+  static KvmEncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (KvmEncodeTiled)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 map over a row-major region: `inner` contiguous elements per row, `outer` rows, row stride ld elements.
+static int kvm_tmap_bf16(KvmExec* h, std::map<std::tuple<void*, int, int, int, int, int>, int>& cache, void* base, int inner, int outer, int ld, int box_inner, int box_outer) {
+  auto key = std::make_tuple(base, inner, outer, ld, box_inner, box_outer);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  KvmEncodeTiled enc = kvm_encode_fn();
+  if (!enc) return -1;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return -1;
+  h->tmaps.push_back(m);
+  const int idx = (int)h->tmaps.size() - 1;
+  cache[key] = idx;
+  return idx;
+}
+
+static int kvm_plan_tc(KvmExec* h, int first_task) {
+  if (h->cfg.flags & KVM_CFG_NO_TENSOR_CORES) return 0;
+  std::map<std::tuple<void*, int, int, int, int, int>, int> cache;
+  for (size_t i = first_task; i < h->tasks.size(); ++i) {
+    const KvmTaskDesc& d = h->tasks[i];
+    if (d.op_id != 122) continue;
+    const int32_t* a = h->args.data() + d.args_off;
+    const KvmBuf& A = h->bufs[a[0]];
+    const KvmBuf& B = h->bufs[a[1]];
+    const int m0 = a[6], n0 = a[7], M = a[8], N = a[9], K = a[10], fl = a[11];
+    const bool ta = fl & 1, tb = fl & 2;
+    if (A.dtype != KVM_BF16 || B.dtype != KVM_BF16 || (A.ld & 7) || (B.ld & 7) || ((uintptr_t)A.p & 15) || ((uintptr_t)B.p & 15) || (m0 & 7) || (n0 & 7) || M <= 0 || N <= 0 || K <= 0)
+      continue;
+    if ((ta ? (A.rows < K || A.cols < M) : (A.rows < M || A.cols < K)) || (tb ? (B.rows < N || B.cols < K) : (B.rows < K || B.cols < N))) continue;   // the op reports it
+    const int ia = ta ? kvm_tmap_bf16(h, cache, A.p, M, K, A.ld, 64, 64) : kvm_tmap_bf16(h, cache, A.p, K, M, A.ld, 64, 128);
+    const int ib = tb ? kvm_tmap_bf16(h, cache, B.p, K, N, B.ld, 64, 256) : kvm_tmap_bf16(h, cache, B.p, N, K, B.ld, 64, 64);
+    if (ia < 0 || ib < 0) continue;
+    h->aux[i] = make_int4(1, ia, ib, 0);
+  }
+  return 0;
+}

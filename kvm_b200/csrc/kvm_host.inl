@@ -310,7 +310,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
 }
 
 // Upload whatever changed since the last run, arm the counters and enqueue the roots.
-static int kvm_prepare(KvmExec* h) {
+static int kvm_prepare(KvmExec* h, bool keep_error = false) {
   cudaSetDevice(h->device);
   const size_t nt = h->tasks.size();
   if (nt == 0) { h->error = "nothing submitted"; return KVM_E_STATE; }
@@ -341,7 +341,7 @@ static int kvm_prepare(KvmExec* h) {
   }
   KvmDevState S = kvm_dev_state(h);
   KVM_CUDA(cudaMemsetAsync(h->d_ctl, 0, 64 * sizeof(int), h->stream));
-  KVM_CUDA(cudaMemsetAsync(h->d_err, 0, sizeof(KvmErrRec), h->stream));
+  if (!keep_error) KVM_CUDA(cudaMemsetAsync(h->d_err, 0, sizeof(KvmErrRec), h->stream));
   if (h->cfg.trace) { cudaMemsetAsync(h->d_tstart, 0, nt * 8, h->stream); cudaMemsetAsync(h->d_tend, 0, nt * 8, h->stream); }
   const int blocks = (int)((nt > (size_t)h->nvars ? nt : (size_t)h->nvars) + 255) / 256;
   kvm_arm_kernel<<<blocks, 256, 0, h->stream>>>(S);
@@ -407,6 +407,22 @@ extern "C" int kvm_run(KvmExec* h, KvmResult* res) {
   return kvm_finish(h, res);
 }
 
+extern "C" int kvm_run_steps(KvmExec* h, int32_t steps, KvmResult* res) {
+  if (!h || steps < 1) return KVM_E_ARG;
+  if (h->started) { h->error = "kvm_run_steps: a run is in flight"; return KVM_E_STATE; }
+  if (int r = kvm_prepare(h)) return r;
+  KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
+  for (int s = 0; s < steps; ++s) {
+    if (s) if (int r = kvm_prepare(h, true)) return r;
+    KvmDevState S = kvm_dev_state(h);
+    kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);
+    KVM_CUDA(cudaGetLastError());
+  }
+  KVM_CUDA(cudaEventRecord(h->ev1, h->stream));
+  h->started = true; h->armed = false;
+  return kvm_finish(h, res);
+}
+
 extern "C" int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t n) {
   if (!h || n < 0 || n > (int)h->tasks.size() || !h->d_exec) { if (h) h->error = "kvm_task_counts: bad argument or no run yet"; return KVM_E_ARG; }
   cudaSetDevice(h->device);
@@ -432,6 +448,13 @@ extern "C" int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, i
   if (threads) *threads = KVM_NT + 32;
   if (smem_bytes) *smem_bytes = h->smem_bytes;
   return 0;
+}
+
+extern "C" int kvm_tc_task_count(KvmExec* h) {
+  if (!h) return KVM_E_ARG;
+  int n = 0;
+  for (auto& a : h->aux) n += a.x != 0;
+  return n;
 }
 
 #include "kvm_gemm_host.inl"

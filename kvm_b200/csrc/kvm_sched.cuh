@@ -277,6 +277,8 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       }
       const int op = sl.desc[0];
       if (op != 0 && *(volatile int*)&S.err->code == 0) kvm_dispatch(c, op, sl.args, sl.aux);
+      // this task's generic-proxy writes (global results, shared scratch) ordered before any later TMA access to them
+      asm volatile("fence.proxy.async;" ::: "memory");
       __threadfence();
       kvm_sync();
       if (tid == 0) {

@@ -60,11 +60,13 @@ SYMBOLS = {
     'kvm_start': (C.c_int, [C.c_void_p]),
     'kvm_finish': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
     'kvm_run': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
+    'kvm_run_steps': (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(KvmResult)]),
     'kvm_rearm': (C.c_int, [C.c_void_p]),
     'kvm_clear_tasks': (C.c_int, [C.c_void_p]),
     'kvm_task_counts': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_trace': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_launch_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    'kvm_tc_task_count': (C.c_int, [C.c_void_p]),
     'kvm_last_error': (C.c_char_p, [C.c_void_p]),
     'kvm_err_name': (C.c_char_p, [C.c_int32]),
     'kvm_op_arity': (C.c_int, [C.c_int32]),
@@ -258,6 +260,13 @@ class Executor:
             raise KvmError(r, (self.L.kvm_last_error(self._h) or b'').decode())
         return res
 
+    def run_steps(self, steps, check=True) -> KvmResult:
+        res = KvmResult()
+        r = self.L.kvm_run_steps(self._h, steps, C.byref(res))
+        if check and r != 0:
+            raise KvmError(r, (self.L.kvm_last_error(self._h) or b'').decode())
+        return res
+
     def task_counts(self, n=None):
         n = n if n is not None else len(self.bundle.tasks)
         ex, ob = np.empty(n, np.int32), np.empty(n, np.int32)
@@ -269,6 +278,9 @@ class Executor:
         s, e, sm = np.empty(n, np.uint64), np.empty(n, np.uint64), np.empty(n, np.int32)
         self._check(self.L.kvm_trace(self._h, s.ctypes.data, e.ctypes.data, sm.ctypes.data, n))
         return s, e, sm
+
+    def tc_task_count(self) -> int:
+        return self.L.kvm_tc_task_count(self._h)
 
     def launch_info(self):
         w, t, s = C.c_int32(), C.c_int32(), C.c_int32()

@@ -52,6 +52,9 @@ class Graph:
         self.blobs: dict[str, bytes] = {}
         self.ops = abi.load_ops()
         self._pubs = {}
+        self._joins = {}
+        self._wver = {}
+        self.join_threshold = 24
 
     # ---- declarations
     def buffer(self, name, rows, cols, dtype='f32', init=None):
@@ -62,6 +65,7 @@ class Graph:
         self.buffers[name] = {'name': name, 'rows': int(rows), 'cols': int(cols), 'dtype': dtype,
                               'init': init or {'kind': 'fill', 'value': 0}}
         self._w[name], self._r[name] = _Records(), _Records()
+        self._wver[name] = 0
         return name
 
     def stream(self, name, values: np.ndarray, cols=1):
@@ -76,6 +80,18 @@ class Graph:
             init = {'kind': 'file', 'path': rel}
         return self.buffer(name, rows, cols, 'i32', init)
 
+    def data(self, name, values: np.ndarray, dtype='f32'):
+        """A buffer initialised from an array (2-D), carried as a `file` init: raw little-endian f32 / i32 / bf16 bits."""
+        values = np.atleast_2d(values)
+        rel = f'data/{name}.bin'
+        if dtype == 'bf16':
+            u = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32)
+            raw = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype('<u2').tobytes()
+        else:
+            raw = np.ascontiguousarray(values, dtype='<i4' if dtype == 'i32' else '<f4').tobytes()
+        self.blobs[rel] = raw
+        return self.buffer(name, values.shape[0], values.shape[1], dtype, {'kind': 'file', 'path': rel})
+
     def variable(self, name):
         if name not in self.variables:
             self.variables.append(name)
@@ -88,27 +104,51 @@ class Graph:
         return (e0 // c, -(-e1 // c))
 
     # ---- emission
-    def task(self, op, args, reads=(), writes=(), priority=0, name=None, publishes=None, after=()):
-        """reads / writes: iterables of (buffer, (r0, r1), (c0, c1)); a buffer name alone means the whole buffer."""
+    def task(self, op, args, reads=(), writes=(), priority=0, name=None, publishes=None, after=(), quiet_reads=()):
+        """reads / writes: iterables of (buffer, (r0, r1), (c0, c1)); a buffer name alone means the whole buffer.
+        quiet_reads are recorded for later writers (write-after-read) but add no edge now: the caller orders them through `after`
+        (a join task that already waits for their producers)."""
         spec = self.ops[op]
         tid = len(self.tasks)
         deps = set(after)
         norm = lambda acc: [(a, ALL, ALL) if isinstance(a, str) else (a[0], a[1], a[2] if len(a) > 2 else ALL) for a in acc if a is not None and a[0] is not None]
-        reads, writes = norm(reads), norm(writes)
+        reads, writes, quiet_reads = norm(reads), norm(writes), norm(quiet_reads)
         for buf, (r0, r1), (c0, c1) in reads:
             w = self._w[buf]
             if w.n:
-                deps.update(w.a[:w.n][w.overlapping(r0, r1, c0, c1), 4].tolist())
+                prod = w.a[:w.n][w.overlapping(r0, r1, c0, c1), 4]
+                if len(prod) > self.join_threshold:
+                    # many producers of one region, usually shared by many readers: a noop join waits for them once
+                    key = (buf, r0, r1, c0, c1, self._wver[buf])
+                    if key not in self._joins:
+                        self._joins[key] = len(self.tasks)
+                        self.tasks.append({'name': f'join{len(self._joins)}:{buf}', 'op': self.ops['noop'], 'args': {}, 'priority': int(priority),
+                                           'deadline_us': -1, 'pub': None, 'wait': None, 'gi': 0, 'publishes': None})
+                        self.preds.append(sorted(set(prod.tolist())))
+                        tid = len(self.tasks)
+                    deps.add(self._joins[key])
+                else:
+                    deps.update(prod.tolist())
         for buf, (r0, r1), (c0, c1) in writes:
-            for rec in (self._w[buf], self._r[buf]):
-                if rec.n:
-                    deps.update(rec.a[:rec.n][rec.overlapping(r0, r1, c0, c1), 4].tolist())
+            w, r = self._w[buf], self._r[buf]
+            ws = w.a[:w.n][w.overlapping(r0, r1, c0, c1)] if w.n else w.a[:0]
+            deps.update(ws[:, 4].tolist())
+            if r.n:
+                rs = r.a[:r.n][r.overlapping(r0, r1, c0, c1)]
+                if len(rs) and len(ws):
+                    # a reader R is already ordered before this write if some overlapping earlier writer W was emitted after R
+                    # and touched R's region (W then carries the edge R -> W, and W -> this task was just added)
+                    covered = ((ws[None, :, 4] > rs[:, None, 4]) & (ws[None, :, 0] < rs[:, None, 1]) & (ws[None, :, 1] > rs[:, None, 0]) &
+                               (ws[None, :, 2] < rs[:, None, 3]) & (ws[None, :, 3] > rs[:, None, 2])).any(axis=1)
+                    rs = rs[~covered]
+                deps.update(rs[:, 4].tolist())
         deps.discard(tid)
         for buf, (r0, r1), (c0, c1) in writes:
             self._w[buf].drop_covered(r0, r1, c0, c1)
             self._r[buf].drop_covered(r0, r1, c0, c1)
             self._w[buf].add(r0, r1, c0, c1, tid)
-        for buf, (r0, r1), (c0, c1) in reads:
+            self._wver[buf] += 1
+        for buf, (r0, r1), (c0, c1) in reads + quiet_reads:
             self._r[buf].add(r0, r1, c0, c1, tid)
         pub = None
         if publishes is not None:
