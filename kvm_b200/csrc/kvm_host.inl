@@ -30,7 +30,7 @@ struct KvmExec {
   size_t task_cap = 0;
   // control words
   int* d_ctl = nullptr;          // [0] head [1] tail [2] done
-  int* d_versions = nullptr; int* d_park_head = nullptr;
+  int* d_versions = nullptr; int* d_park_head = nullptr; int* d_ver_base = nullptr; int* d_ver_off = nullptr;
   KvmErrRec* d_err = nullptr;
   bool started = false, armed = false;
   KvmResult last{};
@@ -84,7 +84,7 @@ extern "C" int kvm_create(const KvmConfig* cfg, KvmExec** out) {
   if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
   cudaEventCreate(&h->ev0); cudaEventCreate(&h->ev1);
   if ((e = cudaMalloc(&h->d_ctl, 64 * sizeof(int))) != cudaSuccess) return fail("cudaMalloc", e);
-  cudaMalloc(&h->d_versions, h->nvars * sizeof(int)); cudaMalloc(&h->d_park_head, h->nvars * sizeof(int)); cudaMalloc(&h->d_err, sizeof(KvmErrRec));
+  cudaMalloc(&h->d_versions, h->nvars * sizeof(int)); cudaMalloc(&h->d_park_head, h->nvars * sizeof(int)); cudaMalloc(&h->d_ver_base, h->nvars * sizeof(int)); cudaMalloc(&h->d_ver_off, h->nvars * sizeof(int)); cudaMalloc(&h->d_err, sizeof(KvmErrRec));
   cudaMemset(h->d_versions, 0, h->nvars * sizeof(int)); cudaMemset(h->d_err, 0, sizeof(KvmErrRec)); cudaMemset(h->d_ctl, 0, 64 * sizeof(int));
   if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail("init", e);
   *out = h;
@@ -97,7 +97,7 @@ extern "C" void kvm_destroy(KvmExec* h) {
   cudaStreamSynchronize(h->stream);
   for (auto& o : h->owned) cudaFree(o.p);
   kvm_free_tasks(h);
-  for (void* p : {(void*)h->d_bufs, (void*)h->d_ctl, (void*)h->d_versions, (void*)h->d_park_head, (void*)h->d_err}) if (p) cudaFree(p);
+  for (void* p : {(void*)h->d_bufs, (void*)h->d_ctl, (void*)h->d_versions, (void*)h->d_park_head, (void*)h->d_ver_base, (void*)h->d_ver_off, (void*)h->d_err}) if (p) cudaFree(p);
   if (h->ev0) cudaEventDestroy(h->ev0);
   if (h->ev1) cudaEventDestroy(h->ev1);
   if (h->stream) cudaStreamDestroy(h->stream);
@@ -300,7 +300,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.indeg = h->d_indeg; S.exec_count = h->d_exec; S.ring = h->d_ring;
   S.head = (unsigned*)h->d_ctl; S.tail = (unsigned*)h->d_ctl + 1; S.done = h->d_ctl + 2;
   S.bufs = h->d_bufs; S.nbufs = (int)h->bufs.size();
-  S.versions = h->d_versions; S.nvars = h->nvars; S.park_head = h->d_park_head; S.park_next = h->d_park_next;
+  S.versions = h->d_versions; S.nvars = h->nvars; S.ver_base = h->d_ver_base; S.ver_off = h->d_ver_off; S.park_head = h->d_park_head; S.park_next = h->d_park_next;
   S.err = h->d_err;
   S.t_start = h->d_tstart; S.t_end = h->d_tend; S.t_smid = h->d_tsmid; S.trace = h->cfg.trace;
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
@@ -337,6 +337,7 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
     if (!h->tmaps.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_tmaps, h->tmaps.data(), h->tmaps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, h->stream));
+    KVM_CUDA(cudaMemcpyAsync(h->d_ver_base, h->d_versions, h->nvars * sizeof(int), cudaMemcpyDeviceToDevice, h->stream));   // the versions these tasks were compiled against
     h->tasks_dirty = false; h->task_cap = nt;
   }
   KvmDevState S = kvm_dev_state(h);

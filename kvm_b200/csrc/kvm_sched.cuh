@@ -31,6 +31,8 @@ struct KvmDevState {
   int nbufs;
   int* versions;
   int nvars;
+  const int* ver_base;        // versions when the submitted tasks were first armed (what they were compiled against)
+  int* ver_off;               // versions now minus ver_base at arm time: a re-run is the next window of the same template
   int* park_head;             // per variable: head of the parked list (-1 empty)
   int* park_next;             // per task
   KvmErrRec* err;
@@ -91,7 +93,7 @@ __device__ void kvm_scan_parked(const KvmDevState& S, int var) {
     bool reparked = false;
     while (list != -1) {
       const int nxt = S.park_next[list];
-      if (v0 >= S.tasks[list].wait_ver) kvm_push_ready(S, list);
+      if (v0 >= S.tasks[list].wait_ver + S.ver_off[var]) kvm_push_ready(S, list);
       else { kvm_park_push(S, list, var); reparked = true; }
       list = nxt;
     }
@@ -111,7 +113,7 @@ __device__ __forceinline__ void kvm_release_task(const KvmDevState& S, int task)
   const int wv = S.tasks[task].wait_var;
   if (wv >= 0) {
     if (wv >= S.nvars) { kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, wv); return; }
-    const int want = S.tasks[task].wait_ver;
+    const int want = S.tasks[task].wait_ver + S.ver_off[wv];
     if (kvm_ld_acquire(&S.versions[wv]) < want) { kvm_park(S, task, wv, want); return; }
   }
   kvm_push_ready(S, task);
@@ -126,7 +128,7 @@ __global__ void kvm_arm_kernel(KvmDevState S) {
     S.ring[i] = 0;
     S.park_next[i] = -1;
   }
-  if (i < S.nvars) S.park_head[i] = -1;
+  if (i < S.nvars) { S.park_head[i] = -1; S.ver_off[i] = S.versions[i] - S.ver_base[i]; }
 }
 __global__ void kvm_roots_kernel(KvmDevState S) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -148,7 +150,7 @@ __device__ int kvm_finish_task(const KvmDevState& S, const int32_t* desc, int ta
       if (pv >= S.nvars) kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, pv);
       else {
         __threadfence();
-        const int ver = desc[11];
+        const int ver = desc[11] + S.ver_off[pv];
         if (atomicCAS(&S.versions[pv], ver - 1, ver) != ver - 1) kvm_dev_fail(S, KVM_ERR_VERSION_GAP, task, pv, ver);
         __threadfence();
         kvm_scan_parked(S, pv);
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       if (tid == 0) {
         if (atomicAdd(&S.exec_count[task], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, task);
         const int wv = sl.desc[8];
-        if (wv >= 0 && wv < S.nvars && kvm_ld_acquire(&S.versions[wv]) < sl.desc[9]) kvm_dev_fail(S, KVM_ERR_WAIT_VIOLATION, task, wv);
+        if (wv >= 0 && wv < S.nvars && kvm_ld_acquire(&S.versions[wv]) < sl.desc[9] + S.ver_off[wv]) kvm_dev_fail(S, KVM_ERR_WAIT_VIOLATION, task, wv);
         if (S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
       }
       const int op = sl.desc[0];

@@ -48,10 +48,12 @@ def materialize(bundle: Bundle, b: dict) -> Buf:
 
 
 class VM:
-    def __init__(self, bundle: Bundle, exact_matmul: bool = True, buffers: list | None = None):
+    def __init__(self, bundle: Bundle, exact_matmul: bool = True, buffers: list | None = None, lazy: bool = False, zeros: bool = False):
         self.bundle = bundle
         self.exact = exact_matmul
-        self.bufs = buffers if buffers is not None else [materialize(bundle, b) for b in bundle.buffers]
+        self.zeros = zeros      # timing-only mode: every buffer starts as zeros instead of its init (values do not change op cost)
+        # lazy=True materialises a buffer at its first use (bounded timing samples touch a fraction of a large model)
+        self.bufs = buffers if buffers is not None else [None if lazy else materialize(bundle, b) for b in bundle.buffers]
         self.versions = {v['id']: v['base_version'] for v in bundle.metadata.get('variables', [])}
         self.ops = abi.ops_by_id()
         nt = len(bundle.tasks)
@@ -60,9 +62,11 @@ class VM:
         self.order = []
 
     def buffer(self, name: str) -> Buf:
-        for b, buf in zip(self.bundle.buffers, self.bufs):
+        for i, b in enumerate(self.bundle.buffers):
             if b['name'] == name:
-                return buf
+                if self.bufs[i] is None:
+                    self.bufs[i] = materialize(self.bundle, b)
+                return self.bufs[i]
         raise KeyError(name)
 
     def run_task(self, i: int):
@@ -72,6 +76,10 @@ class VM:
         bufs, scal = {}, {}
         for a, w in zip(op.args, words):
             if a.type == 'buf':
+                if w != abi.ABSENT_BUF and self.bufs[int(w)] is None:
+                    spec = self.bundle.buffers[int(w)]
+                    self.bufs[int(w)] = Buf(np.zeros((spec['rows'], spec['cols']), np.int32 if spec['dtype'] == I32 else np.float32), spec['dtype']) \
+                        if self.zeros else materialize(self.bundle, spec)
                 bufs[a.name] = None if w == abi.ABSENT_BUF else self.bufs[int(w)]
             elif a.type == 'i32':
                 scal[a.name] = int(w)
@@ -79,8 +87,10 @@ class VM:
                 scal[a.name] = float(np.array([w], '<i4').view('<f4')[0])
         ops_np.OPS[op.name](bufs, scal, exact_matmul=self.exact)
 
-    def run(self, subset=None):
-        """Run every task (or stop after `subset` tasks, for bounded timing samples). Returns self."""
+    def run(self, subset=None, time_limit=None):
+        """Run every task (or stop after `subset` tasks / `time_limit` seconds, for bounded timing samples). Returns self."""
+        import time
+        t_end = None if time_limit is None else time.perf_counter() + time_limit
         t = self.bundle.tasks
         nt = len(t)
         rem = t['indegree'].astype(np.int64).copy()
@@ -118,8 +128,8 @@ class VM:
                 self.observed[s] += 1
                 if rem[s] == 0:
                     heapq.heappush(ready, (-int(t['priority'][s]), s))
-            if subset is not None and done >= subset:
+            if (subset is not None and done >= subset) or (t_end is not None and time.perf_counter() >= t_end):
                 break
-        if subset is None and done != nt:
+        if subset is None and time_limit is None and done != nt:
             raise VMError(f'{done}/{nt} tasks ran')
         return self
