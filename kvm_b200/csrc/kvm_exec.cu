@@ -18,6 +18,7 @@
 #include "kvm_ops_attn.cuh"
 #include "kvm_ops_decode.cuh"
 #include "kvm_gemm_tc.cuh"
+#include "kvm_attn_tc.cuh"
 #include "kvm_sched.cuh"
 
 // ---------------------------------------------------------------------------------------------------------------- registry
@@ -75,10 +76,10 @@ __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* a, const in
     case 42: kvm_op_residual_add(c, a); break;
     case 43: kvm_op_rope_fwd(c, a); break;
     case 44: kvm_op_rope_bwd(c, a); break;
-    case 45: kvm_op_attn_fwd(c, a); break;
+    case 45: if ((aux.x & 255) == 2 && !(c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) kvm_attn_fwd_tc(c, a, aux); else kvm_op_attn_fwd(c, a); break;
     case 46: kvm_op_attn_bwd_delta(c, a); break;
-    case 47: kvm_op_attn_bwd_dq(c, a); break;
-    case 48: kvm_op_attn_bwd_dkv(c, a); break;
+    case 47: if ((aux.x & 255) == 2 && !(c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) kvm_attn_dq_tc(c, a, aux); else kvm_op_attn_bwd_dq(c, a); break;
+    case 48: if ((aux.x & 255) == 2 && !(c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) kvm_attn_dkv_tc(c, a, aux); else kvm_op_attn_bwd_dkv(c, a); break;
     case 49: kvm_op_kv_append(c, a); break;
     case 50: kvm_op_attn_decode(c, a); break;
     case 51: kvm_op_softmax_ce_fwd(c, a); break;

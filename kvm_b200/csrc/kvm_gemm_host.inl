@@ -43,6 +43,36 @@ static int kvm_plan_tc(KvmExec* h, int first_task) {
   std::map<std::tuple<void*, int, int, int, int, int>, int> cache;
   for (size_t i = first_task; i < h->tasks.size(); ++i) {
     const KvmTaskDesc& d = h->tasks[i];
+    if (d.op_id == 45 || d.op_id == 47 || d.op_id == 48) {
+      // tensor-core attention: bf16 q / k / v (/ dO), head dimension 64, whole 128-row blocks, TMA-addressable rows
+      const int32_t* a = h->args.data() + d.args_off;
+      const bool fwd = d.op_id == 45, dkv = d.op_id == 48;
+      const int nb = fwd ? 5 : dkv ? 8 : 7;                       // buffer argument count
+      const int b = a[nb], hh = a[nb + 1], r0 = a[nb + 2], T = a[nb + 3], H = a[nb + 4];
+      const int hd = dkv ? a[nb + 5] : a[nb + 6];
+      const KvmBuf& Q = h->bufs[a[0]]; const KvmBuf& K = h->bufs[a[1]]; const KvmBuf& V = h->bufs[a[2]];
+      const KvmBuf* DO = fwd ? nullptr : &h->bufs[a[3]];
+      if (hd != 64 || T <= 0 || (T & 127) || (r0 & 127) || r0 < 0 || r0 >= T || b < 0 || H <= 0 || (K.cols % 64)) continue;
+      const int Hkv = dkv ? K.cols / 64 : a[nb + 5];
+      if (Hkv <= 0 || H % Hkv || hh < 0 || hh >= (dkv ? Hkv : H)) continue;
+      const long long R = (long long)(b + 1) * T;
+      bool okb = true;
+      for (const KvmBuf* B : {&Q, &K, &V, DO}) if (B && (B->dtype != KVM_BF16 || (B->ld & 7) || ((uintptr_t)B->p & 15) || B->rows < R)) okb = false;
+      if (!okb || Q.cols < H * 64 || K.cols < Hkv * 64 || V.cols < Hkv * 64 || (DO && DO->cols < H * 64)) continue;
+      // outputs and the lse / delta vectors are checked here too: the tensor-core bodies assume a valid geometry
+      bool oko = true;
+      auto mat = [&](int idx, int cols) { const KvmBuf& B = h->bufs[idx]; if (B.dtype == KVM_I32 || B.rows < R || B.cols < cols) oko = false; };
+      auto vec = [&](int idx) { const KvmBuf& B = h->bufs[idx]; if (B.dtype != KVM_F32 || B.ld != B.cols || (long long)B.rows * B.cols < R * H) oko = false; };
+      if (fwd) { mat(a[3], H * 64); vec(a[4]); }
+      else if (!dkv) { vec(a[4]); vec(a[5]); mat(a[6], H * 64); }
+      else { vec(a[4]); vec(a[5]); mat(a[6], Hkv * 64); mat(a[7], Hkv * 64); }
+      if (!oko) continue;
+      const int tq = kvm_tmap_bf16(h, cache, Q.p, Q.cols, Q.rows, Q.ld, 64, 128), tk = kvm_tmap_bf16(h, cache, K.p, K.cols, K.rows, K.ld, 64, 128),
+                tv = kvm_tmap_bf16(h, cache, V.p, V.cols, V.rows, V.ld, 64, 128), tdo = DO ? kvm_tmap_bf16(h, cache, DO->p, DO->cols, DO->rows, DO->ld, 64, 128) : 0;
+      if (tq < 0 || tk < 0 || tv < 0 || tdo < 0) continue;
+      h->aux[i] = make_int4(2 | (tdo << 8), tq, tk, tv);
+      continue;
+    }
     if (d.op_id != 122) continue;
     const int32_t* a = h->args.data() + d.args_off;
     const KvmBuf& A = h->bufs[a[0]];

@@ -87,6 +87,7 @@ __device__ __forceinline__ uint32_t kvm_idesc_bf16(int M, int N, bool a_mn, bool
 }
 
 // Whole CTA, once at kernel start: TMEM allocation (all 512 columns: one CTA per SM) and mbarrier initialisation.
+__device__ __forceinline__ void kvm_att_init(int* ctl);
 __device__ __forceinline__ void kvm_tc_init(int* ctl, unsigned char* smem) {
   (void)smem;
   if (threadIdx.x < 32) {
@@ -96,6 +97,7 @@ __device__ __forceinline__ void kvm_tc_init(int* ctl, unsigned char* smem) {
   if (threadIdx.x == 32) {
     for (int i = 0; i < 2 * KVM_TC_STAGES + 1; ++i) kvm_mbar_init(kvm_bar_addr(ctl, i), 1);
     ctl[KVM_CTL_PROD_IT] = 0; ctl[KVM_CTL_MMA_IT] = 0; ctl[KVM_CTL_ACC_PH] = 0;
+    kvm_att_init(ctl);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }

@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
   KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
   int* ctl = (int*)(kvm_smem + 2 * sizeof(KvmSlot));   // ctl[0] = TMEM base, ctl[1..] scratch
-  static_assert(2 * sizeof(KvmSlot) + 64 <= KVM_EXEC_SMEM_HDR, "header too small");
+  static_assert(2 * sizeof(KvmSlot) + 96 * sizeof(int) <= KVM_EXEC_SMEM_HDR, "header too small");
   const int tid = threadIdx.x;
   const bool is_sched = tid >= KVM_NT;
   if (tid < 2) { slots[tid].state = 0; slots[tid].task = -1; }

@@ -135,12 +135,12 @@ class _Emit:
 
     # ---- op helpers (each emits the tile tasks of one logical op)
     def flat(self, op, bufs_r, bufs_w, n_elems, args, tag):
-        g, ch = self.g, self.c.flat_chunk
-        for e0 in range(0, n_elems, ch):
-            e1 = min(e0 + ch, n_elems)
-            rd = [(b, g.rows_of(b, e0, e1)) for b in bufs_r]
-            wr = [(b, g.rows_of(b, e0, e1)) for b in bufs_w]
-            g.task(op, {**args, 'e0': e0, 'e1': e1}, rd, wr, self.prio, f'{tag}.{e0 // ch}')
+        """Elementwise op over equally shaped buffers, chunked on row boundaries."""
+        g = self.g
+        for i, (e0, e1) in enumerate(g.flat_chunks(bufs_w[0], self.c.flat_chunk)):
+            rd = [(b, *g.region_of(b, e0, e1)) for b in bufs_r]
+            wr = [(b, *g.region_of(b, e0, e1)) for b in bufs_w]
+            g.task(op, {**args, 'e0': e0, 'e1': e1}, rd, wr, self.prio, f'{tag}.{i}')
 
     def linear(self, tag, a, w, out, M, N, K, flags=0, bias=None, res=None, pre=None, alpha=1.0):
         """out[M,N] (+)= alpha * op(a) op(w) (+bias) (gelu) (+res), tiled. Region reads follow the transposes."""
@@ -372,12 +372,12 @@ class _Emit:
         # ---------------- clip + AdamW, bracketed by the two publishes of `weights`
         chunks = []
         for name, (rows, cols, _) in self.params.items():
-            for e0 in range(0, rows * cols, c.flat_chunk):
-                chunks.append((name, e0, min(e0 + c.flat_chunk, rows * cols)))
+            for e0, e1 in g.flat_chunks('w.' + name, c.flat_chunk):
+                chunks.append((name, e0, e1))
         partial = B('gn_partial', 1, len(chunks))
         for slot, (name, e0, e1) in enumerate(chunks):
             g.task('gradnorm_partial', {'g': 'g.' + name, 'partial': partial, 'slot': slot, 'e0': e0, 'e1': e1},
-                   [('g.' + name, g.rows_of('g.' + name, e0, e1))], [(partial, (0, 1), (slot, slot + 1))], 2, f'{tag}gnorm.{slot}')
+                   [('g.' + name, *g.region_of('g.' + name, e0, e1))], [(partial, (0, 1), (slot, slot + 1))], 2, f'{tag}gnorm.{slot}')
         g.task('gradnorm_finish', {'partial': partial, 'nslots': len(chunks), 'out': 'clip_coef', 'max_norm': c.clip}, [partial], ['clip_coef'],
                2, tag + 'gnorm.finish')
         g.task('counter_inc', {'x': 'opt_step', 'i0': 0, 'i1': 1, 'delta': 1}, ['opt_step'], ['opt_step'], 2, tag + 'step_inc')
@@ -386,10 +386,10 @@ class _Emit:
         ups = []
         for name, e0, e1 in chunks:
             wd = c.wd if self.params[name][2] or name in ('wte', 'wpe') else 0.0
-            rr = g.rows_of('w.' + name, e0, e1)
+            rr = g.region_of('w.' + name, e0, e1)
             ups.append(g.task('adamw', {'p': 'w.' + name, 'g': 'g.' + name, 'm': 'm.' + name, 'v': 'v.' + name, 'gscale': 'clip_coef', 'step': 'opt_step',
                                         'e0': e0, 'e1': e1, 'lr': c.lr, 'b1': c.b1, 'b2': c.b2, 'eps': c.eps, 'wd': wd},
-                              [('g.' + name, rr), 'clip_coef', 'opt_step'], [('w.' + name, rr), ('m.' + name, rr), ('v.' + name, rr)], 1,
+                              [('g.' + name, *rr), 'clip_coef', 'opt_step'], [('w.' + name, *rr), ('m.' + name, *rr), ('v.' + name, *rr)], 1,
                               f'{tag}adamw.{name}.{e0}', after=[pre_id]))
         g.task('noop', {}, [], ['version_token'], 1, tag + 'barrier.post', publishes='weights', after=ups)
 

@@ -103,6 +103,30 @@ class Graph:
         c = self.buffers[buf]['cols']
         return (e0 // c, -(-e1 // c))
 
+    def region_of(self, buf, e0, e1):
+        """(rows, cols) region of the flat range [e0,e1): exact when it is whole rows or lies inside one row."""
+        c = self.buffers[buf]['cols']
+        if e0 // c == (e1 - 1) // c:
+            return (e0 // c, e0 // c + 1), (e0 % c, (e1 - 1) % c + 1)
+        return (e0 // c, -(-e1 // c)), ALL
+
+    def flat_chunks(self, buf, target):
+        """Flat ranges [e0,e1) of about `target` elements covering `buf`, cut on row boundaries (or inside single rows when a row
+        is longer than the target), so neighbouring chunks never share a region and get no false dependency."""
+        rows, c = self.buffers[buf]['rows'], self.buffers[buf]['cols']
+        out = []
+        if c >= 2 * target:
+            per = -(-c // -(-c // target))
+            per = -(-per // 8) * 8
+            for r in range(rows):
+                for c0 in range(0, c, per):
+                    out.append((r * c + c0, r * c + min(c0 + per, c)))
+        else:
+            per = max(1, target // c)
+            for r0 in range(0, rows, per):
+                out.append((r0 * c, min(r0 + per, rows) * c))
+        return out
+
     # ---- emission
     def task(self, op, args, reads=(), writes=(), priority=0, name=None, publishes=None, after=(), quiet_reads=()):
         """reads / writes: iterables of (buffer, (r0, r1), (c0, c1)); a buffer name alone means the whole buffer.
