@@ -1,0 +1,156 @@
+"""Host-side logic without a GPU: op registry, bundle compiler / validator, graph builder dataflow, the C ABI's symbols."""
+import json
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from kvm_b200 import abi
+from kvm_b200.bundle import Bundle, CompileError, compile_spec, load_bundle, validate
+from kvm_b200.workloads.gpt import build_training, preset, token_stream
+from kvm_b200.workloads.graph import Graph
+from oracle.vm_np import VM
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_registry_ids_and_arities():
+    ops = abi.load_ops()
+    assert ops['noop'].id == 0 and ops['matmul_tile'].id == 34 and ops['matmul_mma_bf16'].id == 122 and ops['gemv_bf16'].id == 134
+    assert ops['attn_decode_part'].arity == 18 and ops['adamw'].arity == 13 and ops['matmul_tile'].arity == 13
+    assert len({o.id for o in ops.values()}) == len(ops)
+    assert [a.optional for a in ops['embedding_fwd'].args][:4] == [False, False, True, False]
+    assert all(o.arity <= abi.MAX_ARGS for o in ops.values())
+
+
+def test_c_abi_exports_every_declared_symbol(kvm_lib):
+    from kvm_b200.executor import SYMBOLS, lib
+    header = (ROOT / 'include' / 'kvm_b200.h').read_text()
+    declared = set(re.findall(r'\b(kvm_[a-z_0-9]+)\s*\(', header))
+    assert declared == set(SYMBOLS), declared ^ set(SYMBOLS)
+    L = lib()
+    for name in declared:
+        assert hasattr(L, name), name
+    ops = abi.load_ops()
+    for o in ops.values():          # the library's registry is the same text
+        assert L.kvm_op_arity(o.id) == o.arity and L.kvm_op_name(o.id).decode() == o.name
+    assert L.kvm_op_arity(64) == -1 and L.kvm_err_name(7) == b'VERSION_GAP' and L.kvm_err_name(1005) == b'E_TOKEN'
+
+
+def test_executor_fails_loudly_without_gpu(kvm_lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip('a GPU is present')
+    from kvm_b200.executor import Executor, KvmError
+    with pytest.raises(KvmError):
+        Executor()
+
+
+def _spec():
+    return {'variables': ['weights'], 'buffers': [{'name': 'x', 'rows': 1, 'cols': 8, 'init': {'kind': 'values', 'values': list(range(8))}},
+                                                  {'name': 'y', 'rows': 1, 'cols': 8}],
+            'graphs': [{'name': 'g', 'tasks': [
+                {'id': 'a', 'op': 'scale', 'args': {'x': 'x', 'out': 'y', 'alpha': 2.0, 'n': 8}, 'publishes': 'weights'},
+                {'id': 'b', 'op': 'add', 'args': {'a': 'x', 'b': 'y', 'out': 'y', 'n': 8}, 'after': ['a'], 'priority': 3, 'reads': [{'var': 'weights', 'policy': 'at_least', 'version': 1}]},
+                {'id': 'c', 'op': 'noop', 'after': ['b'], 'publishes': 'weights'}]}]}
+
+
+def test_compile_spec_versions_and_roundtrip(tmp_path):
+    b = compile_spec(_spec())
+    assert validate(b) == ''
+    t = b.tasks
+    assert t['pub_ver'].tolist() == [1, 0, 2] and t['wait_var'].tolist() == [-1, 0, -1] and t['wait_ver'][1] == 1
+    assert t['indegree'].tolist() == [0, 1, 1] and b.metadata['initial_ready'] == [0] and b.metadata['final_versions'] == {'weights': 2}
+    b.write(tmp_path / 'bundle')
+    b2 = load_bundle(tmp_path / 'bundle')
+    assert np.array_equal(b2.tasks, b.tasks) and np.array_equal(b2.succ, b.succ) and np.array_equal(b2.args, b.args)
+    vm = VM(b2).run()
+    assert vm.buffer('y').a.reshape(-1).tolist() == [3.0 * i for i in range(8)] and vm.versions == {0: 2}
+    assert (vm.exec_count == 1).all() and np.array_equal(vm.observed, b.tasks['indegree'])
+
+
+@pytest.mark.parametrize('mutate, msg', [
+    (lambda s: s['graphs'][0]['tasks'][0].update(op='nope'), 'unknown op'),
+    (lambda s: s['graphs'][0]['tasks'][0]['args'].update(x='zz'), 'undeclared buffer'),
+    (lambda s: s['graphs'][0]['tasks'][1].update(after=['zz']), 'unknown task'),
+    (lambda s: s['graphs'][0]['tasks'][0].update(priority=40), 'priority'),
+    (lambda s: s['graphs'][0]['tasks'][1]['reads'][0].update(version=9), 'never be satisfied'),
+    (lambda s: s['graphs'][0]['tasks'][0]['args'].pop('out'), 'missing'),
+    (lambda s: s['buffers'].append({'name': 'x', 'rows': 1, 'cols': 1}), 'duplicate buffer'),
+])
+def test_compile_errors(mutate, msg):
+    s = _spec()
+    mutate(s)
+    with pytest.raises(CompileError, match=msg):
+        compile_spec(s)
+
+
+def test_validate_catches_malformed_bundles():
+    b = compile_spec(_spec())
+    def broken(f):
+        c = Bundle(b.tasks.copy(), b.succ.copy(), b.args.copy(), b.metadata)
+        f(c)
+        return validate(c)
+    assert 'bad op_id' in broken(lambda c: c.tasks['op_id'].__setitem__(0, 77))
+    assert 'takes' in broken(lambda c: c.tasks['args_words'].__setitem__(0, 3))
+    assert 'indegree' in broken(lambda c: c.tasks['indegree'].__setitem__(2, 0))
+    assert 'buffer index' in broken(lambda c: c.args.__setitem__(0, 9))
+    assert 'cycle' in broken(lambda c: (c.succ.__setitem__(1, 0), c.tasks['indegree'].__setitem__(0, 1), c.tasks['indegree'].__setitem__(2, 0)))
+    assert 'version variable' in broken(lambda c: c.tasks['pub_var'].__setitem__(0, 5))
+
+
+def test_graph_dataflow_orders_raw_war_waw():
+    g = Graph('t')
+    g.buffer('a', 4, 4), g.buffer('b', 4, 4)
+    w0 = g.task('fill', {'x': 'a', 'value': 1.0, 'n': 16}, [], ['a'])
+    r0 = g.task('copy', {'src': 'a', 'dst': 'b', 'n': 16}, [('a', (0, 2))], ['b'])
+    w1 = g.task('fill', {'x': 'a', 'value': 2.0, 'n': 8}, [], [('a', (0, 2))])          # WAR on r0, WAW on w0
+    r1 = g.task('copy', {'src': 'a', 'dst': 'b', 'n': 16}, [('a', (2, 4))], ['b'])       # RAW on w0 only (rows 2..4), WAW on r0
+    assert g.preds[r0] == [w0] and g.preds[w1] == [w0, r0] and g.preds[r1] == [w0, r0]
+    assert validate(g.to_bundle()) == ''
+
+
+def test_training_graph_is_order_independent():
+    """Dataflow completeness: any topological order of the emitted graph gives bit-identical state (the reference checks its
+    frontend the same way, frontend/mvmfe/refvm.py:1-6)."""
+    b = build_training(preset('gpt_micro'), 2).to_bundle()
+    base = VM(b).run()
+    rng = np.random.default_rng(3)
+    t = b.tasks
+    for trial in range(2):
+        vm = VM(b)
+        rem = t['indegree'].astype(np.int64).copy()
+        ready = list(np.flatnonzero(rem == 0))
+        while ready:
+            i = int(ready.pop(int(rng.integers(len(ready)))))
+            vm.run_task(i)
+            for s in b.succ[t['succ_off'][i]:t['succ_off'][i] + t['succ_cnt'][i]]:
+                rem[s] -= 1
+                if rem[s] == 0:
+                    ready.append(int(s))
+        for x, y in zip(vm.bufs, base.bufs):
+            assert np.array_equal(x.a.view(np.uint32), y.a.view(np.uint32))
+
+
+def test_token_stream_data_parallel_split():
+    cfg = preset('gpt_micro')
+    ids_all, tgt_all = token_stream(cfg, 4, 0, 1)
+    N = cfg.tokens
+    for r in range(2):
+        ids, tgt = token_stream(cfg, 2, r, 2)
+        for s in range(2):        # rank r takes microbatch r of each group of 2
+            assert np.array_equal(ids[s * N:(s + 1) * N], ids_all[(2 * s + r) * N:(2 * s + r + 1) * N])
+    assert ((ids_all >= 0) & (ids_all < cfg.vocab)).all()
+    assert np.array_equal(ids_all.reshape(-1, cfg.seq)[:, 1:], tgt_all.reshape(-1, cfg.seq)[:, :-1])
+
+
+def test_flat_chunks_never_overlap():
+    g = Graph('t')
+    g.buffer('w', 768, 50304), g.buffer('v', 50304, 768), g.buffer('s', 1, 100000)
+    for buf in ('w', 'v', 's'):
+        ch = g.flat_chunks(buf, 262144)
+        assert ch[0][0] == 0 and ch[-1][1] == g.buffers[buf]['rows'] * g.buffers[buf]['cols'] and all(a[1] == b[0] for a, b in zip(ch, ch[1:]))
+        regs = [g.region_of(buf, *c) for c in ch]
+        for (r0, c0), (r1, c1) in zip(regs, regs[1:]):
+            assert r0[1] <= r1[0] or (r0 == r1 and c0[1] <= c1[0])
