@@ -158,10 +158,38 @@ __device__ void kvm_norm_bwd_dx(const KvmCtx& c, int xi, int dyi, int gi, int mi
       !kvm_flat_ok(c, mean, r1) || !kvm_flat_ok(c, rstd, r1)) { c.fail(KVM_OPE_RANGE, r0, r1); return; }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* gp = (const float*)g.p;
+  const bool vec = (d & 7) == 0 && d <= 1024 && (x.ld & 7) == 0 && (dy.ld & 7) == 0 && (dx.ld & 7) == 0 && kvm_vec_ok(x) && kvm_vec_ok(dy) && kvm_vec_ok(dx) && kvm_vec_ok(g);
   for (int r = r0 + warp; r < r1; r += KVM_NWARPS) {
     const float mu = RMS ? 0.0f : ((const float*)mean.p)[r], rs = ((const float*)rstd.p)[r];
     const size_t xo = (size_t)r * x.ld, yo = (size_t)r * dy.ld, oo = (size_t)r * dx.ld;
     float s1 = 0.0f, s2 = 0.0f;
+    if (vec) {      // the row stays in registers between the two passes: up to four 8-element vectors of x and dy per lane
+      float xv[4][8], gv[4][8];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int k = lane * 8 + t * 256;
+        if (k < d) {
+          float yv[8], gm[8];
+          kvm_ld8(x, xo + k, xv[t]); kvm_ld8(dy, yo + k, yv); kvm_ld8(g, k, gm);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { gv[t][j] = yv[j] * gm[j]; xv[t][j] = (xv[t][j] - mu) * rs; s1 += gv[t][j]; s2 += gv[t][j] * xv[t][j]; }
+        }
+      }
+      s1 = RMS ? 0.0f : kvm_warp_sum(s1) / d;
+      s2 = kvm_warp_sum(s2) / d;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int k = lane * 8 + t * 256;
+        if (k < d) {
+          float o[8];
+          if (acc) kvm_ld8(dx, oo + k, o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float v = rs * (gv[t][j] - s1 - xv[t][j] * s2); o[j] = acc ? __fadd_rn(o[j], v) : v; }
+          kvm_st8(dx, oo + k, o);
+        }
+      }
+      continue;
+    }
     for (int k = lane; k < d; k += 32) {
       float gs = kvm_ld(dy, yo + k) * gp[k], xh = (kvm_ld(x, xo + k) - mu) * rs;
       s1 += gs; s2 += gs * xh;
