@@ -114,6 +114,17 @@ int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* sme
 /* Number of submitted tasks the host planned onto the tcgen05 / TMA path (the rest run SIMT bodies). */
 int kvm_tc_task_count(KvmExec* h);
 const char* kvm_last_error(KvmExec* h);
+/* Read n elements of device memory `dev_src` (storage type dtype: KVM_F32 / KVM_I32 / KVM_BF16) back as float32 WITHOUT allocating
+ * anything: no counterpart in the reference (its read_buffer, like kvm_read_buffer here, may allocate).  For callers that must not
+ * call cudaMalloc: a decode loop reading logits / tokens every step beside other streams (cudaMalloc and cudaFree synchronise the
+ * device), or code that runs while a stream is being captured.  The widening uses a fixed scratch array inside the library,
+ * KVM_NOALLOC_MAX_ELEMS floats (4 MiB) per GPU; larger n is refused with KVM_E_ARG and a message from kvm_noalloc_last_error().
+ * The first call on a device looks the array's address up (do it before any stream capture).  All calls on a GPU share the
+ * array: calls whose device work overlaps race, so serialise them.  `stream` is a cudaStream_t (NULL = default stream); the
+ * call returns after the copy has completed. */
+#define KVM_NOALLOC_MAX_ELEMS (1u << 20)
+int kvm_read_f32_noalloc(int32_t device, const void* dev_src, int32_t dtype, size_t n, float* host_out, void* stream);
+const char* kvm_noalloc_last_error(void);
 const char* kvm_err_name(int32_t code);
 /* Registry lookups (include/kvm_ops.def): arity of op id, or -1; name or NULL. */
 int kvm_op_arity(int32_t op_id);

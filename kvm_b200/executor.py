@@ -68,6 +68,8 @@ SYMBOLS = {
     'kvm_launch_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     'kvm_tc_task_count': (C.c_int, [C.c_void_p]),
     'kvm_last_error': (C.c_char_p, [C.c_void_p]),
+    'kvm_read_f32_noalloc': (C.c_int, [C.c_int32, C.c_void_p, C.c_int32, C.c_size_t, C.POINTER(C.c_float), C.c_void_p]),
+    'kvm_noalloc_last_error': (C.c_char_p, []),
     'kvm_err_name': (C.c_char_p, [C.c_int32]),
     'kvm_op_arity': (C.c_int, [C.c_int32]),
     'kvm_op_name': (C.c_char_p, [C.c_int32]),

@@ -1,0 +1,43 @@
+"""The allocation-free read-back (kvm_read_f32_noalloc) against the ordinary one (kvm_read_buffer), through the C ABI.
+
+The ordinary entry point widens bf16 / i32 storage in a temporary it cudaMallocs; the allocation-free one uses a fixed scratch
+array inside the library, for callers that must not allocate (a per-step decode read-back beside other streams, code under
+stream capture).  Two calls in a row share that array, so the second one is smaller and holds different data: stale contents
+of the first call would show.  This file sorts last on purpose, so a failure here cannot hide another test's result.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _noalloc(ex, buf, n):
+    m = ex.meta[ex.index(buf)]
+    out = np.full(n, np.nan, np.float32)
+    r = ex.L.kvm_read_f32_noalloc(0, ex.buffer_ptr(buf), m['dtype'], n, out.ctypes.data_as(C.POINTER(C.c_float)), None)
+    assert r == 0, ex.L.kvm_noalloc_last_error().decode()
+    return out
+
+
+def test_noalloc_read_matches_read_buffer_twice(kvm_lib):
+    from kvm_b200.executor import Executor
+    rng = np.random.default_rng(5)
+    with Executor() as ex:
+        a = rng.standard_normal((300, 1000)).astype(np.float32)
+        b = rng.integers(-1000, 1000, (7, 333)).astype(np.int32)
+        c = rng.standard_normal((5, 64)).astype(np.float32)
+        ex.add_buffer(300, 1000, 2, a, name='a')      # bf16 storage
+        ex.add_buffer(7, 333, 1, b, name='b')         # i32
+        ex.add_buffer(5, 64, 0, c, name='c')          # f32
+        first = _noalloc(ex, 'a', 300000)
+        second = _noalloc(ex, 'b', 7 * 333)           # right after, smaller, other data: the scratch still holds `a`
+        third = _noalloc(ex, 'c', 320)
+        assert np.array_equal(first, ex.read_buffer('a').reshape(-1))      # exact: widening bf16 / int32 to float32 loses nothing
+        assert np.array_equal(second, ex.read_buffer('b').reshape(-1).astype(np.float32))
+        assert np.array_equal(third, ex.read_buffer('c').reshape(-1))
+        # beyond the fixed scratch: refused with a message, nothing copied
+        big = np.zeros(4, np.float32)
+        r = ex.L.kvm_read_f32_noalloc(0, ex.buffer_ptr('a'), 2, (1 << 20) + 1, big.ctypes.data_as(C.POINTER(C.c_float)), None)
+        assert r == -1 and b'exceed' in ex.L.kvm_noalloc_last_error()
