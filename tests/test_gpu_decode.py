@@ -1,0 +1,103 @@
+"""GPU parity of the decode (serving) ops against the CPU oracle: bf16 GEMV with its prologues, KV append, one-row attention
+(whole and split-context with fused RoPE + append), RMSNorm, SwiGLU, RoPE, argmax and sampling."""
+import numpy as np
+import pytest
+
+from kvm_b200.workloads.graph import Graph
+from tests.parity import compare, run_both
+
+pytestmark = pytest.mark.gpu
+rng = np.random.default_rng(11)
+f = lambda *s: rng.standard_normal(s).astype(np.float32)
+
+
+@pytest.mark.parametrize('pro', [0, 1, 2])
+@pytest.mark.parametrize('K,N', [(256, 100), (4096, 520), (12288, 64)])
+def test_gemv_bf16(kvm_lib, pro, K, N):
+    g = Graph('gemv')
+    g.data('x', f(1, K), 'f32' if pro != 2 else 'bf16'), g.data('x2', f(1, K)), g.data('gamma', f(1, K)), g.data('w', f(N, K) * 0.05, 'bf16')
+    g.data('res', f(1, N)), g.buffer('out', 1, N, 'bf16' if pro == 1 else 'f32')
+    for n0 in range(0, N, 48):
+        g.task('gemv_bf16', {'x': 'x', 'x2': 'x2' if pro == 2 else None, 'gamma': 'gamma' if pro == 1 else None, 'w': 'w', 'out': 'out', 'res': 'res' if pro else None,
+                             'n0': n0, 'n1': min(n0 + 48, N), 'K': K, 'pro': pro, 'eps': 1e-6})
+    ex, vm, res = run_both(g.to_bundle())
+    compare(ex, vm, 4e-3 if pro == 1 else 2e-5)
+    ex.close()
+
+
+def _cache(B, Hkv, Tmax, hd, dt):
+    return f(B * Hkv * Tmax, hd), f(B * Hkv * Tmax, hd)
+
+
+@pytest.mark.parametrize('hd,H,Hkv,dt', [(128, 8, 2, 'bf16'), (64, 4, 4, 'f32'), (32, 8, 1, 'f32')])
+def test_decode_attention_whole_and_split(kvm_lib, hd, H, Hkv, dt):
+    B, Tmax, S = 2, 300, 4
+    lens = np.array([[257], [5]], np.int32)
+    kc, vc = _cache(B, Hkv, Tmax, hd, dt)
+    g = Graph('dec')
+    g.data('q', f(B, H * hd), dt), g.data('kc', kc, dt), g.data('vc', vc, dt), g.data('lens', lens, 'i32')
+    g.data('knew', f(B, Hkv * hd)), g.data('vnew', f(B, Hkv * hd))
+    g.buffer('o1', B, H * hd, dt), g.buffer('o2', B, H * hd, dt), g.buffer('part', B * S * H, hd + 2)
+    sc = hd ** -0.5
+    for b in range(B):
+        for h in range(H):
+            g.task('attn_decode', {'q': 'q', 'kc': 'kc', 'vc': 'vc', 'lens': 'lens', 'o': 'o1', 'b': b, 'h': h, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': Tmax, 'scale': sc},
+                   ['q', 'kc', 'vc', 'lens'], [('o1', (b, b + 1), (h * hd, (h + 1) * hd))])
+    parts = []
+    for b in range(B):
+        for kvh in range(Hkv):
+            for s in range(S):
+                parts.append(g.task('attn_decode_part', {'q': 'q', 'kc': 'kc', 'vc': 'vc', 'lens': 'lens', 'part': 'part', 'knew': None, 'vnew': None, 'b': b, 'kvh': kvh, 's': s, 'S': S,
+                                                         'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': Tmax, 'scale': sc, 'theta': 1e6, 'flags': 0}, ['q', 'kc', 'vc', 'lens'], []))
+        g.task('attn_decode_merge', {'part': 'part', 'o': 'o2', 'b': b, 'h0': 0, 'h1': H, 'S': S, 'H': H, 'hd': hd}, [], [('o2', (b, b + 1))], after=parts)
+    ex, vm, res = run_both(g.to_bundle())
+    tol = 6e-3 if dt == 'bf16' else 2e-5
+    compare(ex, vm, tol)
+    assert np.abs(ex.read_buffer('o1') - ex.read_buffer('o2')).max() <= (2e-2 if dt == 'bf16' else 1e-5)     # split + merge equals the whole
+    ex.close()
+
+
+@pytest.mark.parametrize('flags', [1, 3])
+def test_decode_part_fused_rope_append(kvm_lib, flags):
+    B, H, Hkv, hd, Tmax, S = 2, 8, 2, 128, 200, 3
+    lens = np.array([[100], [0]], np.int32)
+    kc, vc = _cache(B, Hkv, Tmax, hd, 'bf16')
+    g = Graph('dec')
+    g.data('q', f(B, H * hd)), g.data('kc', kc, 'bf16'), g.data('vc', vc, 'bf16'), g.data('lens', lens, 'i32'), g.data('knew', f(B, Hkv * hd)), g.data('vnew', f(B, Hkv * hd))
+    g.buffer('part', B * S * H, hd + 2), g.buffer('o', B, H * hd, 'bf16')
+    for b in range(B):
+        ps = []
+        for kvh in range(Hkv):
+            for s in range(S):
+                base = (b * Hkv + kvh) * Tmax
+                ps.append(g.task('attn_decode_part', {'q': 'q', 'kc': 'kc', 'vc': 'vc', 'lens': 'lens', 'part': 'part', 'knew': 'knew', 'vnew': 'vnew', 'b': b, 'kvh': kvh, 's': s,
+                                                      'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': Tmax, 'scale': hd ** -0.5, 'theta': 1e6, 'flags': flags},
+                                 ['q', 'lens', 'knew', 'vnew'], [('kc', (base, base + Tmax)), ('vc', (base, base + Tmax))]))
+        g.task('attn_decode_merge', {'part': 'part', 'o': 'o', 'b': b, 'h0': 0, 'h1': H, 'S': S, 'H': H, 'hd': hd}, [], [('o', (b, b + 1))], after=ps)
+    ex, vm, res = run_both(g.to_bundle())
+    compare(ex, vm, 6e-3)
+    ex.close()
+
+
+def test_kv_append_rmsnorm_silu_rope_argmax_sample(kvm_lib):
+    B, Hkv, hd, Tmax, V, d = 3, 2, 64, 50, 1000, 256
+    g = Graph('misc')
+    g.data('knew', f(B * 2, Hkv * hd)), g.data('vnew', f(B * 2, Hkv * hd)), g.data('lens', np.array([[3], [0], [48]], np.int32), 'i32')
+    g.buffer('kc', B * Hkv * Tmax, hd, 'bf16'), g.buffer('vc', B * Hkv * Tmax, hd)
+    g.task('kv_append', {'knew': 'knew', 'vnew': 'vnew', 'kc': 'kc', 'vc': 'vc', 'lens': 'lens', 'b0': 0, 'b1': B, 'n_new': 2, 'Hkv': Hkv, 'hd': hd, 'Tmax': Tmax})
+    g.data('x', f(8, d)), g.data('gm', f(1, d)), g.buffer('xn', 8, d, 'bf16'), g.buffer('rs', 8, 1)
+    g.task('rmsnorm_fwd', {'x': 'x', 'gamma': 'gm', 'out': 'xn', 'rstd': 'rs', 'r0': 0, 'r1': 8, 'd': d, 'eps': 1e-6})
+    g.data('gate', f(8, d), 'bf16'), g.data('up', f(8, d)), g.buffer('act', 8, d)
+    g.task('silu_mul_fwd', {'gate': 'gate', 'up': 'up', 'out': 'act', 'e0': 0, 'e1': 8 * d})
+    g.data('pos', np.array([[4090]], np.int32), 'i32'), g.buffer('xr', 8, d)
+    g.task('rope_fwd', {'x': 'x', 'out': 'xr', 'pos': 'pos', 'r0': 0, 'r1': 8, 'T': 1, 'H': 2, 'hd': 128, 'theta': 1e6})
+    logits = f(6, V) * 3
+    logits[2, 10] = logits[2, 500] = 50.0       # tie: lowest index wins
+    g.data('logits', logits), g.data('lb', logits, 'bf16'), g.buffer('tok', 6, 1, 'i32'), g.buffer('tokb', 6, 1, 'i32'), g.buffer('smp', 6, 1, 'i32'), g.data('ctr', np.array([[3]], np.int32), 'i32')
+    g.task('argmax', {'logits': 'logits', 'out': 'tok', 'r0': 0, 'r1': 6, 'V': V})
+    g.task('argmax', {'logits': 'lb', 'out': 'tokb', 'r0': 0, 'r1': 6, 'V': V})
+    g.task('sample', {'logits': 'logits', 'out': 'smp', 'ctr': 'ctr', 'r0': 0, 'r1': 6, 'V': V, 'temp': 0.9, 'topk': 40, 'seed': 77})
+    ex, vm, res = run_both(g.to_bundle())
+    compare(ex, vm, 4e-3, tols={'xr': 1e-5, 'act': 1e-5, 'vc': 0.0, 'rs': 1e-6})
+    assert ex.read_buffer('tok')[2, 0] == 10
+    ex.close()
