@@ -264,6 +264,12 @@ def run_ours(args, rank, world, local_rank):
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': None,
                          'peak_source': f'{pk_kind} bf16_tflops_sustained', 'flops_per_launch': gemm_fl + attn_fl},
         }
+        if args.decode_tokens > 0 and world == 1:
+            ex.close()
+            try:
+                line['decode'] = run_decode(args, local_rank)
+            except Exception as e:      # the training line stands on its own
+                line['decode'] = {'error': str(e)[:300]}
         if cpu:
             line['cpu_baseline'] = {'value': cpu['steps_per_s'], 'unit': 'steps/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
                                     'sample': f"{cpu['tasks']} of {cpu['of_tasks']} tasks of one step, a few of each of its {cpu['kinds']} op kinds, {cpu['seconds']:.1f} s on the numpy oracle; step time = sum over kinds of count x mean task time"}
@@ -273,6 +279,121 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_dp(args, rank, world, local_rank):
+    """N > 1: data-parallel training. Per step and rank: backward launch -> one NCCL all-reduce (mean) over the gradient arena ->
+    optimizer launch. Weak scaling: every rank keeps the micro-batch of 8 x 1024 tokens."""
+    import torch
+    import torch.distributed as dist
+    from kvm_b200 import build
+    from kvm_b200.dp import DataParallelStep, grad_arena_layout
+    from kvm_b200.workloads.gpt import build_training, preset
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local_rank))
+    torch.cuda.set_device(local_rank)
+    if rank == 0:
+        build.build()
+    dist.barrier()
+    cfg = preset(args.model)
+    total = args.warmup + args.steps
+    g = build_training(cfg, 1, rank=rank, world=world, stream_steps=total + 1)
+    bundles = g.to_bundles_split(g.split_at)
+    _, n_arena = grad_arena_layout(bundles[0])
+    arena = torch.zeros(n_arena, dtype=torch.float32, device='cuda')
+    dp = DataParallelStep(cfg, rank, world, local_rank, arena.data_ptr(), total + 1, bundles=bundles)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    comm_ms = []
+
+    def all_reduce_mean():
+        ev0.record()
+        dist.all_reduce(arena, op=dist.ReduceOp.AVG)
+        ev1.record()
+        torch.cuda.synchronize()
+        comm_ms.append(ev0.elapsed_time(ev1))
+
+    for _ in range(args.warmup):
+        dp.step(all_reduce_mean)
+    dist.barrier(); torch.cuda.synchronize()
+    comm_ms.clear()
+    dev_ms, t0 = 0.0, time.perf_counter()
+    with ClockSampler(local_rank) as clk:
+        for _ in range(args.steps):
+            r1, r2 = dp.step(all_reduce_mean)
+            dev_ms += r1.ms + r2.ms
+        dist.barrier(); torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    dev_ms += sum(comm_ms)
+    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device='cuda')
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_total, wall_total = float(t[0]), float(t[1])
+    loss = float(dp.bwd.read_buffer('loss.0')[0, 0])
+    losses = torch.tensor([loss], dtype=torch.float64, device='cuda')
+    w0 = torch.tensor([float(np.abs(dp.bwd.read_buffer('w.lnf.g')).sum())], dtype=torch.float64, device='cuda')
+    wmax, wmin = w0.clone(), w0.clone()
+    dist.all_reduce(wmax, op=dist.ReduceOp.MAX); dist.all_reduce(wmin, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        gemm_fl, attn_fl = algorithmic_flops(cfg)
+        pk, pk_kind = peaks()
+        ms_step = dev_total / args.steps
+        value = world * args.steps / (wall_total / 1e3)          # host wall clock between barriers: includes launch gaps and the collective
+        achieved = (gemm_fl + attn_fl) / (ms_step / 1e3) / 1e12
+        peak = pk.get('bf16_tflops_sustained', PEAK_FALLBACK['bf16_tflops_sustained'])
+        print(json.dumps({
+            'metric': 'gpt162m_train_steps_per_s', 'value': value, 'unit': 'steps/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': wall_total / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+            'config': {'workload': f'{args.model} training step, micro-batch {cfg.batch}x{cfg.seq} per GPU, bf16 storage + f32 masters, AdamW; data parallel: backward launch, '
+                                   f'NCCL all-reduce (mean) of {n_arena * 4 / 1e6:.0f} MB of f32 gradients, optimizer launch',
+                       'tokens_per_step_per_gpu': cfg.tokens, 'parallelism': f'dp{world}', 'l2': 'per-step working set (> 6 GB) exceeds the 126 MB L2',
+                       'device_ms_per_step': ms_step, 'allreduce_ms_per_step': float(np.mean(comm_ms)), 'loss_last_step_rank0': loss,
+                       'replicas_equal': bool(float(wmax) == float(wmin))},
+            'e2e': {'value': value, 'unit': 'steps/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0, 'note': 'multi-GPU arm keeps tokens resident; the 1-GPU line carries the host-copy arm'},
+            'gpu_launches': 6 * args.steps, 'clocks': clk.summary(),
+            'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': None,
+                         'peak_source': f'{pk_kind} bf16_tflops_sustained (per GPU, device time incl. all-reduce)'}}))
+    dp.close()
+    dist.destroy_process_group()
+
+
+def run_decode(args, device):
+    """Second headline: greedy decode of the 8B shape (batch 1, 4K context) through the same executor: tokens/s and the
+    fraction of the measured HBM copy bandwidth that the algorithmic bytes per token (bf16 weights + KV cache read) reach."""
+    import ctypes as C
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.decode import build_decode, kv_bytes, preset, weight_bytes
+    cfg = preset(args.decode_model)
+    d = Path(tempfile.gettempdir()) / 'kvm_b200_bundles' / f'decode-{args.decode_model}-b{cfg.batch}'
+    from kvm_b200.bundle import load_bundle
+    if (d / 'metadata.json').exists():
+        bundle = load_bundle(d)
+    else:
+        bundle = build_decode(cfg).to_bundle(check=False)
+        try:
+            bundle.write(d)
+        except OSError:
+            pass
+    ex = Executor(device=device)
+    ex.load(bundle)
+    ntok, warm = args.decode_tokens, 3
+    ex.run_steps(warm)
+    res = ex.run_steps(ntok)
+    tok_s = ntok / (res.ms / 1e3)
+    ctx_mid = cfg.ctx + warm + ntok / 2
+    bytes_tok = weight_bytes(cfg) + kv_bytes(cfg, ctx_mid)
+    pk, kind = peaks()
+    gbs = bytes_tok * tok_s / 1e9
+    tok = np.zeros(1, np.int32)
+    t0 = time.perf_counter()
+    for _ in range(ntok):
+        ex.run()
+        ex._check(ex.L.kvm_read_buffer_raw(ex._h, ex.index('u0.tok'), tok.ctypes.data, 4, 0))
+    e2e = ntok / (time.perf_counter() - t0)
+    out = {'metric': 'decode_tokens_per_s', 'workload': f'{args.decode_model}: {cfg.layers}L hidden {cfg.hidden} {cfg.heads}q/{cfg.kv_heads}kv heads hd{cfg.head_dim} ffn {cfg.ffn} '
+                                                      f'vocab {cfg.vocab}, bf16 weights, batch {cfg.batch}, context {cfg.ctx}, greedy; {len(bundle.tasks)} tasks per token, no QK-norm',
+           'value': tok_s, 'unit': 'tok/s', 'ms_per_token': res.ms / ntok, 'tokens': ntok, 'e2e': {'value': e2e, 'unit': 'tok/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 4},
+           'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'unit': 'GB/s', 'frac': gbs / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
+                        'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0])}
+    ex.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -280,12 +401,16 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--model', default='gpt_162m')
+    ap.add_argument('--decode-model', default='qwen3_8b')
+    ap.add_argument('--decode-tokens', type=int, default=32, help='tokens of the decode measurement appended to the line (0 = skip)')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='length of the CPU-oracle sample behind cpu_baseline (0 = skip)')
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
     if args.impl == 'reference':
         run_reference(args, rank, world)
+    elif world > 1:
+        run_dp(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -210,7 +210,9 @@ def _parse_init(where, init, rows, cols, dtype):
         _need(isinstance(raw, list) and len(raw) == n, f'{where}: init.values must be a list of {n} numbers')
         return {'kind': 'values', 'values': [conv(x) for x in raw]}
     if kind == 'seeded':
-        _need(dtype == 'f32', f'{where}: seeded init needs dtype f32')
+        # the reference compiler takes seeded only for f32; here a bf16 buffer may be seeded too (value rounded once to bf16):
+        # serving weights of the 8B-shape decode workload are generated in place instead of through 30 GB of f32 masters
+        _need(dtype in ('f32', 'bf16'), f'{where}: seeded init needs dtype f32 or bf16')
         scale = float(np.float32(init['scale']))
         dist = init.get('dist', 'normal')
         draws, bias, coef = seeded_params(dist, scale)

@@ -125,7 +125,7 @@ __device__ __forceinline__ float kvm_seeded_u(unsigned long long seed, unsigned 
   z ^= z >> 31;
   return __fmul_rn((float)(z >> 40), 1.0f / 16777216.0f);
 }
-__global__ void kvm_seeded_kernel(float* p, size_t n, unsigned long long seed, int draws, float bias, float coef) {
+__global__ void kvm_seeded_kernel(void* p, size_t n, unsigned long long seed, int draws, float bias, float coef, int dtype) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     float acc;
     if (draws == 1) acc = kvm_seeded_u(seed, i);
@@ -133,7 +133,9 @@ __global__ void kvm_seeded_kernel(float* p, size_t n, unsigned long long seed, i
       const unsigned long long j = i * (unsigned long long)draws;
       acc = __fadd_rn(__fadd_rn(kvm_seeded_u(seed, j), kvm_seeded_u(seed, j + 1)), __fadd_rn(kvm_seeded_u(seed, j + 2), kvm_seeded_u(seed, j + 3)));
     }
-    p[i] = __fmul_rn(__fsub_rn(acc, bias), coef);
+    const float v = __fmul_rn(__fsub_rn(acc, bias), coef);
+    if (dtype == KVM_BF16) ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+    else ((float*)p)[i] = v;
   }
 }
 __global__ void kvm_fill_kernel(void* p, size_t n, int dtype, double value) {

@@ -121,8 +121,8 @@ extern "C" int kvm_add_buffer(KvmExec* h, int32_t rows, int32_t cols, int32_t dt
     KVM_CUDA(cudaMemcpyAsync(p, init->data, bytes, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaStreamSynchronize(h->stream));
   } else if (kind == KVM_INIT_SEEDED) {
-    if (dtype != KVM_F32 || (init->draws != 1 && init->draws != 4)) { cudaFree(p); h->error = "kvm_add_buffer: seeded init needs f32 and draws 1 or 4"; return KVM_E_ARG; }
-    kvm_seeded_kernel<<<blocks, 256, 0, h->stream>>>((float*)p, n, init->seed, init->draws, init->bias, init->coef);
+    if (dtype == KVM_I32 || (init->draws != 1 && init->draws != 4)) { cudaFree(p); h->error = "kvm_add_buffer: seeded init needs f32 or bf16 storage and draws 1 or 4"; return KVM_E_ARG; }
+    kvm_seeded_kernel<<<blocks, 256, 0, h->stream>>>(p, n, init->seed, init->draws, init->bias, init->coef, dtype);
   } else if (kind != KVM_INIT_NONE) { cudaFree(p); h->error = "kvm_add_buffer: unknown init kind"; return KVM_E_ARG; }
   KVM_CUDA(cudaGetLastError());
   KvmBuf b{p, rows, cols, cols, dtype, {0, 0}};

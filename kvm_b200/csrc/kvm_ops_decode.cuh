@@ -83,6 +83,96 @@ __device__ void kvm_decode_group(const KvmBuf& kc, const KvmBuf& vc, size_t base
   }
 }
 
+// Vector form of the same partial attention for power-of-two head sizes (8..128) and 16-byte aligned cache rows: a key is
+// handled by hd/8 lanes (each holds 8 contiguous columns of K and V, one 16-byte load each for bf16), so a warp covers 32/(hd/8)
+// keys per step; two steps of loads are in flight before the first is consumed.  Every lane group keeps its own online-softmax
+// state per head; groups are merged by shuffles, warps through shared memory as in kvm_decode_group, same emit contract.
+template <int GT, class Emit>
+__device__ void kvm_decode_group_vec_t(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int LPK = hd >> 3, KPI = 32 / LPK, slot = lane / LPK, c0 = (lane % LPK) * 8;
+  float m[GT], l[GT], acc[GT][8];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) { m[g] = KVM_ATTN_EMPTY_M; l[g] = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc[g][t] = 0.0f; }
+  // contiguous key range per warp
+  const int n = j1 - j0, per = (n + KVM_NWARPS - 1) / KVM_NWARPS, w0 = j0 + warp * per, w1 = min(j1, w0 + per);
+  for (int jb = w0; jb < w1; jb += 2 * KPI) {
+    float kr[2][8], vr[2][8];
+    int jj[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      jj[u] = jb + u * KPI + slot;
+      if (jj[u] < w1) { kvm_ld8(kc, (base + jj[u]) * kc.ld + c0, kr[u]); kvm_ld8(vc, (base + jj[u]) * vc.ld + c0, vr[u]); }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const bool live = jj[u] < w1;
+#pragma unroll
+      for (int g = 0; g < GT; ++g) if (g < G) {
+        float s = 0.0f;
+        if (live) {
+          const float4 qa = *(const float4*)(qs + g * hd + c0), qb = *(const float4*)(qs + g * hd + c0 + 4);     // query columns of this lane (shared memory)
+          s = qa.x * kr[u][0] + qa.y * kr[u][1] + qa.z * kr[u][2] + qa.w * kr[u][3] + qb.x * kr[u][4] + qb.y * kr[u][5] + qb.z * kr[u][6] + qb.w * kr[u][7];
+        }
+        for (int o = LPK >> 1; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (live) {
+          s *= sc;
+          const float mn = fmaxf(m[g], s), corr = __expf(m[g] - mn), p = __expf(s - mn);
+          l[g] = l[g] * corr + p;
+#pragma unroll
+          for (int t = 0; t < 8; ++t) acc[g][t] = acc[g][t] * corr + p * vr[u][t];
+          m[g] = mn;
+        }
+      }
+    }
+  }
+  // merge the key slots of the warp (lanes with equal column range)
+#pragma unroll
+  for (int g = 0; g < GT; ++g) if (g < G) {
+    for (int o = LPK; o < 32; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o), lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo), ca = __expf(m[g] - mn), cb = __expf(mo - mn);
+      l[g] = l[g] * ca + lo * cb;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) acc[g][t] = acc[g][t] * ca + __shfl_xor_sync(0xffffffffu, acc[g][t], o) * cb;
+      m[g] = mn;
+    }
+  }
+  const int stride = hd + 2;
+  kvm_sync();
+#pragma unroll
+  for (int g = 0; g < GT; ++g) if (g < G && slot == 0) {
+    float* w = ws + (size_t)(warp * G + g) * stride;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) w[c0 + t] = acc[g][t];
+    if (lane == 0) { w[hd] = m[g]; w[hd + 1] = l[g]; }
+  }
+  kvm_sync();
+  for (int e = threadIdx.x; e < G * hd; e += KVM_NT) {
+    const int g = e / hd, cc = e % hd;
+    float M = KVM_ATTN_EMPTY_M;
+    for (int w = 0; w < KVM_NWARPS; ++w) if (ws[(size_t)(w * G + g) * stride + hd + 1] > 0.0f) M = fmaxf(M, ws[(size_t)(w * G + g) * stride + hd]);
+    float L = 0.0f, A = 0.0f;
+    for (int w = 0; w < KVM_NWARPS; ++w) {
+      const float* r = ws + (size_t)(w * G + g) * stride;
+      if (r[hd + 1] > 0.0f) { const float e2 = __expf(r[hd] - M); L += e2 * r[hd + 1]; A += e2 * r[cc]; }
+    }
+    emit(g, cc, M, L, A);
+  }
+}
+template <class Emit>
+__device__ void kvm_decode_group_vec(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+  if (G <= 1) kvm_decode_group_vec_t<1>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+  else if (G <= 2) kvm_decode_group_vec_t<2>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+  else if (G <= 4) kvm_decode_group_vec_t<4>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+  else kvm_decode_group_vec_t<8>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+}
+__device__ __forceinline__ bool kvm_decode_vec_ok(const KvmBuf& kc, const KvmBuf& vc, int hd) {
+  return hd >= 8 && hd <= 128 && (hd & (hd - 1)) == 0 && (kc.ld & 7) == 0 && (vc.ld & 7) == 0 && kvm_vec_ok(kc) && kvm_vec_ok(vc);
+}
+
 __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, kc, vc, lens, o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
@@ -100,7 +190,9 @@ __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) qs[cc] = kvm_ld(q, (size_t)b * q.ld + h * hd + cc);
   kvm_sync();
   const size_t base = (size_t)(b * Hkv + h / (H / Hkv)) * Tmax;
-  kvm_decode_group(kc, vc, base, 0, n, 1, hd, sc, qs, ws, [&](int, int cc, float, float Lsum, float A) { kvm_st(o, (size_t)b * o.ld + h * hd + cc, A / Lsum); });
+  auto emit = [&](int, int cc, float, float Lsum, float A) { kvm_st(o, (size_t)b * o.ld + h * hd + cc, A / Lsum); };
+  if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, 0, n, 1, hd, sc, qs, ws, emit);
+  else kvm_decode_group(kc, vc, base, 0, n, 1, hd, sc, qs, ws, emit);
 }
 
 __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
@@ -147,11 +239,13 @@ __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
   }
   kvm_sync();
   float* pp = (float*)part.p;
-  kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, [&](int g, int cc, float M, float Lsum, float A) {
+  auto emit = [&](int g, int cc, float M, float Lsum, float A) {
     const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
     pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
     if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M; pp[row + hd + 1] = Lsum; }
-  });
+  };
+  if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+  else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
 }
 
 __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
@@ -163,12 +257,20 @@ __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
   const float* pp = (const float*)part.p;
   for (int e = threadIdx.x; e < (h1 - h0) * hd; e += KVM_NT) {
     const int h = h0 + e / hd, cc = e % hd;
-    float M = KVM_ATTN_EMPTY_M;
-    for (int s = 0; s < S; ++s) { const float* r = pp + ((size_t)(b * S + s) * H + h) * part.ld; if (r[hd + 1] > 0.0f) M = fmaxf(M, r[hd]); }
-    float L = 0.0f, A = 0.0f;
-    for (int s = 0; s < S; ++s) {
-      const float* r = pp + ((size_t)(b * S + s) * H + h) * part.ld;
-      if (r[hd + 1] > 0.0f) { const float e2 = __expf(r[hd] - M); L += e2 * r[hd + 1]; A += e2 * r[cc]; }
+    float M = KVM_ATTN_EMPTY_M, L = 0.0f, A = 0.0f;
+    for (int s0 = 0; s0 < S; s0 += 8) {        // eight splits at a time: their loads are independent and issued together
+      float ms[8], ls[8], as[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int s = s0 + u;
+        const float* r = pp + ((size_t)(b * S + (s < S ? s : 0)) * H + h) * part.ld;
+        ms[u] = r[hd]; ls[u] = s < S ? r[hd + 1] : 0.0f; as[u] = r[cc];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (ls[u] > 0.0f) {      // split order, as the reference merges
+        const float mn = fmaxf(M, ms[u]), ca = __expf(M - mn), cb = __expf(ms[u] - mn);
+        L = L * ca + ls[u] * cb; A = A * ca + as[u] * cb; M = mn;
+      }
     }
     kvm_st(o, (size_t)b * o.ld + h * hd + cc, A / L);
   }
@@ -203,38 +305,52 @@ __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
   kvm_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p;
-  for (int nb = n0 + warp * 4; nb < n1; nb += KVM_NWARPS * 4) {
+  // Work units = (group of 4 rows) x (slice of K): few rows are split along K so that all 16 warps stream weights;
+  // the slices of a row are then added in slice order (fixed order, deterministic).
+  const int rows = n1 - n0, RG = (rows + 3) / 4;
+  int KS = 1;
+  while (KS < 16 && RG * KS < 2 * KVM_NWARPS && (K / (KS * 2)) >= 512) KS *= 2;
+  const int kslice = ((K / KS + 255) / 256) * 256;
+  float* parts = red + 64;                       // [RG][KS][4]
+  if ((K + 64 + RG * KS * 4) * 4 + 256 > c.smem_bytes) { c.fail(KVM_OPE_SMEM, K, rows); return; }
+  for (int u = warp; u < RG * KS; u += KVM_NWARPS) {
+    const int rg = u / KS, ks = u % KS, nb = n0 + rg * 4, nr = min(4, n1 - nb);
+    const int kend = min(K, (ks + 1) * kslice);
     float acc[4] = {0, 0, 0, 0};
-    const int nr = min(4, n1 - nb);
-    for (int k = lane * 8; k < K; k += 512) {
-      uint4 u[4][2];
-      const bool two = k + 256 < K;
+    for (int k = ks * kslice + lane * 8; k < kend; k += 512) {
+      uint4 wv[4][2];
+      const bool two = k + 256 < kend;
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const __nv_bfloat16* row = wp + (size_t)(nb + (r < nr ? r : 0)) * w.ld;
-        u[r][0] = __ldcs((const uint4*)(row + k));
-        u[r][1] = two ? __ldcs((const uint4*)(row + k + 256)) : make_uint4(0, 0, 0, 0);
+        wv[r][0] = __ldcs((const uint4*)(row + k));
+        wv[r][1] = two ? __ldcs((const uint4*)(row + k + 256)) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int hstep = 0; hstep < 2; ++hstep) {
         if (hstep == 1 && !two) break;
-        const float* vv = vs + k + hstep * 256;
+        const float4 va = *(const float4*)(vs + k + hstep * 256), vb = *(const float4*)(vs + k + hstep * 256 + 4);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          const __nv_bfloat162* hh = (const __nv_bfloat162*)&u[r][hstep];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(hh[j]); acc[r] = fmaf(vv[2 * j], f.x, acc[r]); acc[r] = fmaf(vv[2 * j + 1], f.y, acc[r]); }
+          const __nv_bfloat162* hh = (const __nv_bfloat162*)&wv[r][hstep];
+          const float2 f0 = __bfloat1622float2(hh[0]), f1 = __bfloat1622float2(hh[1]), f2 = __bfloat1622float2(hh[2]), f3 = __bfloat1622float2(hh[3]);
+          acc[r] = fmaf(va.x, f0.x, acc[r]); acc[r] = fmaf(va.y, f0.y, acc[r]); acc[r] = fmaf(va.z, f1.x, acc[r]); acc[r] = fmaf(va.w, f1.y, acc[r]);
+          acc[r] = fmaf(vb.x, f2.x, acc[r]); acc[r] = fmaf(vb.y, f2.y, acc[r]); acc[r] = fmaf(vb.z, f3.x, acc[r]); acc[r] = fmaf(vb.w, f3.y, acc[r]);
         }
       }
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const float s = kvm_warp_sum(acc[r]);
-      if (lane == 0 && r < nr) {
-        const int n = nb + r;
-        kvm_st(out, n, res.p ? __fadd_rn(s, kvm_ld(res, n)) : s);
-      }
+      const float sum = kvm_warp_sum(acc[r]);
+      if (lane == 0) parts[(rg * KS + ks) * 4 + r] = sum;
     }
+  }
+  kvm_sync();
+  for (int i = threadIdx.x; i < rows; i += KVM_NT) {
+    float sum = 0.0f;
+    for (int ks = 0; ks < KS; ++ks) sum += parts[((i >> 2) * KS + ks) * 4 + (i & 3)];
+    const int n = n0 + i;
+    kvm_st(out, n, res.p ? __fadd_rn(sum, kvm_ld(res, n)) : sum);
   }
 }
 

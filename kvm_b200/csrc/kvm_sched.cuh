@@ -240,14 +240,19 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       }
       // 3. termination / failure / stall
       if (!progressed) {
-        int d = 0, e = 0;
-        if (lane == 0) { d = kvm_ld_acquire(S.done); e = *(volatile int*)&S.err->code; }
-        d = __shfl_sync(0xffffffffu, d, 0); e = __shfl_sync(0xffffffffu, e, 0);
-        if (d >= S.nt || e != 0) stop = true;
-        if (stop && inflight == 0) break;
-        if ((++polls & 63u) == 0) {
-          if (kvm_globaltimer() - t_begin > S.timeout_ns) { if (lane == 0) kvm_dev_fail(S, KVM_ERR_TIMEOUT, ticket, d, inflight); stop = true; if (inflight == 0) break; }
-          __nanosleep(64);
+        // An idle worker mostly watches its ring cell (step 2); the global done / error words are looked at every 8th idle pass,
+        // so a newly pushed task is picked up within one cell poll rather than behind three dependent global loads.
+        if ((++polls & 7u) == 0 || stop) {
+          int d = 0, e = 0;
+          if (lane == 0) { d = kvm_ld_acquire(S.done); e = *(volatile int*)&S.err->code; }
+          d = __shfl_sync(0xffffffffu, d, 0); e = __shfl_sync(0xffffffffu, e, 0);
+          if (d >= S.nt || e != 0) stop = true;
+          if (stop && inflight == 0) break;
+          if ((polls & 255u) == 0 && kvm_globaltimer() - t_begin > S.timeout_ns) {
+            if (lane == 0) kvm_dev_fail(S, KVM_ERR_TIMEOUT, ticket, d, inflight);
+            stop = true;
+            if (inflight == 0) break;
+          }
         }
       } else polls = 0;
     }

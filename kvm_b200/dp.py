@@ -1,0 +1,62 @@
+"""Data-parallel training step: backward bundle -> gradient all-reduce -> optimizer bundle, one process per GPU.
+
+The semantics are the reference planner's (`runtime/partition.py:1301-1386`, DPPlanner): rank r trains on microbatch r of each
+group of P, every gradient is averaged over the P ranks before its first reader (the gradient-norm partials), clip and AdamW
+then run redundantly on identical values, so the replicas stay equal and the result equals gradient accumulation over P
+microbatches.  The reference builds the exchange from peer-store tasks inside its kernel; here it is one NCCL all-reduce
+(supplied by the caller, e.g. torch.distributed) over a single arena that holds every gradient buffer, between two launches
+of the persistent kernel.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .executor import Executor
+from .workloads.gpt import GPTConfig, build_training
+
+
+def grad_arena_layout(bundle):
+    """{buffer index: (offset_elems, n_elems)} of the f32 gradient buffers ('g.*') inside one contiguous arena, 64-element
+    (256-byte) aligned so vector accesses and TMA stay legal; and the arena length."""
+    lay, off = {}, 0
+    for b in bundle.buffers:
+        if b['name'].startswith('g.') and b['dtype'] == 0:
+            n = b['rows'] * b['cols']
+            lay[b['index']] = (off, n)
+            off += -(-n // 64) * 64
+    return lay, off
+
+
+class DataParallelStep:
+    """Two executor handles over one buffer table: `bwd` (data window, forward, backward) and `opt` (clip, AdamW, publishes)."""
+
+    def __init__(self, cfg: GPTConfig, rank: int, world: int, device: int, arena_ptr: int, stream_steps: int, bundles=None, **exec_kw):
+        if bundles is None:
+            g = build_training(cfg, 1, rank=rank, world=world, stream_steps=stream_steps)
+            bundles = g.to_bundles_split(g.split_at)
+        self.b_bwd, self.b_opt = bundles
+        self.layout, self.arena_elems = grad_arena_layout(self.b_bwd)
+        self.bwd = Executor(device=device, **exec_kw)
+        for spec in self.b_bwd.buffers:
+            if spec['index'] in self.layout:      # gradients live in the caller's arena so one collective covers them all
+                self.bwd.bind_buffer(arena_ptr + 4 * self.layout[spec['index']][0], spec['rows'], spec['cols'], 0, name=spec['name'])
+            else:
+                self.bwd.add_bundle_buffer(self.b_bwd, spec)
+        self.bwd.submit(self.b_bwd.tasks, self.b_bwd.succ, self.b_bwd.args)
+        self.bwd.bundle = self.b_bwd
+        self.opt = Executor(device=device, **exec_kw)
+        for spec in self.b_opt.buffers:
+            self.opt.bind_buffer(self.bwd.buffer_ptr(spec['index']), spec['rows'], spec['cols'], spec['dtype'], name=spec['name'])
+        self.opt.submit(self.b_opt.tasks, self.b_opt.succ, self.b_opt.args)
+        self.opt.bundle = self.b_opt
+
+    def step(self, all_reduce_mean):
+        """all_reduce_mean(): averages the arena over the ranks in place and returns when the result is visible to the device."""
+        r1 = self.bwd.run()
+        all_reduce_mean()
+        r2 = self.opt.run()
+        return r1, r2
+
+    def close(self):
+        self.opt.close()
+        self.bwd.close()

@@ -218,26 +218,30 @@ class Executor:
         """Create the bundle's buffers (metadata.json order, with their inits), set base versions, submit its tasks."""
         b = bundle if isinstance(bundle, Bundle) else load_bundle(bundle)
         for spec in b.buffers:
-            init, dt = spec['init'], spec['dtype']
-            kind = init['kind']
-            if kind == 'fill':
-                arg = init['value']
-            elif kind == 'values':
-                arg = np.array(init['values'], dtype=np.int32 if dt == 1 else np.float32)
-            elif kind == 'seeded':
-                arg = ('seeded', init['seed'], init['draws'], init['bias'], init['coef'])
-            elif kind == 'file':
-                raw = b.init_bytes(spec)
-                arg = np.frombuffer(raw, dtype='<u2' if dt == 2 else '<i4' if dt == 1 else '<f4')
-            else:
-                raise KvmError(-3, f"buffer {spec['name']!r}: unknown init kind {kind!r}")
-            self.add_buffer(spec['rows'], spec['cols'], dt, arg, name=spec['name'])
+            self.add_bundle_buffer(b, spec)
         for v in b.metadata.get('variables', []):
             if v.get('base_version', 0):
                 self.set_version(v['id'], v['base_version'])
         self.submit(b.tasks, b.succ, b.args)
         self.bundle = b
         return self
+
+    def add_bundle_buffer(self, b: Bundle, spec: dict) -> int:
+        """One buffer of a bundle's metadata with its init (fill / values / seeded / file)."""
+        init, dt = spec['init'], spec['dtype']
+        kind = init['kind']
+        if kind == 'fill':
+            arg = init['value']
+        elif kind == 'values':
+            arg = np.array(init['values'], dtype=np.int32 if dt == 1 else np.float32)
+        elif kind == 'seeded':
+            arg = ('seeded', init['seed'], init['draws'], init['bias'], init['coef'])
+        elif kind == 'file':
+            raw = b.init_bytes(spec)
+            arg = np.frombuffer(raw, dtype='<u2' if dt == 2 else '<i4' if dt == 1 else '<f4')
+        else:
+            raise KvmError(-3, f"buffer {spec['name']!r}: unknown init kind {kind!r}")
+        return self.add_buffer(spec['rows'], spec['cols'], dt, arg, name=spec['name'])
 
     def rearm(self):
         self._check(self.L.kvm_rearm(self._h))

@@ -1,0 +1,131 @@
+"""Greedy decode workloads in the reference's task ABI: a Llama/Qwen-shaped decoder (RMSNorm, GQA with RoPE, SwiGLU) generating
+one token per run for `batch` independent users, one row per user as the reference serves (`frontend/mvmfe/serve.py:1-11,72-83`).
+
+Per layer and user: q/k/v = gemv_bf16 with the RMSNorm prologue (pro 1); attn_decode_part over S context splits with fused
+RoPE + KV append (flags 3) and attn_decode_merge; o-projection gemv with the residual; gate / up gemv (pro 1); down-projection
+gemv with the SwiGLU prologue (pro 2) and the residual.  Then final norm folded into the LM-head gemv, argmax, and the
+bookkeeping for the next token (token -> gather_rows of the embedding, lens += 1).  Re-arming the one-token template generates
+the next token.  Op semantics: include/mvm_ops_extra.def:79-95 of the reference.  Weights are bf16 [N, K] serving copies
+(`serve.py:317-344`), here seeded in place; the KV cache is prefilled with seeded values standing in for a prompt of `ctx` tokens.
+QK RMSNorm (Qwen3) is not part of the reference op set and is left out.
+"""
+from __future__ import annotations
+
+import zlib
+from dataclasses import dataclass, replace
+
+import numpy as np
+
+from .graph import Graph
+
+
+@dataclass(frozen=True)
+class DecodeConfig:
+    name: str = 'decode_tiny'
+    layers: int = 2
+    hidden: int = 256
+    heads: int = 8
+    kv_heads: int = 2
+    head_dim: int = 32
+    ffn: int = 512
+    vocab: int = 1000
+    ctx: int = 40            # tokens already in the cache
+    tmax: int = 128
+    batch: int = 1
+    splits: int = 4
+    theta: float = 1e6
+    eps: float = 1e-6
+    init_std: float = 0.02
+    seed: int = 0
+    rows_per_task: int = 64
+
+
+PRESETS = {
+    'decode_tiny': DecodeConfig(),
+    # BASELINE config 5 (Qwen3-8B shape), 4K context
+    'qwen3_8b': DecodeConfig(name='qwen3_8b', layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
+                             splits=8, rows_per_task=128),
+    'qwen3_8b_4l': DecodeConfig(name='qwen3_8b_4l', layers=4, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
+                                splits=8, rows_per_task=128),
+}
+
+
+def preset(name, **over):
+    return replace(PRESETS[name], **over)
+
+
+def weight_bytes(c: DecodeConfig) -> int:
+    """bf16 bytes one token reads: all projection weights + LM head (the embedding row is negligible)."""
+    per_layer = c.hidden * (c.heads + 2 * c.kv_heads) * c.head_dim + c.heads * c.head_dim * c.hidden + 3 * c.hidden * c.ffn
+    return 2 * (c.layers * per_layer + c.vocab * c.hidden)
+
+
+def kv_bytes(c: DecodeConfig, ctx: int) -> int:
+    return c.layers * 2 * c.kv_heads * ctx * c.head_dim * 2
+
+
+def build_decode(c: DecodeConfig) -> Graph:
+    g = Graph('decode')
+    d, H, Hkv, hd, F, V, B, S = c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.batch, c.splits
+    seeded = lambda name, scale=None: {'kind': 'seeded', 'seed': zlib.crc32(f'{c.seed}/{name}'.encode()), 'scale': scale or c.init_std, 'dist': 'normal'}
+
+    def W(name, n, k):
+        return g.buffer('wb.' + name, n, k, 'bf16', seeded(name))
+
+    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20):
+        for n0 in range(0, n, c.rows_per_task):
+            n1 = min(n0 + c.rows_per_task, n)
+            g.task('gemv_bf16', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
+                   [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{n0 // c.rows_per_task}')
+
+    g.buffer('wb.embed', V, d, 'bf16', seeded('embed'))
+    g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
+    W('head', V, d)
+    for l in range(c.layers):
+        p = f'l{l}.'
+        g.buffer('w.' + p + 'ln1', 1, d, init={'kind': 'fill', 'value': 1.0}), g.buffer('w.' + p + 'ln2', 1, d, init={'kind': 'fill', 'value': 1.0})
+        W(p + 'q', H * hd, d), W(p + 'k', Hkv * hd, d), W(p + 'v', Hkv * hd, d), W(p + 'o', d, H * hd), W(p + 'gate', F, d), W(p + 'up', F, d), W(p + 'down', d, F)
+    # Every user is an independent one-row request with its own cache, length counter and activations (b = 0 in every op);
+    # the weights are shared.
+    for u in range(B):
+        t = f'u{u}.'
+        lens = g.buffer(t + 'lens', 1, 1, 'i32', {'kind': 'fill', 'value': c.ctx})
+        tok = g.buffer(t + 'tok', 1, 1, 'i32', {'kind': 'fill', 'value': (7 * u + 3) % V})
+        x = g.buffer(t + 'x', 1, d)
+        g.task('gather_rows', {'src': 'wb.embed', 'idx': tok, 'dst': x, 'r0': 0, 'r1': 1, 'd': d}, ['wb.embed', tok], [x], 31, t + 'embed')
+        for l in range(c.layers):
+            p, tl = f'l{l}.', f'{t}l{l}.'
+            prio = max(30 - l, 2)
+            kc = g.buffer(tl + 'kc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'kc', 1.0))
+            vc = g.buffer(tl + 'vc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'vc', 1.0))
+            q, k, v = g.buffer(tl + 'q', 1, H * hd), g.buffer(tl + 'k', 1, Hkv * hd), g.buffer(tl + 'v', 1, Hkv * hd)
+            gemv(tl + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
+            gemv(tl + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
+            gemv(tl + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
+            part, o = g.buffer(tl + 'part', S * H, hd + 2), g.buffer(tl + 'o', 1, H * hd)
+            G = H // Hkv
+            for kvh in range(Hkv):
+                rows = (kvh * c.tmax, (kvh + 1) * c.tmax)
+                # Only the split that holds the newest key appends (one cache row); which one depends on the length at run time.
+                # The splits of one step never touch each other's rows, so each declares a disjoint slice of the head's rows as
+                # written (ordering against the next step comes through `lens`), and the S splits run concurrently.
+                slice_ = c.tmax // S
+                for s in range(S):
+                    rows = (kvh * c.tmax + s * slice_, kvh * c.tmax + (s + 1) * slice_)
+                    g.task('attn_decode_part', {'q': q, 'kc': kc, 'vc': vc, 'lens': lens, 'part': part, 'knew': k, 'vnew': v, 'b': 0, 'kvh': kvh, 's': s, 'S': S, 'H': H,
+                                                'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
+                           [q, k, v, lens], [(kc, rows), (vc, rows), (part, (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{tl}part.{kvh}.{s}')
+            g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': 0, 'h1': H, 'S': S, 'H': H, 'hd': hd}, [part], [o], prio, tl + 'merge')
+            x1 = g.buffer(tl + 'x1', 1, d)
+            gemv(tl + 'o', o, 'wb.' + p + 'o', x1, d, H * hd, 0, res=x, prio=prio)
+            gate, up = g.buffer(tl + 'gate', 1, F), g.buffer(tl + 'up', 1, F)
+            gemv(tl + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio)
+            gemv(tl + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio)
+            xn = g.buffer(tl + 'x2', 1, d)
+            gemv(tl + 'down', gate, 'wb.' + p + 'down', xn, d, F, 2, x2=up, res=x1, prio=prio)
+            x = xn
+        logits = g.buffer(t + 'logits', 1, V)
+        gemv(t + 'head', x, 'wb.head', logits, V, d, 1, gamma='w.lnf', prio=1)
+        g.task('argmax', {'logits': logits, 'out': tok, 'r0': 0, 'r1': 1, 'V': V}, [logits], [tok], 1, t + 'argmax')
+        g.task('counter_inc', {'x': lens, 'i0': 0, 'i1': 1, 'delta': 1}, [lens], [lens], 0, t + 'advance')
+    return g

@@ -372,6 +372,7 @@ class _Emit:
             g.task('embedding_bwd', {'ids': None, 'dout': dres, 'dtab': 'g.wpe', 'N': N, 'mod': T, 'v0': v0, 'v1': v1, 'd': d, 'acc': 0},
                    [dres], [('g.wpe', (v0, v1))], self.prio, f'{tag}pos.bwd.{v0}')
 
+        g.split_at = len(g.tasks)       # data parallelism: the gradient all-reduce sits here, between backward and the optimizer
         # ---------------- clip + AdamW, bracketed by the two publishes of `weights`
         chunks = []
         for name, (rows, cols, _) in self.params.items():

@@ -215,6 +215,22 @@ class Graph:
             assert not problem, problem
         return b
 
+    def to_bundles_split(self, split_at: int):
+        """Two bundles over the same buffer table: tasks [0, split_at) and [split_at, end). The second is meant to run after the
+        first has finished entirely (a collective sits between them), so its edges from first-half tasks are dropped."""
+        import copy
+        first, second = copy.copy(self), copy.copy(self)
+        first.tasks, first.preds = self.tasks[:split_at], self.preds[:split_at]
+        first._pubs = {v: sum(1 for t in first.tasks if t['publishes'] == v) for v in self.variables}
+        second.tasks = [dict(t) for t in self.tasks[split_at:]]
+        second.preds = [[p - split_at for p in ps if p >= split_at] for ps in self.preds[split_at:]]
+        base = dict(first._pubs)
+        for t in second.tasks:      # publishes of the second half are numbered from 1 again: it is its own batch on its own handle
+            if t['pub']:
+                t['pub'] = (t['pub'][0], t['pub'][1] - base[t['pub'][0]])
+        second._pubs = {v: self._pubs[v] - base[v] for v in self.variables}
+        return first.to_bundle(), second.to_bundle()
+
     def to_spec(self) -> dict:
         """The same program as workload JSON (`FRAMEWORK.md:27-60` of the reference): what its compiler takes."""
         tasks = []

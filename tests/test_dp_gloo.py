@@ -1,0 +1,92 @@
+"""Data parallelism on CPU ranks (gloo, world size 2) with the oracle as the engine: the per-rank token split, the
+backward / all-reduce / optimizer split of the step, and the reference planner's contract that the replicas end bit-identical
+and equal to gradient accumulation over the two microbatches (runtime/partition.py:1302-1311 of the reference)."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kvm_b200.dp import grad_arena_layout
+from kvm_b200.workloads.gpt import build_training, preset
+from oracle.vm_np import VM
+
+
+def _run_rank_halves(rank, world, reduce_fn):
+    cfg = preset('gpt_micro')
+    g = build_training(cfg, 1, rank=rank, world=world, stream_steps=2)
+    b_bwd, b_opt = g.to_bundles_split(g.split_at)
+    lay, n = grad_arena_layout(b_bwd)
+    vm = VM(b_bwd)
+    for step in range(2):
+        vm.run()
+        arena = np.zeros(n, np.float32)
+        for idx, (off, cnt) in lay.items():
+            arena[off:off + cnt] = vm.bufs[idx].a.reshape(-1)
+        arena = reduce_fn(arena)
+        for idx, (off, cnt) in lay.items():
+            vm.bufs[idx].a.reshape(-1)[:] = arena[off:off + cnt]
+        vo = VM(b_opt, buffers=vm.bufs)
+        vo.run()
+        vm = VM(b_bwd, buffers=vo.bufs)
+    names = [s['name'] for s in b_bwd.buffers if s['name'].startswith('w.')]
+    return {nme: vm.buffer(nme).a.copy() for nme in names}
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+
+    def reduce_fn(arena):
+        t = torch.from_numpy(arena)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return (t * (1.0 / world)).numpy()
+
+    w = _run_rank_halves(rank, world, reduce_fn)
+    q.put((rank, {k: v.tobytes() for k, v in w.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_gradient_accumulation():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context('spawn')
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got[0].keys() == got[1].keys()
+    for k in got[0]:
+        assert got[0][k] == got[1][k], f'replicas diverged on {k}'
+    # single-process reference: both microbatches, gradients averaged, one optimizer step per step
+    cfg = preset('gpt_micro')
+    gs = [build_training(cfg, 1, rank=r, world=2, stream_steps=2) for r in range(2)]
+    halves = [g.to_bundles_split(g.split_at) for g in gs]
+    lay, n = grad_arena_layout(halves[0][0])
+    vms = [VM(h[0]) for h in halves]
+    for step in range(2):
+        for vm in vms:
+            vm.run()
+        for idx in lay:
+            avg = (vms[0].bufs[idx].a + vms[1].bufs[idx].a) * np.float32(0.5)
+            for vm in vms:
+                vm.bufs[idx].a[:] = avg
+        nxt = []
+        for vm, h in zip(vms, halves):
+            vo = VM(h[1], buffers=vm.bufs)
+            vo.run()
+            nxt.append(VM(h[0], buffers=vo.bufs))
+        vms = nxt
+    for k in got[0]:
+        assert vms[0].buffer(k).a.tobytes() == got[0][k], f'{k} differs from gradient accumulation'
+    # and the step really moved the weights
+    fresh = VM(halves[0][0])
+    assert any(fresh.buffer(k).a.tobytes() != got[0][k] for k in got[0])

@@ -101,3 +101,29 @@ def test_kv_append_rmsnorm_silu_rope_argmax_sample(kvm_lib):
     compare(ex, vm, 4e-3, tols={'xr': 1e-5, 'act': 1e-5, 'vc': 0.0, 'rs': 1e-6})
     assert ex.read_buffer('tok')[2, 0] == 10
     ex.close()
+
+
+def test_greedy_decode_32_tokens_identical(kvm_lib):
+    """North-star criterion: greedy tokens of the first 32 steps equal the CPU model's (two users, re-armed one-token template)."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.decode import build_decode, preset
+    from oracle.vm_np import VM
+    cfg = preset('decode_tiny', batch=2, init_std=0.08)
+    b = build_decode(cfg).to_bundle()
+    vm, ref = VM(b), []
+    for s in range(32):
+        vm.run()
+        ref.append([int(vm.buffer(f'u{u}.tok').a[0, 0]) for u in range(2)])
+        vm = VM(b, buffers=vm.bufs)
+    with Executor() as ex:
+        ex.load(b)
+        got = []
+        for s in range(32):
+            res = ex.run()
+            assert res.done == len(b.tasks)
+            got.append([int(ex.read_buffer(f'u{u}.tok')[0, 0]) for u in range(2)])
+        assert int(ex.read_buffer('u0.lens')[0, 0]) == cfg.ctx + 32
+        execs, observed = ex.task_counts()
+        assert (execs == 1).all() and np.array_equal(observed, b.tasks['indegree'])
+    assert got == ref
+    assert len({tuple(x) for x in ref}) > 1, 'degenerate test: the model emits one token pair only'
