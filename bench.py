@@ -319,7 +319,7 @@ def run_dp(args, rank, world, local_rank):
             r1, r2 = dp.step(all_reduce_mean)
             dev_ms += r1.ms + r2.ms
         dist.barrier(); torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
+        wall = time.perf_counter() - t0
     dev_ms += sum(comm_ms)
     t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device='cuda')
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
