@@ -43,6 +43,19 @@ __device__ __forceinline__ void kvm_store_tile_row32(unsigned char* tile, int r,
     *(uint4*)(rowp + (((u0 + u) ^ (r & 7)) << 4)) = w;
   }
 }
+// 16 consecutive values of row r, logical columns [k0, k0+16), same tile layout.
+__device__ __forceinline__ void kvm_store_tile_row16(unsigned char* tile, int r, int k0, const float (&v)[16]) {
+  unsigned char* rowp = tile + (k0 >> 6) * 16384 + r * 128;
+  const int u0 = (k0 & 63) >> 3;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    uint4 w;
+    __nv_bfloat162* hh = (__nv_bfloat162*)&w;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) hh[j] = __floats2bfloat162_rn(v[u * 8 + 2 * j], v[u * 8 + 2 * j + 1]);
+    *(uint4*)(rowp + (((u0 + u) ^ (r & 7)) << 4)) = w;
+  }
+}
 __device__ __forceinline__ void kvm_att_fail(const KvmCtx& c, int where) {
   if (atomicCAS(&c.err->code, 0, KVM_ERR_TIMEOUT) == 0) { c.err->task = c.task; c.err->a = where; c.err->b = (int)threadIdx.x; }
 }
@@ -227,15 +240,19 @@ __device__ void kvm_attn_dq_tc(const KvmCtx& c, const int32_t* a, const int4& au
     __syncwarp();
     if (!kvm_mbar_wait(bar(BS), (cS + j) & 1)) ok = false;
     kvm_tc_fence_after();
-    float s[32], dp[32];
-    kvm_tmem_ld32(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(cg * 32), s);
-    kvm_tmem_ld32(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(128 + cg * 32), dp);
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {        // two halves of 16 columns: half the live registers
+      float s[16], dp[16];
+      const int c0 = cg * 32 + hf * 16;
+      kvm_tmem_ld16(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)c0, s);
+      kvm_tmem_ld16(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(128 + c0), dp);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float p = (j == nb - 1 && cg * 32 + i > row) ? 0.0f : kvm_ex2(s[i] * sc2 - li2);
-      s[i] = p * (dp[i] - di);
+      for (int i = 0; i < 16; ++i) {
+        const float p = (j == nb - 1 && c0 + i > row) ? 0.0f : kvm_ex2(s[i] * sc2 - li2);
+        s[i] = p * (dp[i] - di);
+      }
+      kvm_store_tile_row16(DSt, row, c0, s);
     }
-    kvm_store_tile_row32(DSt, row, cg * 32, s);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     kvm_tc_fence_before();
     kvm_sync();
@@ -342,18 +359,22 @@ __device__ void kvm_attn_dkv_tc(const KvmCtx& c, const int32_t* a, const int4& a
     __syncwarp();
     if (!kvm_mbar_wait(bar(BS), (cS + it) & 1)) ok = false;
     kvm_tc_fence_after();
-    float s[32], dp[32];
-    kvm_tmem_ld32(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(cg * 32), s);
-    kvm_tmem_ld32(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(128 + cg * 32), dp);
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {        // two halves of 16 columns: half the live registers
+      float s[16], dp[16];
+      const int c0 = cg * 32 + hf * 16;
+      kvm_tmem_ld16(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)c0, s);
+      kvm_tmem_ld16(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(128 + c0), dp);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int qi = cg * 32 + i;                    // query index inside the block (column); row = key index inside the block
-      const float p = (diag && qi < row) ? 0.0f : kvm_ex2(s[i] * sc2 - vv[qi]);
-      s[i] = p;
-      dp[i] = p * (dp[i] - vv[128 + qi]);
+      for (int i = 0; i < 16; ++i) {
+        const int qi = c0 + i;                       // query index inside the block (column); row = key index inside the block
+        const float p = (diag && qi < row) ? 0.0f : kvm_ex2(s[i] * sc2 - vv[qi]);
+        s[i] = p;
+        dp[i] = p * (dp[i] - vv[128 + qi]);
+      }
+      kvm_store_tile_row16(PTt, row, c0, s);
+      kvm_store_tile_row16(DSTt, row, c0, dp);
     }
-    kvm_store_tile_row32(PTt, row, cg * 32, s);
-    kvm_store_tile_row32(DSTt, row, cg * 32, dp);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     kvm_tc_fence_before();
     kvm_sync();
@@ -391,7 +412,14 @@ __device__ void kvm_attn_dkv_tc(const KvmCtx& c, const int32_t* a, const int4& a
   kvm_tmem_ld16(tmem + ((uint32_t)(qd * 32) << 16) + (uint32_t)(320 + cg * 16), tk);
   if (ok) {
     const size_t kr = (size_t)(b * T + k0 + row) * dk.ld + kvh * 64 + cg * 16, vr = (size_t)(b * T + k0 + row) * dv.ld + kvh * 64 + cg * 16;
-    for (int i = 0; i < 16; ++i) { kvm_st(dk, kr + i, tk[i] * sc); kvm_st(dv, vr + i, tv[i]); }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tk[i] *= sc;
+    if ((dk.ld & 7) == 0 && (dv.ld & 7) == 0 && kvm_vec_ok(dk) && kvm_vec_ok(dv)) {
+      float a0[8], a1[8], b0[8], b1[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { a0[i] = tk[i]; a1[i] = tk[8 + i]; b0[i] = tv[i]; b1[i] = tv[8 + i]; }
+      kvm_st8(dk, kr, a0); kvm_st8(dk, kr + 8, a1); kvm_st8(dv, vr, b0); kvm_st8(dv, vr + 8, b1);
+    } else for (int i = 0; i < 16; ++i) { kvm_st(dk, kr + i, tk[i]); kvm_st(dv, vr + i, tv[i]); }
   }
   kvm_tc_fence_before();
   kvm_sync();
