@@ -298,7 +298,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   KvmDevState S{};
   S.tasks = h->d_tasks; S.succ = h->d_succ; S.args = h->d_args; S.nt = (int)h->tasks.size();
   S.indeg = h->d_indeg; S.exec_count = h->d_exec; S.ring = h->d_ring;
-  S.head = (unsigned*)h->d_ctl; S.tail = (unsigned*)h->d_ctl + 1; S.done = h->d_ctl + 2;
+  S.head = (unsigned*)h->d_ctl + 8; S.tail = (unsigned*)h->d_ctl + 12; S.done = h->d_ctl + 2;      // head[4], tail[4]: 16-byte aligned, one sector
   S.bufs = h->d_bufs; S.nbufs = (int)h->bufs.size();
   S.versions = h->d_versions; S.nvars = h->nvars; S.ver_base = h->d_ver_base; S.ver_off = h->d_ver_off; S.park_head = h->d_park_head; S.park_next = h->d_park_next;
   S.err = h->d_err;
@@ -330,7 +330,7 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     KVM_CUDA(cudaMalloc(&h->d_args, (h->args.size() + 1) * 4));
     KVM_CUDA(cudaMalloc(&h->d_aux, nt * sizeof(int4)));
     KVM_CUDA(cudaMalloc(&h->d_tmaps, (h->tmaps.size() + 1) * sizeof(CUtensorMap)));
-    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4));
+    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4));
     if (h->cfg.trace) { KVM_CUDA(cudaMalloc(&h->d_tstart, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tend, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tsmid, nt * 4)); }
     KVM_CUDA(cudaMemcpyAsync(h->d_tasks, h->tasks.data(), nt * sizeof(KvmTaskDesc), cudaMemcpyHostToDevice, h->stream));
     if (!h->succ.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_succ, h->succ.data(), h->succ.size() * 4, cudaMemcpyHostToDevice, h->stream));

@@ -37,6 +37,17 @@ __device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
   if (N < 0 || v0 < 0 || v1 < v0 || d <= 0 || (!ids.p && mod <= 0) || !kvm_mat_ok(c, dout, N, d) || !kvm_mat_ok(c, dt, v1, d) ||
       !kvm_flat_ok(c, ids, N)) { c.fail(KVM_OPE_RANGE, v0, v1); return; }
   float* tab = (float*)dt.p;
+  if (!ids.p) {
+    // positional table: key k collects rows k, k+mod, k+2*mod, ... in that (ascending) order; thread = (key, column)
+    for (long long e = threadIdx.x; e < (long long)(v1 - v0) * d; e += KVM_NT) {
+      const int key = v0 + (int)(e / d), col = (int)(e % d);
+      const size_t o = (size_t)key * dt.ld + col;
+      float sum = acc ? tab[o] : 0.0f;
+      if (key < mod) for (int r = key; r < N; r += mod) sum = __fadd_rn(sum, kvm_ld(dout, (size_t)r * dout.ld + col));
+      tab[o] = sum;
+    }
+    return;
+  }
   if (!acc)
     for (long long e = threadIdx.x; e < (long long)(v1 - v0) * d; e += KVM_NT) tab[(size_t)(v0 + e / d) * dt.ld + e % d] = 0.0f;
   int* list = (int*)c.smem;                       // [cap] rows, then KVM_NWARPS+1 counters

@@ -23,9 +23,9 @@ struct KvmDevState {
   int nt;
   int* indeg;                 // remaining predecessors per task
   int* exec_count;            // times executed (exactly-once witness)
-  int* ring;                  // ready ring: ring[ticket] = task + 1 once filled
-  unsigned* head;             // next pop ticket
-  unsigned* tail;             // next push ticket
+  int* ring;                  // ready rings, one per priority class: ring[c * nt + ticket] = task + 1 once filled
+  unsigned* head;             // head[c]: next pop ticket of class c   (head and tail words share one 32-byte sector)
+  unsigned* tail;             // tail[c]: next push ticket of class c
   int* done;                  // tasks finished
   const KvmBuf* bufs;
   int nbufs;
@@ -67,10 +67,42 @@ __device__ __forceinline__ void kvm_dev_fail(const KvmDevState& S, int code, int
   if (atomicCAS(&S.err->code, 0, code) == 0) { S.err->task = task; S.err->a = a; S.err->b = b; __threadfence_system(); }
 }
 
+// Priority classes: the ABI's 32 priorities (larger first, include/mvm_task_abi.h:16) fold into KVM_NCLASS rings, class = priority / 8.
+// A pop looks at the classes from the highest down and claims a ticket only where one is known to be filled or about to be
+// (head < tail, compare-and-swap), so no worker ever commits to a ticket that may stay empty.
+#define KVM_NCLASS 4
+__device__ __forceinline__ int kvm_class_of(int priority) { return priority < 0 ? 0 : (priority >> 3) >= KVM_NCLASS ? KVM_NCLASS - 1 : (priority >> 3); }
 __device__ __forceinline__ void kvm_push_ready(const KvmDevState& S, int task) {
-  unsigned t = atomicAdd(S.tail, 1u);
+  const int c = kvm_class_of(S.tasks[task].priority);
+  unsigned t = atomicAdd(&S.tail[c], 1u);
   if (t >= (unsigned)S.nt) { kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, task, (int)t); return; }
-  kvm_st_release(&S.ring[t], task + 1);
+  kvm_st_release(&S.ring[(size_t)c * S.nt + t], task + 1);
+}
+// Pop, highest class first.  Tickets are taken with atomicAdd (no compare-and-swap convoy when many workers are idle) but only
+// where head < tail was just seen; a ticket that lost that race and points past the tail is HELD: the worker keeps polling its
+// cell while it goes on serving the other classes, so a held ticket can never starve anyone.  held[c] = ring cell or -1.
+// Returns task or -1.
+__device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM_NCLASS]) {
+#pragma unroll
+  for (int c = KVM_NCLASS - 1; c >= 0; --c)
+    if (held[c] >= 0) {
+      const int v = kvm_ld_acquire(&S.ring[held[c]]);
+      if (v > 0) { held[c] = -1; return v - 1; }
+    }
+  unsigned t[4], h[4];
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "l"(S.head) : "memory");
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]) : "l"(S.tail) : "memory");
+#pragma unroll
+  for (int c = KVM_NCLASS - 1; c >= 0; --c)
+    if (held[c] < 0 && h[c] < t[c]) {
+      const unsigned tk = atomicAdd(&S.head[c], 1u);
+      if (tk >= (unsigned)S.nt) continue;
+      const int cell = (int)((size_t)c * S.nt + tk);
+      const int v = kvm_ld_acquire(&S.ring[cell]);
+      if (v > 0) return v - 1;
+      held[c] = cell;                      // its pusher is one store away, or the race was lost: look again next pass
+    }
+  return -1;
 }
 
 // Push `task` onto the parked list of `var` (lock-free stack).
@@ -125,7 +157,8 @@ __global__ void kvm_arm_kernel(KvmDevState S) {
   if (i < S.nt) {
     S.indeg[i] = S.tasks[i].indegree;
     S.exec_count[i] = 0;
-    S.ring[i] = 0;
+#pragma unroll
+    for (int c = 0; c < KVM_NCLASS; ++c) S.ring[(size_t)c * S.nt + i] = 0;
     S.park_next[i] = -1;
   }
   if (i < S.nvars) { S.park_head[i] = -1; S.ver_off[i] = S.versions[i] - S.ver_base[i]; }
@@ -198,7 +231,8 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
     int fill = 0;              // slot to fill next
     int drain = 0;             // slot whose completion is due next (tasks finish in slot order)
     int inflight = 0;          // slots handed to the compute group and not yet released
-    int ticket = -1;           // claimed, unfilled ticket
+    int ticket = -1;           // >= 0 while this worker holds an unfilled ticket
+    int held[KVM_NCLASS] = {-1, -1, -1, -1};
     int cont = -1;             // continuation ready to be staged
     bool stop = false;
     unsigned polls = 0;
@@ -219,11 +253,10 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         int task = -1;
         if (cont >= 0) { task = cont; cont = -1; }
         else {
-          if (ticket < 0) { int t = 0; if (lane == 0) t = (int)atomicAdd(S.head, 1u); ticket = __shfl_sync(0xffffffffu, t, 0); }
-          int v = 0;
-          if (lane == 0 && ticket < S.nt) v = kvm_ld_acquire(&S.ring[ticket]);
-          v = __shfl_sync(0xffffffffu, v, 0);
-          if (v > 0) { task = v - 1; ticket = -1; }
+          int tk = -1, hold = 0;
+          if (lane == 0) { tk = kvm_try_pop(S, held); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
+          task = __shfl_sync(0xffffffffu, tk, 0);
+          ticket = __shfl_sync(0xffffffffu, hold, 0) ? 0 : -1;      // ticket >= 0 now only means: this worker holds a ticket (no continuation then)
         }
         if (task >= 0) {
           KvmSlot& sl = slots[fill];

@@ -169,7 +169,7 @@ class _Emit:
                 if pre:
                     wr.append((pre, (m0, m1), (n0, n1)))
                 g.task(op, {'a': a, 'b': w, 'out': out, 'bias': bias, 'res': res, 'pre': pre, 'm0': m0, 'n0': n0, 'M': M, 'N': N, 'K': K,
-                            'flags': flags, 'alpha': alpha}, rd, wr, self.prio, f'{tag}.{m0 // tm}.{n0 // tn}')
+                            'flags': flags, 'alpha': alpha}, rd, wr, min(self.prio, 7) if ta else self.prio, f'{tag}.{m0 // tm}.{n0 // tn}')
 
     def rows(self, op, tag, N, per, args, reads, writes, vec_r=(), vec_w=()):
         """Row-block tasks over [0,N): matrices in reads/writes are touched on rows [r0,r1); vec_* are [N]-long flat vectors."""
@@ -305,7 +305,7 @@ class _Emit:
             self.linear(t + 'proj', a, self.W(p + 'proj.w'), xo, N, d, F, bias='w.' + p + 'proj.b', res=xm)
             saved.append((x, h1, mu1, rs1, q, k, v, o, lse, xm, h2, mu2, rs2, pre, a))
             x = xo
-        self.prio = 15
+        self.prio = 23
         hf, muf, rsf = B('hf', N, d, act), B('muf', N, 1), B('rsf', N, 1)
         self.layernorm(tag + 'lnf', x, 'w.lnf.g', 'w.lnf.b', hf, muf, rsf)
         logits = B('logits', N, V, act)
@@ -322,7 +322,9 @@ class _Emit:
         g.task('softmax_ce_reduce', {'rowloss': rowloss, 'tgt': tgt, 'loss': loss, 'N': N, 'ignore': -1}, [rowloss, tgt], [loss], 0, tag + 'loss')
 
         # ---------------- backward
-        self.prio = 14
+        # backward: the chain of input-gradient ops is the critical path (class 1); weight / bias / norm-parameter gradients only feed
+        # the optimizer and run as filler (class 0: the ready queue serves higher classes first)
+        self.prio = 15
         dhf = B('dhf', N, d, act)
         if c.tied:
             self.linear(tag + 'head.dx', dlog, self.W('wte'), dhf, N, d, V)
@@ -334,7 +336,7 @@ class _Emit:
         self.layernorm_bwd(tag + 'lnf.bwd', x, dhf, 'lnf', muf, rsf, dres, 0)
         for l in reversed(range(L)):
             p, t = f'h{l}.', f'{tag}h{l}.bwd.'
-            self.prio = max(13 - (L - 1 - l), 3)
+            self.prio = 15
             x_in, h1, mu1, rs1, q, k, v, o, lse, xm, h2, mu2, rs2, pre, a = saved[l]
             dres_op = self.to_operand(t + 'dres.bf', dres, N, d)
             da = B('da', N, F, act)
@@ -367,8 +369,9 @@ class _Emit:
             v1 = min(v0 + c.key_chunk, V)
             g.task('embedding_bwd', {'ids': ids, 'dout': dres, 'dtab': 'g.wte', 'N': N, 'mod': 0, 'v0': v0, 'v1': v1, 'd': d, 'acc': 1 if c.tied else 0},
                    [ids, dres, ('g.wte', (v0, v1))] if c.tied else [ids, dres], [('g.wte', (v0, v1))], self.prio, f'{tag}embed.bwd.{v0}')
-        for v0 in range(0, T, c.key_chunk):
-            v1 = min(v0 + c.key_chunk, T)
+        pos_chunk = max(1, min(c.key_chunk, T // 32 if T >= 64 else T))
+        for v0 in range(0, T, pos_chunk):
+            v1 = min(v0 + pos_chunk, T)
             g.task('embedding_bwd', {'ids': None, 'dout': dres, 'dtab': 'g.wpe', 'N': N, 'mod': T, 'v0': v0, 'v1': v1, 'd': d, 'acc': 0},
                    [dres], [('g.wpe', (v0, v1))], self.prio, f'{tag}pos.bwd.{v0}')
 
