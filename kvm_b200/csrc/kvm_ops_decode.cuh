@@ -6,6 +6,7 @@
 #include "kvm_dev.cuh"
 #include "kvm_ops_flat.cuh"
 #include "kvm_ops_rows.cuh"
+#include "kvm_decode_stream.cuh"
 
 #define KVM_ATTN_EMPTY_M (-3.4028234663852886e38f)
 
@@ -210,40 +211,55 @@ __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
   if (p0 < 0 || n > Tmax) { c.fail(KVM_OPE_KVLEN, b, p0); return; }
   const int chunk = (n + S - 1) / S, j0 = s * chunk, j1 = min(n, s * chunk + chunk), half = hd / 2;
   const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
-  float* qs = (float*)c.smem;                 // G*hd
-  float* inv = qs + 8 * 128;                  // hd/2 inverse frequencies
-  float* ws = inv + 64;
-  kvm_sync();
-  if (fl & 1) for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
-  kvm_sync();
-  if ((fl & 1) && j0 <= n - 1 && n - 1 < j1) {   // this split appends the new key / value (rotated key), rounded to the cache dtype
-    for (int i = threadIdx.x; i < half; i += KVM_NT) {
-      float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-      const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
-      kvm_st(kc, (base + n - 1) * kc.ld + i, x1 * co - x2 * sn);
-      kvm_st(kc, (base + n - 1) * kc.ld + i + half, x1 * sn + x2 * co);
-    }
-    for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) kvm_st(vc, (base + n - 1) * vc.ld + cc, kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc));
-    __threadfence_block();
-  }
-  for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
-    const int g = e / half, i = e % half, h = kvh * G + g;
-    float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
+  float* qs = (float*)(c.smem + KVM_AS_OFF_QS);                  // G*hd rotated queries
+  float* inv = (float*)(c.smem + KVM_AS_OFF_INV);                // hd/2 inverse frequencies
+  float* kns = (float*)(c.smem + KVM_AS_OFF_KNEW);               // the appended key (rotated) and value, float
+  float* vns = (float*)(c.smem + KVM_AS_OFF_VNEW);
+  float* ws = (float*)(c.smem + KVM_AS_OFF_SC);
+  const bool appends = (fl & 1) && j0 <= n - 1 && n - 1 < j1;    // this split holds the newest key: it appends (rotated key), rounded to the cache dtype
+  auto prologue = [&]() {
     if (fl & 1) {
-      float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-      const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
-      x1 = y1; x2 = y2;
-      if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
+      for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
+      kvm_sync();
     }
-    qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
-  }
-  kvm_sync();
+    if (appends) {
+      for (int i = threadIdx.x; i < half; i += KVM_NT) {
+        float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+        const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
+        const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+        kns[i] = y1; kns[i + half] = y2;
+        kvm_st(kc, (base + n - 1) * kc.ld + i, y1);
+        kvm_st(kc, (base + n - 1) * kc.ld + i + half, y2);
+      }
+      for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) {
+        const float t = kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc);
+        vns[cc] = t;
+        kvm_st(vc, (base + n - 1) * vc.ld + cc, t);
+      }
+    }
+    for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
+      const int g = e / half, i = e % half, h = kvh * G + g;
+      float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
+      if (fl & 1) {
+        float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+        const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+        x1 = y1; x2 = y2;
+        if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
+      }
+      qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
+    }
+  };
   float* pp = (float*)part.p;
   auto emit = [&](int g, int cc, float M, float Lsum, float A) {
     const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
     pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
     if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M; pp[row + hd + 1] = Lsum; }
   };
+  if (kvm_attn_part_stream(c, kc, vc, base, j0, j1, appends ? n - 1 - j0 : -1, G, hd, sc, prologue, emit)) return;
+  kvm_sync();
+  prologue();
+  __threadfence_block();
+  kvm_sync();
   if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
   else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
 }
@@ -288,6 +304,7 @@ __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
   if (n0 < 0 || n1 <= n0 || K <= 0 || (K & 7) || pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || (w.ld & 7) || !kvm_vec_ok(w) ||
       K * 4 + 256 > c.smem_bytes) { c.fail(KVM_OPE_SHAPE, K, pro); return; }
   if (!kvm_mat_ok(c, w, n1, K) || !kvm_mat_ok(c, x, 1, K) || !kvm_mat_ok(c, x2, 1, K) || !kvm_flat_ok(c, gm, K) || !kvm_mat_ok(c, out, 1, n1) || !kvm_mat_ok(c, res, 1, n1)) return;
+  if (kvm_gemv_stream(c, x, x2, gm, w, out, res, n0, n1, K, pro, eps)) return;      // bulk-copy ring; the form below serves what does not fit
   float* vs = (float*)c.smem;
   float* red = vs + K;
   float rs = 1.0f;

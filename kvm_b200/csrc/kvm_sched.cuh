@@ -81,8 +81,10 @@ __device__ __forceinline__ void kvm_push_ready(const KvmDevState& S, int task) {
 // Pop, highest class first.  Tickets are taken with atomicAdd (no compare-and-swap convoy when many workers are idle) but only
 // where head < tail was just seen; a ticket that lost that race and points past the tail is HELD: the worker keeps polling its
 // cell while it goes on serving the other classes, so a held ticket can never starve anyone.  held[c] = ring cell or -1.
+// `min_depth`: a worker that is still running a task stages its next one only while at least that many tasks are queued
+// (one for every worker): with fewer, the queued tasks are left to the idle workers instead of waiting behind a running one.
 // Returns task or -1.
-__device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM_NCLASS]) {
+__device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM_NCLASS], unsigned min_depth) {
 #pragma unroll
   for (int c = KVM_NCLASS - 1; c >= 0; --c)
     if (held[c] >= 0) {
@@ -92,6 +94,12 @@ __device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM
   unsigned t[4], h[4];
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "l"(S.head) : "memory");
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]) : "l"(S.tail) : "memory");
+  if (min_depth > 1) {
+    unsigned depth = 0;
+#pragma unroll
+    for (int c = 0; c < KVM_NCLASS; ++c) depth += t[c] > h[c] ? t[c] - h[c] : 0u;
+    if (depth < min_depth) return -1;
+  }
 #pragma unroll
   for (int c = KVM_NCLASS - 1; c >= 0; --c)
     if (held[c] < 0 && h[c] < t[c]) {
@@ -254,7 +262,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         if (cont >= 0) { task = cont; cont = -1; }
         else {
           int tk = -1, hold = 0;
-          if (lane == 0) { tk = kvm_try_pop(S, held); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
+          if (lane == 0) { tk = kvm_try_pop(S, held, inflight > 0 ? gridDim.x : 1u); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
           task = __shfl_sync(0xffffffffu, tk, 0);
           ticket = __shfl_sync(0xffffffffu, hold, 0) ? 0 : -1;      // ticket >= 0 now only means: this worker holds a ticket (no continuation then)
         }

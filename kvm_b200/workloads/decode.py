@@ -37,16 +37,17 @@ class DecodeConfig:
     eps: float = 1e-6
     init_std: float = 0.02
     seed: int = 0
-    rows_per_task: int = 64
+    rows_per_task: int = 64  # weight rows per gemv task; 0 = balance every phase over `workers` SMs
+    workers: int = 148
 
 
 PRESETS = {
     'decode_tiny': DecodeConfig(),
     # BASELINE config 5 (Qwen3-8B shape), 4K context
     'qwen3_8b': DecodeConfig(name='qwen3_8b', layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                             splits=8, rows_per_task=128),
+                             splits=16, rows_per_task=0),
     'qwen3_8b_4l': DecodeConfig(name='qwen3_8b_4l', layers=4, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                                splits=8, rows_per_task=128),
+                                splits=16, rows_per_task=0),
 }
 
 
@@ -72,11 +73,24 @@ def build_decode(c: DecodeConfig) -> Graph:
     def W(name, n, k):
         return g.buffer('wb.' + name, n, k, 'bf16', seeded(name))
 
-    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20):
-        for n0 in range(0, n, c.rows_per_task):
-            n1 = min(n0 + c.rows_per_task, n)
+    def phase_rows(ns, k):
+        """Weight rows per task for a phase of concurrent GEMVs with ns[i] rows of length k: the smallest equal share that fits
+        the phase into whole waves over the SMs, with as many waves as keep a task near 2 MB of weights."""
+        if c.rows_per_task > 0:
+            return c.rows_per_task
+        total = sum(ns)
+        slots = c.workers * max(1, round(total * k * 2 / (c.workers * (2 << 20))))
+        rows = max(8, -(-total // slots))
+        while sum(-(-n // rows) for n in ns) > slots:
+            rows += 1
+        return rows
+
+    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20, rows=None):
+        rows = rows or phase_rows([n], k)
+        for i, n0 in enumerate(range(0, n, rows)):
+            n1 = min(n0 + rows, n)
             g.task('gemv_bf16', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
-                   [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{n0 // c.rows_per_task}')
+                   [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{i}')
 
     g.buffer('wb.embed', V, d, 'bf16', seeded('embed'))
     g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
@@ -99,9 +113,10 @@ def build_decode(c: DecodeConfig) -> Graph:
             kc = g.buffer(tl + 'kc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'kc', 1.0))
             vc = g.buffer(tl + 'vc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'vc', 1.0))
             q, k, v = g.buffer(tl + 'q', 1, H * hd), g.buffer(tl + 'k', 1, Hkv * hd), g.buffer(tl + 'v', 1, Hkv * hd)
-            gemv(tl + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
-            gemv(tl + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
-            gemv(tl + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio)
+            r_qkv = phase_rows([H * hd, Hkv * hd, Hkv * hd], d)           # q, k and v run as one phase
+            gemv(tl + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
+            gemv(tl + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
+            gemv(tl + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
             part, o = g.buffer(tl + 'part', S * H, hd + 2), g.buffer(tl + 'o', 1, H * hd)
             G = H // Hkv
             for kvh in range(Hkv):
@@ -115,12 +130,15 @@ def build_decode(c: DecodeConfig) -> Graph:
                     g.task('attn_decode_part', {'q': q, 'kc': kc, 'vc': vc, 'lens': lens, 'part': part, 'knew': k, 'vnew': v, 'b': 0, 'kvh': kvh, 's': s, 'S': S, 'H': H,
                                                 'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
                            [q, k, v, lens], [(kc, rows), (vc, rows), (part, (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{tl}part.{kvh}.{s}')
-            g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': 0, 'h1': H, 'S': S, 'H': H, 'hd': hd}, [part], [o], prio, tl + 'merge')
+            for kvh in range(Hkv):                              # one merge per GQA group: short tasks, all concurrent
+                g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': H, 'hd': hd},
+                       [part], [(o, (0, 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{tl}merge.{kvh}')
             x1 = g.buffer(tl + 'x1', 1, d)
             gemv(tl + 'o', o, 'wb.' + p + 'o', x1, d, H * hd, 0, res=x, prio=prio)
             gate, up = g.buffer(tl + 'gate', 1, F), g.buffer(tl + 'up', 1, F)
-            gemv(tl + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio)
-            gemv(tl + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio)
+            r_gu = phase_rows([F, F], d)
+            gemv(tl + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
+            gemv(tl + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
             xn = g.buffer(tl + 'x2', 1, d)
             gemv(tl + 'down', gate, 'wb.' + p + 'down', xn, d, F, 2, x2=up, res=x1, prio=prio)
             x = xn
