@@ -44,7 +44,9 @@ struct KvmDevState {
   int cfg_flags;
   const void* tmaps;          // CUtensorMap table for tensor-core tasks
   const int4* task_aux;       // per task: tensor-map indices / path selector
+  const int32_t* recs;        // per task KVM_REC_WORDS words: descriptor [0,16), argument words [16,36), path selector [36,40)
 };
+#define KVM_REC_WORDS 48
 
 struct KvmSlot {
   int task;                   // -1 = leave
@@ -61,6 +63,7 @@ __device__ __forceinline__ int kvm_ld_acquire(const int* p) {
   return v;
 }
 __device__ __forceinline__ void kvm_st_release(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void kvm_st_relaxed(int* p, int v) { asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ int kvm_ld_volatile_shared(const int* p) { return *(volatile const int*)p; }
 
 __device__ __forceinline__ void kvm_dev_fail(const KvmDevState& S, int code, int task, int a = 0, int b = 0) {
@@ -180,18 +183,21 @@ __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* args, const
 
 #define KVM_EXEC_SMEM_HDR 1024     // slots + control words at the start of dynamic shared memory
 
-// The scheduler warp's share of finishing `task` (descriptor words in `desc`): publish, release successors.
-// Returns a continuation task (>= 0) when exactly the caller may run one directly, else -1.
-__device__ int kvm_finish_task(const KvmDevState& S, const int32_t* desc, int task, bool want_cont) {
+// The scheduler warp's share of finishing `task`: publish its version, then release its successors.
+// The successors are taken eight per lane at a time and every step is done for all of them before the next one starts: the
+// index loads, the counter decrements, the look at the ready ones' descriptors, and one ticket grab per priority class for the
+// whole warp - so a fan-out of a few hundred costs the same handful of memory round trips as a fan-out of one.
+// Returns a continuation task (>= 0) when the caller may run one directly, else -1.
+#define KVM_REL_U 8
+__device__ int kvm_finish_task(const KvmDevState& S, int task, int so, int sc, int pv, int pver, bool want_cont) {
   const int lane = threadIdx.x & 31;
   __threadfence();             // pairs with the compute group's fence before it flagged the slot finished
-  const int pv = desc[10];
   if (pv >= 0) {
     if (lane == 0) {
       if (pv >= S.nvars) kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, pv);
       else {
         __threadfence();
-        const int ver = desc[11] + S.ver_off[pv];
+        const int ver = pver + S.ver_off[pv];
         if (atomicCAS(&S.versions[pv], ver - 1, ver) != ver - 1) kvm_dev_fail(S, KVM_ERR_VERSION_GAP, task, pv, ver);
         __threadfence();
         kvm_scan_parked(S, pv);
@@ -199,27 +205,68 @@ __device__ int kvm_finish_task(const KvmDevState& S, const int32_t* desc, int ta
     }
     __syncwarp();
   }
-  const int so = desc[1], sc = desc[2];
   int cont = -1;
-  for (int k0 = 0; k0 < sc; k0 += 32) {
-    const int k = k0 + lane;
-    int rdy = -1;
-    if (k < sc) {
-      const int s = S.succ[so + k];
-      const int old = atomicSub(&S.indeg[s], 1);
-      if (old == 1) rdy = s;
-      else if (old <= 0) kvm_dev_fail(S, KVM_ERR_BAD_TASK, s, old);
+  for (int k0 = 0; k0 < sc; k0 += 32 * KVM_REL_U) {
+    int s[KVM_REL_U], kind[KVM_REL_U];       // kind: -1 nothing, 0..3 enqueue in that class, 4 version wait
+#pragma unroll
+    for (int u = 0; u < KVM_REL_U; ++u) { const int k = k0 + u * 32 + lane; s[u] = k < sc ? S.succ[so + k] : -1; }
+#pragma unroll
+    for (int u = 0; u < KVM_REL_U; ++u) {
+      kind[u] = -1;
+      if (s[u] >= 0) {
+        const int old = atomicSub(&S.indeg[s[u]], 1);
+        if (old == 1) kind[u] = 0;
+        else if (old <= 0) kvm_dev_fail(S, KVM_ERR_BAD_TASK, s[u], old);
+      }
     }
-    // The first ready successor without a version wait may become the continuation (no queue hop).
-    unsigned m = __ballot_sync(0xffffffffu, rdy >= 0 && want_cont && cont < 0 && S.tasks[rdy >= 0 ? rdy : 0].wait_var < 0);
-    int take = -1;
-    if (m) { take = __ffs(m) - 1; cont = __shfl_sync(0xffffffffu, rdy, take); }
-    if (rdy >= 0 && lane != take) kvm_release_task(S, rdy);
+    // One fence for the whole batch: whoever made a counter reach zero has seen every other predecessor's decrement, and those
+    // came after their data; the ring cells below are then plain stores (their readers load with acquire).
+    __threadfence();
+#pragma unroll
+    for (int u = 0; u < KVM_REL_U; ++u)
+      if (kind[u] == 0) {
+        const KvmTaskDesc& d = S.tasks[s[u]];
+        kind[u] = d.wait_var >= 0 ? 4 : kvm_class_of(d.priority);
+      }
+    // the continuation: the first ready successor without a version wait (no queue hop)
+#pragma unroll
+    for (int u = 0; u < KVM_REL_U; ++u) {
+      const unsigned mc = __ballot_sync(0xffffffffu, kind[u] >= 0 && kind[u] < 4 && want_cont && cont < 0);
+      if (mc) {
+        const int take = __ffs(mc) - 1;
+        cont = __shfl_sync(0xffffffffu, s[u], take);
+        if (lane == take) kind[u] = -1;
+      }
+    }
+    // enqueue: one ticket grab per class for the warp
+#pragma unroll
+    for (int c = KVM_NCLASS - 1; c >= 0; --c) {
+      int n = 0;
+#pragma unroll
+      for (int u = 0; u < KVM_REL_U; ++u) n += kind[u] == c;
+      if (!__any_sync(0xffffffffu, n > 0)) continue;
+      int incl = n;                                           // inclusive prefix sum over the lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      const int total = __shfl_sync(0xffffffffu, incl, 31);
+      unsigned base = 0;
+      if (lane == 0) base = atomicAdd(&S.tail[c], (unsigned)total);
+      base = __shfl_sync(0xffffffffu, base, 0);
+      unsigned t = base + (unsigned)(incl - n);
+#pragma unroll
+      for (int u = 0; u < KVM_REL_U; ++u)
+        if (kind[u] == c) {
+          if (t >= (unsigned)S.nt) kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, s[u], (int)t);
+          else kvm_st_relaxed(&S.ring[(size_t)c * S.nt + t], s[u] + 1);
+          ++t;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < KVM_REL_U; ++u) if (kind[u] == 4) kvm_release_task(S, s[u]);     // version waits: check, park or enqueue
   }
   if (lane == 0) atomicAdd(S.done, 1);
   return cont;
 }
-
 __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S) {
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
   KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
@@ -241,6 +288,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
     int inflight = 0;          // slots handed to the compute group and not yet released
     int ticket = -1;           // >= 0 while this worker holds an unfilled ticket
     int held[KVM_NCLASS] = {-1, -1, -1, -1};
+
     int cont = -1;             // continuation ready to be staged
     bool stop = false;
     unsigned polls = 0;
@@ -249,7 +297,9 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       // 1. a finished task?
       if (inflight > 0 && kvm_ld_volatile_shared(&slots[drain].state) == 2) {
         __syncwarp();
-        const int c2 = kvm_finish_task(S, slots[drain].desc, slots[drain].task, cont < 0 && ticket < 0 && !stop);
+        const int32_t* dd = slots[drain].desc;
+        const bool wc = cont < 0 && ticket < 0 && !stop;
+        const int c2 = kvm_finish_task(S, slots[drain].task, dd[1], dd[2], dd[10], dd[11], wc);
         if (c2 >= 0) cont = c2;
         __syncwarp();
         if (lane == 0) slots[drain].state = 0;
@@ -268,11 +318,13 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         }
         if (task >= 0) {
           KvmSlot& sl = slots[fill];
-          if (lane < 16) sl.desc[lane] = ((const int32_t*)&S.tasks[task])[lane];
-          __syncwarp();
-          const int ao = sl.desc[6], aw = sl.desc[7];
-          if (lane < aw && lane < KVM_MAX_ARGS) sl.args[lane] = S.args[ao + lane];
-          if (lane == 31) { sl.task = task; sl.aux = S.task_aux ? S.task_aux[task] : make_int4(0, 0, 0, 0); }
+          {   // one fetch: the task's record holds descriptor, argument words and path selector side by side
+            const int32_t* rec = S.recs + (size_t)task * KVM_REC_WORDS;
+            const int32_t w0 = rec[lane], w1 = lane < 8 ? rec[32 + lane] : 0;
+            if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
+            if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
+            if (lane == 31) sl.task = task;
+          }
           __threadfence();       // gpu scope: the predecessors' data must be visible to this CTA's compute group
           __syncwarp();
           if (lane == 0) sl.state = 1;

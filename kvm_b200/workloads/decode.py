@@ -39,15 +39,16 @@ class DecodeConfig:
     seed: int = 0
     rows_per_task: int = 64  # weight rows per gemv task; 0 = balance every phase over `workers` SMs
     workers: int = 148
+    join_threshold: int = 24  # fan-ins wider than this go through a join no-op (fewer edges, one more hop)
 
 
 PRESETS = {
     'decode_tiny': DecodeConfig(),
     # BASELINE config 5 (Qwen3-8B shape), 4K context
     'qwen3_8b': DecodeConfig(name='qwen3_8b', layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                             splits=16, rows_per_task=0),
+                             splits=16, rows_per_task=0, join_threshold=1000),
     'qwen3_8b_4l': DecodeConfig(name='qwen3_8b_4l', layers=4, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                                splits=16, rows_per_task=0),
+                                splits=16, rows_per_task=0, join_threshold=1000),
 }
 
 
@@ -67,6 +68,7 @@ def kv_bytes(c: DecodeConfig, ctx: int) -> int:
 
 def build_decode(c: DecodeConfig) -> Graph:
     g = Graph('decode')
+    g.join_threshold = c.join_threshold
     d, H, Hkv, hd, F, V, B, S = c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.batch, c.splits
     seeded = lambda name, scale=None: {'kind': 'seeded', 'seed': zlib.crc32(f'{c.seed}/{name}'.encode()), 'scale': scale or c.init_std, 'dist': 'normal'}
 

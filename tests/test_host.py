@@ -154,3 +154,41 @@ def test_flat_chunks_never_overlap():
         regs = [g.region_of(buf, *c) for c in ch]
         for (r0, c0), (r1, c1) in zip(regs, regs[1:]):
             assert r0[1] <= r1[0] or (r0 == r1 and c0[1] <= c1[0])
+
+
+def test_mlp_graph_components_and_oracle_loss_falls():
+    """The multi-MLP graph: one connected component per model (the shared input batches are only read), and on the oracle the
+    momentum-SGD steps lower each model's loss."""
+    from kvm_b200.workloads.mlp import build_mlps, preset
+    from oracle.vm_np import VM
+    c = preset('mlp_small')
+    b = build_mlps(c, 6).to_bundle()
+    validate(b)
+    nt = len(b.tasks)
+    parent = list(range(nt))
+
+    def find(x):
+        while parent[x] != x:
+            parent[x] = parent[parent[x]]
+            x = parent[x]
+        return x
+    for t in range(nt):
+        o, n = int(b.tasks['succ_off'][t]), int(b.tasks['succ_cnt'][t])
+        for s in b.succ[o:o + n]:
+            parent[find(t)] = find(int(s))
+    assert len({find(t) for t in range(nt)}) == len(c.widths)
+    vm = VM(b).run()
+    for mi in range(len(c.widths)):
+        losses = [float(vm.buffer(f'm{mi}.loss.{s}').a[0, 0]) for s in range(6)]
+        assert losses[-1] < losses[0], losses
+
+
+def test_decode_phases_fit_whole_waves():
+    """Balanced decode graph: the GEMV tasks of every concurrent phase of a layer fit the SM count (no straggler wave)."""
+    from kvm_b200.workloads.decode import build_decode, preset
+    import collections
+    c = preset('qwen3_8b', layers=1, vocab=4096)
+    names = build_decode(c).to_bundle(check=False).metadata['task_names']
+    cnt = collections.Counter(n.split('.')[2] for n in names if '.l0.' in n and 'join' not in n)
+    assert cnt['q'] + cnt['k'] + cnt['v'] <= c.workers and cnt['gate'] + cnt['up'] <= c.workers and cnt['o'] <= c.workers and cnt['down'] <= c.workers
+    assert cnt['part'] == c.kv_heads * c.splits and cnt['merge'] == c.kv_heads
