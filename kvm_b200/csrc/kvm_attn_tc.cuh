@@ -13,8 +13,6 @@
 #pragma once
 #include "kvm_gemm_tc.cuh"
 
-#define KVM_CTL_ABAR 9          // attention barriers: indices 9.. in the ctl barrier array
-#define KVM_CTL_ACNT 64         // completed-phase counts of the attention barriers (ints)
 #define KVM_ATT_NBAR 12
 
 __device__ __forceinline__ float kvm_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }

@@ -46,6 +46,7 @@ struct KvmCtx {
   int cfg_flags;
   int* ctl;                   // executor control words in shared memory (ctl[0] = TMEM base address)
   const void* tmaps;          // tensor-map table of the tensor-core tasks
+  int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
 
   // First error wins (reference: mvm_fail, include/mvm_exec.cuh:260-266). Every thread may call it with the same arguments.
   __device__ void fail(int code, int a = 0, int b = 0) const {

@@ -3,6 +3,7 @@
 // (deduplicated per GEMM) and mark the task for the tcgen05 path; everything else keeps the SIMT path.
 #include <map>
 #include <tuple>
+#include <vector>
 
 typedef CUresult (*KvmEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -86,6 +87,34 @@ static int kvm_plan_tc(KvmExec* h, int first_task) {
     const int ib = tb ? kvm_tmap_bf16(h, cache, B.p, K, N, B.ld, 64, 256) : kvm_tmap_bf16(h, cache, B.p, N, K, B.ld, 64, 64);
     if (ia < 0 || ib < 0) continue;
     h->aux[i] = make_int4(1, ia, ib, 0);
+  }
+  // Partner tiles: two tensor-core tiles of the same product whose rows start at m0 (a multiple of 256) and m0 + 128 and that
+  // wait for no version; each records the other (index + 1) in word 3 of its path selector, the workers may then run them
+  // stacked as one 256 x 256 tile.
+  if (!(h->cfg.flags & KVM_CFG_NO_PAIRING)) {
+    std::map<std::vector<int32_t>, int> even;
+    auto key_of = [&](size_t i, int m0) {
+      const int32_t* a = h->args.data() + h->tasks[i].args_off;
+      std::vector<int32_t> k(a, a + 13);
+      k[6] = m0;
+      return k;
+    };
+    for (size_t i = first_task; i < h->tasks.size(); ++i) {
+      const KvmTaskDesc& d = h->tasks[i];
+      if (d.op_id != 122 || h->aux[i].x != 1 || d.wait_var >= 0 || d.args_words < 13) continue;
+      const int m0 = (h->args.data() + d.args_off)[6];
+      if ((m0 & 255) == 0) even[key_of(i, m0)] = (int)i;
+    }
+    for (size_t i = first_task; i < h->tasks.size(); ++i) {
+      const KvmTaskDesc& d = h->tasks[i];
+      if (d.op_id != 122 || h->aux[i].x != 1 || d.wait_var >= 0 || d.args_words < 13) continue;
+      const int32_t* a = h->args.data() + d.args_off;
+      if ((a[6] & 255) != 128) continue;
+      auto it = even.find(key_of(i, a[6] - 128));
+      if (it == even.end() || h->aux[it->second].w != 0) continue;
+      h->aux[i].w = it->second + 1;
+      h->aux[it->second].w = (int)i + 1;
+    }
   }
   return 0;
 }

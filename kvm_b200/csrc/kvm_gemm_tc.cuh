@@ -32,6 +32,8 @@
 #define KVM_CTL_MMA_IT 2
 #define KVM_CTL_ACC_PH 3
 #define KVM_CTL_BAR 8          // 8-byte aligned: full[4], empty[4], acc_full at ctl[8 + 2*i]
+#define KVM_CTL_ABAR 9          // second barrier set (attention, paired GEMM tiles): indices 9.. in the ctl barrier array
+#define KVM_CTL_ACNT 64         // completed-phase counts of the second set (ints)
 
 __device__ __forceinline__ uint32_t kvm_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t kvm_bar_addr(int* ctl, int i) { return kvm_smem_addr(ctl + KVM_CTL_BAR + 2 * i); }
@@ -143,11 +145,99 @@ __device__ __forceinline__ void kvm_tc_store32(const KvmMmArgs& g, const float (
   }
 }
 
+// Two stacked tiles (rows m0.. and m0+128.., same 256 columns) as one 256 x 256 product: both read the same B stage, so a
+// k-block moves 64 KB for two tiles instead of 96 KB, which is what the L2 -> shared-memory path of an SM can feed.
+// Three 64 KB stages [A0 16K | A1 16K | B 32K]; two float32 accumulators in TMEM (columns 0..255 and 256..511).
+// Barriers: the attention set (full 0..2, empty 3..5, accumulator 6) with their completed-phase counts in ctl[KVM_CTL_ACNT + i].
+#define KVM_TCP_STAGES 3
+#define KVM_TCP_STAGE_BYTES (2 * KVM_TC_A_BYTES + KVM_TC_B_BYTES)
+__device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const int4& aux) {
+  int* ctl = c.ctl;
+  int* cnt = ctl + KVM_CTL_ACNT;
+  auto bar = [&](int i) { return kvm_bar_addr(ctl, KVM_CTL_ABAR + i); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool ta = g.flags & 1, tb = g.flags & 2;
+  const int num_kb = (g.K + KVM_TC_BK - 1) / KVM_TC_BK;
+  const uint32_t stage0 = kvm_smem_addr(c.smem);
+  const char* tmA = (const char*)c.tmaps + (size_t)aux.y * 128;
+  const char* tmB = (const char*)c.tmaps + (size_t)aux.z * 128;
+  kvm_tc_fence_after();
+  const uint32_t tmem = *(volatile uint32_t*)(ctl + KVM_CTL_TMEM);
+  const int cA = cnt[6];
+  bool ok = true;
+  asm volatile("fence.proxy.async;" ::: "memory");
+  if (warp == 0 && lane == 0) {                         // ---- TMA producer
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % KVM_TCP_STAGES, u = kb / KVM_TCP_STAGES;
+      if (u > 0 && !kvm_mbar_wait(bar(3 + s), (uint32_t)(cnt[3 + s] + u - 1) & 1)) { ok = false; break; }
+      const uint32_t full = bar(s), sa = stage0 + s * KVM_TCP_STAGE_BYTES, sb = sa + 2 * KVM_TC_A_BYTES;
+      kvm_mbar_expect_tx(full, KVM_TCP_STAGE_BYTES);
+      const int k0 = kb * KVM_TC_BK;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int m0 = g.m0 + t * 128;
+        const uint32_t st = sa + t * KVM_TC_A_BYTES;
+        if (!ta) kvm_tma_load_2d(st, tmA, k0, m0, full);
+        else { kvm_tma_load_2d(st, tmA, m0, k0, full); kvm_tma_load_2d(st + 8192, tmA, m0 + 64, k0, full); }
+      }
+      if (tb) kvm_tma_load_2d(sb, tmB, k0, g.n0, full);
+      else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) kvm_tma_load_2d(sb + i * 8192, tmB, g.n0 + 64 * i, k0, full);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {                  // ---- MMA issuer
+    const uint32_t idesc = kvm_idesc_bf16(128, 256, ta, !tb);
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % KVM_TCP_STAGES, u = kb / KVM_TCP_STAGES;
+      if (!kvm_mbar_wait(bar(s), (uint32_t)(cnt[s] + u) & 1)) { ok = false; break; }
+      kvm_tc_fence_after();
+      const uint32_t sa = stage0 + s * KVM_TCP_STAGE_BYTES, sb = sa + 2 * KVM_TC_A_BYTES;
+#pragma unroll
+      for (int j = 0; j < KVM_TC_BK / 16; ++j) {
+        const uint64_t db = tb ? kvm_smem_desc(sb + j * 32, 16, 1024) : kvm_smem_desc(sb + j * 2048, 8192, 1024);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const uint32_t st = sa + t * KVM_TC_A_BYTES;
+          const uint64_t da = ta ? kvm_smem_desc(st + j * 2048, 8192, 1024) : kvm_smem_desc(st + j * 32, 16, 1024);
+          kvm_tc_mma_bf16(tmem + t * 256, da, db, idesc, (kb | j) ? 1u : 0u);
+        }
+      }
+      kvm_tc_commit(bar(3 + s));
+    }
+    kvm_tc_commit(bar(6));
+  }
+  __syncwarp();
+  if (!kvm_mbar_wait(bar(6), (uint32_t)cA & 1)) ok = false;
+  kvm_tc_fence_after();
+  if (!ok && atomicCAS(&c.err->code, 0, KVM_ERR_TIMEOUT) == 0) { c.err->task = c.task; c.err->a = 1122; c.err->b = (int)threadIdx.x; }
+  const int q = warp & 3, cgi = warp >> 2;
+#pragma unroll 1
+  for (int t = 0; t < 2; ++t) {
+    const int m = g.m0 + t * 128 + q * 32 + lane;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = cgi * 64 + h * 32;
+      float acc[32];
+      kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 256 + col), acc);
+      if (ok && m < g.M) kvm_tc_store32(g, acc, m, g.n0 + col);
+    }
+  }
+  kvm_tc_fence_before();
+  kvm_sync();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < KVM_TCP_STAGES; ++s) { const int uses = (num_kb - s + KVM_TCP_STAGES - 1) / KVM_TCP_STAGES; cnt[s] += uses; cnt[3 + s] += uses; }
+    cnt[6] = cA + 1;
+  }
+}
+
 // aux.x = 1: tensor-core path planned by the host (aux.y / aux.z = tensor-map indices of A / B); else SIMT fallback.
 __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmMmArgs g;
   if (!kvm_mm_args(c, a, 2, g)) return;
   if (aux.x != 1 || (c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) { kvm_mm_simt(c, g); return; }
+  if (c.pair >= 0) { g.m0 &= ~255; kvm_mm_tc_pair(c, g, aux); return; }       // this task and its partner: rows m0.. and m0+128..
   int* ctl = c.ctl;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool ta = g.flags & 1, tb = g.flags & 2;

@@ -25,7 +25,7 @@ struct KvmExec {
   std::vector<CUtensorMap> tmaps;
   bool tasks_dirty = true;
   KvmTaskDesc* d_tasks = nullptr; int32_t* d_succ = nullptr; int32_t* d_args = nullptr; int4* d_aux = nullptr; void* d_tmaps = nullptr; int32_t* d_recs = nullptr;
-  int *d_indeg = nullptr, *d_exec = nullptr, *d_ring = nullptr, *d_park_next = nullptr, *d_tsmid = nullptr;
+  int *d_indeg = nullptr, *d_exec = nullptr, *d_ring = nullptr, *d_park_next = nullptr, *d_tsmid = nullptr, *d_claim = nullptr;
   unsigned long long *d_tstart = nullptr, *d_tend = nullptr;
   size_t task_cap = 0;
   // control words
@@ -33,15 +33,16 @@ struct KvmExec {
   int* d_versions = nullptr; int* d_park_head = nullptr; int* d_ver_base = nullptr; int* d_ver_off = nullptr;
   KvmErrRec* d_err = nullptr;
   bool started = false, armed = false;
+  bool has_stream_ops = false;   // a submitted task is a gemv_bf16 / attn_decode_part (look-ahead prefetch pays only for those)
   KvmResult last{};
 };
 
 static void kvm_free_tasks(KvmExec* h) {
   for (void* p : {(void*)h->d_tasks, (void*)h->d_succ, (void*)h->d_args, (void*)h->d_aux, (void*)h->d_tmaps, (void*)h->d_indeg, (void*)h->d_exec, (void*)h->d_ring,
-                  (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend, (void*)h->d_recs})
+                  (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend, (void*)h->d_recs, (void*)h->d_claim})
     if (p) cudaFree(p);
   h->d_tasks = nullptr; h->d_succ = nullptr; h->d_args = nullptr; h->d_aux = nullptr; h->d_tmaps = nullptr; h->d_indeg = h->d_exec = h->d_ring = h->d_park_next = h->d_tsmid = nullptr;
-  h->d_tstart = h->d_tend = nullptr; h->d_recs = nullptr; h->task_cap = 0;
+  h->d_tstart = h->d_tend = nullptr; h->d_recs = nullptr; h->d_claim = nullptr; h->task_cap = 0;
 }
 
 extern "C" const char* kvm_err_name(int32_t code) {
@@ -305,7 +306,8 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.t_start = h->d_tstart; S.t_end = h->d_tend; S.t_smid = h->d_tsmid; S.trace = h->cfg.trace;
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
   S.cfg_flags = h->cfg.flags;
-  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs;
+  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim;
+  S.prefetch = (h->has_stream_ops && !(h->cfg.flags & KVM_CFG_NO_PREFETCH)) ? 1 : 0;
   return S;
 }
 
@@ -330,17 +332,19 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     KVM_CUDA(cudaMalloc(&h->d_args, (h->args.size() + 1) * 4));
     KVM_CUDA(cudaMalloc(&h->d_aux, nt * sizeof(int4)));
     KVM_CUDA(cudaMalloc(&h->d_tmaps, (h->tmaps.size() + 1) * sizeof(CUtensorMap)));
-    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4));
+    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_claim, nt * 4));
     if (h->cfg.trace) { KVM_CUDA(cudaMalloc(&h->d_tstart, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tend, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tsmid, nt * 4)); }
     KVM_CUDA(cudaMemcpyAsync(h->d_tasks, h->tasks.data(), nt * sizeof(KvmTaskDesc), cudaMemcpyHostToDevice, h->stream));
     if (!h->succ.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_succ, h->succ.data(), h->succ.size() * 4, cudaMemcpyHostToDevice, h->stream));
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
+    h->has_stream_ops = false;
     {   // one record per task for the workers: descriptor, argument words and path selector side by side (a single fetch per pop)
       std::vector<int32_t> recs(nt * (size_t)KVM_REC_WORDS, 0);
       for (size_t i = 0; i < nt; ++i) {
         int32_t* r = &recs[i * KVM_REC_WORDS];
         memcpy(r, &h->tasks[i], sizeof(KvmTaskDesc));
+        if (r[0] == 134 || r[0] == 135) h->has_stream_ops = true;
         const int ao = r[6], aw = r[7] < KVM_MAX_ARGS ? r[7] : KVM_MAX_ARGS;
         for (int k = 0; k < aw; ++k) r[16 + k] = h->args[(size_t)ao + k];
         memcpy(r + 16 + KVM_MAX_ARGS, &h->aux[i], sizeof(int4));

@@ -45,13 +45,16 @@ struct KvmDevState {
   const void* tmaps;          // CUtensorMap table for tensor-core tasks
   const int4* task_aux;       // per task: tensor-map indices / path selector
   const int32_t* recs;        // per task KVM_REC_WORDS words: descriptor [0,16), argument words [16,36), path selector [36,40)
+  int prefetch;               // 1: a finishing task prefetches one of its successors' streamed operands into L2
+  int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
 };
 #define KVM_REC_WORDS 48
 
 struct KvmSlot {
   int task;                   // -1 = leave
   int state;                  // 0 free, 1 full, 2 finished (awaiting release)
-  int pad[2];
+  int pair;                   // partner task run together with `task` (stacked GEMM tiles), or -1
+  int pad;
   int32_t desc[16];
   int32_t args[KVM_MAX_ARGS];
   int4 aux;
@@ -168,6 +171,7 @@ __global__ void kvm_arm_kernel(KvmDevState S) {
   if (i < S.nt) {
     S.indeg[i] = S.tasks[i].indegree;
     S.exec_count[i] = 0;
+    S.claim[i] = 0;
 #pragma unroll
     for (int c = 0; c < KVM_NCLASS; ++c) S.ring[(size_t)c * S.nt + i] = 0;
     S.park_next[i] = -1;
@@ -267,6 +271,67 @@ __device__ int kvm_finish_task(const KvmDevState& S, int task, int so, int sc, i
   if (lane == 0) atomicAdd(S.done, 1);
   return cont;
 }
+// ---- look-ahead for the weight-streaming decode ops ------------------------------------------------------------------------------
+// A decode step is a chain of short phases, each streaming its own weights once; between two phases HBM would sit idle while
+// the last tasks finish and the next ones are released and staged.  A worker that has just finished a task therefore asks the
+// memory system for what one task of the NEXT phase is going to stream (gemv_bf16: its weight rows; attn_decode_part: its
+// slice of the key / value cache), up to KVM_PF_BYTES, with L2 prefetches - nothing is copied, no result depends on it.
+// Which successor: entry (task mod workers) of the successor list, then every workers-th one: tasks of one phase carry
+// consecutive indices and share one successor list, so the phase covers the next one evenly.  A successor that streams nothing
+// (a merge, a join) is looked through once.  All lanes run this with the same values; lanes split the ranges.
+#define KVM_PF_BYTES (384 * 1024)
+#define KVM_PF_PIECE 16384
+__device__ __forceinline__ void kvm_prefetch_range(const char* p, long long bytes) {
+  const int lane = threadIdx.x & 31;
+  if (bytes > KVM_PF_BYTES) bytes = KVM_PF_BYTES;
+  const long long lead = (long long)((16 - ((uintptr_t)p & 15)) & 15);      // whole 16-byte units inside [p, p + bytes)
+  p += lead;
+  bytes = (bytes - lead) & ~15ll;
+  for (long long o = (long long)lane * KVM_PF_PIECE; o < bytes; o += 32ll * KVM_PF_PIECE) {
+    const unsigned n = (unsigned)min((long long)KVM_PF_PIECE, bytes - o);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + o), "r"(n) : "memory");
+  }
+}
+__device__ void kvm_prefetch_task(const KvmDevState& S, int t) {
+  const int32_t* rec = S.recs + (size_t)t * KVM_REC_WORDS;
+  const int op = rec[0];
+  const int32_t* a = rec + 16;
+  if (op == 134) {                                   // gemv_bf16: w = a[3], rows [a[6], a[7])
+    const int wi = a[3], n0 = a[6], n1 = a[7];
+    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0) return;
+    const KvmBuf w = S.bufs[wi];
+    if (!w.p || n1 > w.rows || w.dtype != KVM_BF16) return;
+    kvm_prefetch_range((const char*)w.p + (size_t)n0 * w.ld * 2, ((long long)(n1 - n0 - 1) * w.ld + w.cols) * 2);
+  } else if (op == 135) {                            // attn_decode_part: kc = a[1], vc = a[2], lens = a[3], b a[7], kvh a[8], s a[9], S a[10], Hkv a[12], Tmax a[14]
+    const int ki = a[1], vi = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], SS = a[10], Hkv = a[12], Tmax = a[14];
+    if (ki < 0 || ki >= S.nbufs || vi < 0 || vi >= S.nbufs || li < 0 || li >= S.nbufs || b < 0 || SS <= 0 || s < 0 || Hkv <= 0 || kvh < 0 || Tmax <= 0) return;
+    const KvmBuf kc = S.bufs[ki], vc = S.bufs[vi], lens = S.bufs[li];
+    if (!kc.p || !vc.p || !lens.p || lens.dtype != KVM_I32 || kc.dtype == KVM_I32 || vc.dtype == KVM_I32 || (long long)b >= (long long)lens.rows * lens.cols) return;
+    const int n = ((const volatile int*)lens.p)[b] + 1;
+    if (n <= 0 || n > Tmax) return;
+    const int chunk = (n + SS - 1) / SS, j0 = s * chunk, j1 = min(n, j0 + chunk);
+    const long long row0 = (long long)(b * Hkv + kvh) * Tmax + j0;
+    if (j1 <= j0 || row0 + (j1 - j0) > kc.rows || row0 + (j1 - j0) > vc.rows) return;
+    const int ek = kc.dtype == KVM_BF16 ? 2 : 4, ev = vc.dtype == KVM_BF16 ? 2 : 4;
+    kvm_prefetch_range((const char*)kc.p + (size_t)row0 * kc.ld * ek, ((long long)(j1 - j0 - 1) * kc.ld + kc.cols) * ek);
+    kvm_prefetch_range((const char*)vc.p + (size_t)row0 * vc.ld * ev, ((long long)(j1 - j0 - 1) * vc.ld + vc.cols) * ev);
+  }
+}
+__device__ void kvm_prefetch_next(const KvmDevState& S, int task, int so, int sc) {
+  const int W = (int)gridDim.x;
+  for (int k = task % W, n = 0; k < sc && n < 8; k += W, ++n) {
+    int t = S.succ[so + k];
+    const int32_t* rec = S.recs + (size_t)t * KVM_REC_WORDS;
+    const int op = rec[0];
+    if (op != 134 && op != 135) {                    // look through one non-streaming successor
+      const int so2 = rec[1], sc2 = rec[2], k2 = task % W;
+      if (k2 >= sc2) continue;
+      t = S.succ[so2 + k2];
+    }
+    kvm_prefetch_task(S, t);
+  }
+}
+
 __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S) {
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
   KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
@@ -301,6 +366,14 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         const bool wc = cont < 0 && ticket < 0 && !stop;
         const int c2 = kvm_finish_task(S, slots[drain].task, dd[1], dd[2], dd[10], dd[11], wc);
         if (c2 >= 0) cont = c2;
+        if (S.prefetch) kvm_prefetch_next(S, slots[drain].task, dd[1], dd[2]);
+        const int pr = slots[drain].pair;
+        if (pr >= 0) {                                       // the partner tile finished with it
+          const int32_t w = lane < 16 ? ((const int32_t*)&S.tasks[pr])[lane] : 0;
+          const int c4 = kvm_finish_task(S, pr, __shfl_sync(0xffffffffu, w, 1), __shfl_sync(0xffffffffu, w, 2), __shfl_sync(0xffffffffu, w, 10),
+                                         __shfl_sync(0xffffffffu, w, 11), wc && cont < 0);
+          if (c4 >= 0) cont = c4;
+        }
         __syncwarp();
         if (lane == 0) slots[drain].state = 0;
         __syncwarp();
@@ -317,14 +390,30 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
           ticket = __shfl_sync(0xffffffffu, hold, 0) ? 0 : -1;      // ticket >= 0 now only means: this worker holds a ticket (no continuation then)
         }
         if (task >= 0) {
-          KvmSlot& sl = slots[fill];
-          {   // one fetch: the task's record holds descriptor, argument words and path selector side by side
-            const int32_t* rec = S.recs + (size_t)task * KVM_REC_WORDS;
-            const int32_t w0 = rec[lane], w1 = lane < 8 ? rec[32 + lane] : 0;
-            if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
-            if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
-            if (lane == 31) sl.task = task;
+          // one fetch: the task's record holds descriptor, argument words and path selector side by side
+          const int32_t* rec = S.recs + (size_t)task * KVM_REC_WORDS;
+          const int32_t w0 = rec[lane], w1 = lane < 8 ? rec[32 + lane] : 0;
+          // Stacked GEMM tiles: a tensor-core tile whose partner (same product, rows 128 further or nearer; path selector word 3)
+          // is ready too is run together with it as one 256 x 256 tile.  Either ticket may come first: whoever takes a tile's
+          // claim word runs it; a ticket whose tile is already taken is dropped.
+          int pair = -1;
+          bool drop = false;
+          const int ax = __shfl_sync(0xffffffffu, w1, 4), aw = __shfl_sync(0xffffffffu, w1, 7);
+          if (ax == 1 && aw > 0) {
+            int v = 0;
+            if (lane == 0) {
+              if (atomicCAS(&S.claim[task], 0, 1) != 0) v = -2;
+              else if (kvm_ld_acquire(&S.indeg[aw - 1]) == 0 && atomicCAS(&S.claim[aw - 1], 0, 1) == 0) v = aw;
+            }
+            v = __shfl_sync(0xffffffffu, v, 0);
+            drop = v == -2;
+            pair = v > 0 ? v - 1 : -1;
           }
+          if (drop) { progressed = true; continue; }
+          KvmSlot& sl = slots[fill];
+          if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
+          if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
+          if (lane == 31) { sl.task = task; sl.pair = pair; }
           __threadfence();       // gpu scope: the predecessors' data must be visible to this CTA's compute group
           __syncwarp();
           if (lane == 0) sl.state = 1;
@@ -368,12 +457,16 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       if (kvm_ld_volatile_shared(&sl.state) != 1) break;
       const int task = sl.task;
       if (task < 0) break;
-      c.task = task;
+      c.task = task; c.pair = sl.pair;
       if (tid == 0) {
         if (atomicAdd(&S.exec_count[task], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, task);
+        if (c.pair >= 0 && atomicAdd(&S.exec_count[c.pair], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, c.pair);
         const int wv = sl.desc[8];
         if (wv >= 0 && wv < S.nvars && kvm_ld_acquire(&S.versions[wv]) < sl.desc[9] + S.ver_off[wv]) kvm_dev_fail(S, KVM_ERR_WAIT_VIOLATION, task, wv);
-        if (S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
+        if (S.trace) {
+          S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid();
+          if (c.pair >= 0) { S.t_start[c.pair] = S.t_start[task]; S.t_smid[c.pair] = S.t_smid[task]; }
+        }
       }
       const int op = sl.desc[0];
       if (op != 0 && *(volatile int*)&S.err->code == 0) kvm_dispatch(c, op, sl.args, sl.aux);
@@ -382,7 +475,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       __threadfence();
       kvm_sync();
       if (tid == 0) {
-        if (S.trace) S.t_end[task] = kvm_globaltimer();
+        if (S.trace) { S.t_end[task] = kvm_globaltimer(); if (c.pair >= 0) S.t_end[c.pair] = S.t_end[task]; }
         __threadfence();
         sl.state = 2;
       }
