@@ -37,6 +37,15 @@ struct KvmExec {
   KvmResult last{};
 };
 
+// Default of the two newest scheduler features; the environment variables KVM_B200_PREFETCH / KVM_B200_PAIRING (0 or 1)
+// override them for A/B measurements.
+#define KVM_DEFAULT_PREFETCH 0
+#define KVM_DEFAULT_PAIRING 0
+static bool kvm_feature_on(const char* env, int dflt) {
+  const char* v = getenv(env);
+  return v && *v ? atoi(v) != 0 : dflt != 0;
+}
+
 static void kvm_free_tasks(KvmExec* h) {
   for (void* p : {(void*)h->d_tasks, (void*)h->d_succ, (void*)h->d_args, (void*)h->d_aux, (void*)h->d_tmaps, (void*)h->d_indeg, (void*)h->d_exec, (void*)h->d_ring,
                   (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend, (void*)h->d_recs, (void*)h->d_claim})
@@ -307,7 +316,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
   S.cfg_flags = h->cfg.flags;
   S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim;
-  S.prefetch = (h->has_stream_ops && !(h->cfg.flags & KVM_CFG_NO_PREFETCH)) ? 1 : 0;
+  S.prefetch = (h->has_stream_ops && !(h->cfg.flags & KVM_CFG_NO_PREFETCH) && kvm_feature_on("KVM_B200_PREFETCH", KVM_DEFAULT_PREFETCH)) ? 1 : 0;
   return S;
 }
 
