@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
-"""Generate the golden fixtures of tests/golden/ from the reference tree (run where /root/reference is mounted):
+"""Generate the golden fixtures of tests/golden/ from a checkout of the reference (Bobliuuu/kvm):
 
-  python tests/golden/make_golden.py [/path/to/reference]
+  python tests/golden/make_golden.py /path/to/reference
 
   ops_golden.npz        for every on-path op: seeded inputs and the outputs of the reference's own pure-Python CPU ops
                         (runtime/ref_ops.py OPS), called directly, at sizes its scalar loops finish in seconds
@@ -24,7 +24,9 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else '/root/reference')
+if len(sys.argv) < 2:
+    sys.exit('usage: make_golden.py /path/to/reference')
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(REF / 'runtime'))
 
