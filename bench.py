@@ -270,6 +270,10 @@ def run_ours(args, rank, world, local_rank):
                 line['decode'] = run_decode(args, local_rank)
             except Exception as e:      # the training line stands on its own
                 line['decode'] = {'error': str(e)[:300]}
+            try:
+                line['kernels_alone'] = run_alone(local_rank)
+            except Exception as e:
+                line['kernels_alone'] = {'error': str(e)[:300]}
         if cpu:
             line['cpu_baseline'] = {'value': cpu['steps_per_s'], 'unit': 'steps/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
                                     'sample': f"{cpu['tasks']} of {cpu['of_tasks']} tasks of one step, a few of each of its {cpu['kinds']} op kinds, {cpu['seconds']:.1f} s on the numpy oracle; step time = sum over kinds of count x mean task time"}
@@ -359,7 +363,7 @@ def run_decode(args, device):
     from kvm_b200.executor import Executor
     from kvm_b200.workloads.decode import build_decode, kv_bytes, preset, weight_bytes
     cfg = preset(args.decode_model)
-    d = Path(tempfile.gettempdir()) / 'kvm_b200_bundles' / f'decode-{args.decode_model}-b{cfg.batch}'
+    d = Path(tempfile.gettempdir()) / 'kvm_b200_bundles' / f'decode-{args.decode_model}-b{cfg.batch}-s{cfg.splits}-r{cfg.rows_per_task}-j{cfg.join_threshold}'
     from kvm_b200.bundle import load_bundle
     if (d / 'metadata.json').exists():
         bundle = load_bundle(d)
@@ -391,6 +395,49 @@ def run_decode(args, device):
            'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'unit': 'GB/s', 'frac': gbs / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
                         'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0])}
     ex.close()
+    return out
+
+
+def run_alone(device):
+    """The two dominant op kinds timed alone through the executor (a graph of nothing but independent tasks of that kind, inputs
+    larger than L2), to read beside the whole-step numbers: tensor-core GEMM tiles of the three K depths a GPT-162M step has, and
+    the streaming GEMV over an LM-head sized weight matrix."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.graph import Graph
+    pk, kind = peaks()
+    out = {}
+    sd = lambda n, sc: {'kind': 'seeded', 'seed': n, 'scale': sc, 'dist': 'normal'}
+    for name, (M, N, K, flags, reps) in {'gemm_fwd_k768': (8192, 3072, 768, 0, 6), 'gemm_fwd_k3072': (8192, 768, 3072, 0, 8), 'gemm_wgrad_k8192': (3072, 768, 8192, 1, 16)}.items():
+        g = Graph('alone')
+        for r in range(reps):                 # independent products: operands of their own, so nothing is re-read from L2 by design
+            a = g.buffer(f'a{r}', *((K, M) if flags & 1 else (M, K)), 'bf16', sd(3 * r + 1, 1.0))
+            b = g.buffer(f'b{r}', K, N, 'bf16', sd(3 * r + 2, 0.02))
+            o = g.buffer(f'o{r}', M, N, 'bf16')
+            for m0 in range(0, M, 128):
+                for n0 in range(0, N, 256):
+                    g.task('matmul_mma_bf16', {'a': a, 'b': b, 'out': o, 'bias': None, 'res': None, 'pre': None, 'm0': m0, 'n0': n0, 'M': M, 'N': N, 'K': K, 'flags': flags,
+                                               'alpha': 1.0}, [], [(o, (m0, min(m0 + 128, M)), (n0, min(n0 + 256, N)))], 5, f'{r}.{m0}.{n0}')
+        bundle = g.to_bundle(check=False)
+        with Executor(device=device) as ex:
+            ex.load(bundle); ex.run()
+            ms = min(ex.run().ms for _ in range(3))
+        tf = 2.0 * M * N * K * reps / (ms * 1e-3) / 1e12
+        peak = pk.get('bf16_tflops_sustained', PEAK_FALLBACK['bf16_tflops_sustained'])
+        out[name] = {'shape': [M, N, K], 'tiles': len(bundle.tasks), 'ms': ms, 'achieved': tf, 'unit': 'TFLOP/s', 'peak': peak, 'frac': tf / peak, 'bound': 'tensor'}
+    g = Graph('alone')
+    rows, K, ntask = 256, 4096, 148 * 4
+    w = g.buffer('w', rows * ntask, K, 'bf16', sd(1, 0.02)); x = g.buffer('x', 1, K, init=sd(2, 1.0)); o = g.buffer('o', 1, rows * ntask)
+    for i in range(ntask):
+        g.task('gemv_bf16', {'x': x, 'x2': None, 'gamma': None, 'w': w, 'out': o, 'res': None, 'n0': i * rows, 'n1': (i + 1) * rows, 'K': K, 'pro': 0, 'eps': 1e-6},
+               [x, (w, (i * rows, (i + 1) * rows))], [(o, (0, 1), (i * rows, (i + 1) * rows))], 5, f't{i}')
+    bundle = g.to_bundle(check=False)
+    with Executor(device=device) as ex:
+        ex.load(bundle); ex.run()
+        ms = min(ex.run().ms for _ in range(3))
+    gbs = rows * ntask * K * 2 / (ms * 1e-3) / 1e9
+    peak = pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])
+    out['gemv_k4096'] = {'shape': [rows * ntask, K], 'tasks': ntask, 'ms': ms, 'achieved': gbs, 'unit': 'GB/s', 'peak': peak, 'frac': gbs / peak, 'bound': 'hbm'}
+    out['note'] = f'whole launches (about 17 us of launch, arming and shutdown included); peaks: {kind}'
     return out
 
 

@@ -40,8 +40,7 @@ typedef struct KvmConfig {
     int32_t flags;         /* KVM_CFG_* */
 } KvmConfig;
 enum { KVM_CFG_NO_TENSOR_CORES = 1, /* run every GEMM on the SIMT reference path (debugging / bit-exact f32) */
-       KVM_CFG_NO_PREFETCH = 2,     /* do not prefetch the next decode tasks' weights / cache rows into L2 when a task finishes */
-       KVM_CFG_NO_PAIRING = 4       /* never run two stacked tensor-core GEMM tiles as one 256 x 256 tile */ };
+       KVM_CFG_PAIR_TILES = 2       /* run two row-adjacent tensor-core GEMM tiles of one product as one 256 x 256 tile when both are ready */ };
 
 /* Buffer initial value (mvm_exec.cu:1915-1929 buffer init kinds; `file` inits are read by the caller and passed as VALUES). */
 typedef struct KvmInit {

@@ -89,7 +89,21 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
   __syncwarp();
 
   // ---- prologue: v = bf16(pro(x)) as floats in shared memory (all 16 warps)
-  if (pro == 1) {
+  if (pro == 1 && K <= 16 * KVM_NT) {           // x and gamma fetched together and kept in registers over the block sum
+    float xr[16], gr[16], q = 0.0f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int k = tid + u * KVM_NT;
+      xr[u] = k < K ? kvm_ld(x, k) : 0.0f;
+      gr[u] = k < K ? ((const float*)gm.p)[k] : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < 16; ++u) q += xr[u] * xr[u];
+    q = kvm_block_sum(q, red);
+    const float rs = 1.0f / sqrtf(q / K + eps);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) { const int k = tid + u * KVM_NT; if (k < K) vs[k] = kvm_bf16_round(xr[u] * rs * gr[u]); }
+  } else if (pro == 1) {
     float q = 0.0f;
     for (int k = tid; k < K; k += KVM_NT) { const float t = kvm_ld(x, k); vs[k] = t; q += t * t; }
     q = kvm_block_sum(q, red);
@@ -140,8 +154,7 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
 // Keys and values (bf16, rows contiguous: ld == hd) arrive as two bulk copies.  If `newrow` >= 0 that key is the one this task
 // appends: its rotated key / value (float, hd each, in knew / vnew shared arrays) is placed in the staged tiles by the threads
 // and the copies leave it out.
-//   scores   item = (key, half of the head dimension): adjacent lanes hold the halves of one key; 16-byte pieces are visited in
-//            an order rotated by the key index, so that lanes of a warp read different banks
+//   scores   hd/8 lanes per key, query columns in registers, shuffle sums (see below)
 //   softmax  over the whole split at once (warp g = query head g): p = exp(s - m) kept in shared memory as [key][8]
 //   PV       thread = (key group, column pair): all G heads share one read of V; key groups are summed in group order
 // emit(g, column, m, l, acc) as in kvm_decode_group.  Returns false when the split does not fit in shared memory.
@@ -156,7 +169,7 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
 template <int GT, class Pro, class Emit>
 __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
                                        Pro prologue, Emit emit) {
-  const int nk = max(j1 - j0, 0), ncp = hd >> 1, KQ = KVM_NT / ncp, nch = hd >> 3, hc = nch >> 1;
+  const int nk = max(j1 - j0, 0), ncp = hd >> 1, KQ = KVM_NT / ncp;
   const int off_sc = KVM_AS_OFF_SC, off_red = off_sc + ((nk + 3) & ~3) * 32, off_k = (off_red + KQ * G * hd * 4 + 127) & ~127;
   const int tile = (nk * hd * 2 + 127) & ~127;
   if (off_k + 2 * tile > c.smem_bytes) return false;
@@ -194,29 +207,29 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
   kvm_sync();
   if (!kvm_mbar_wait_t(barK, 0)) ok = false;
 
-  // ---- scores
-  for (int it0 = 0; it0 < 2 * nk; it0 += KVM_NT) {
-    const int item = it0 + tid, key = min(item >> 1, nk - 1), half = item & 1;
-    float s[GT];
+  // ---- scores: hd/8 lanes per key (each holds 8 columns of the queries in registers), a warp takes 32/(hd/8) consecutive keys per
+  //      step (one contiguous, conflict-free 512-byte read), partial dot products are summed over the lanes of a key by shuffles
+  {
+    const int LPK = hd >> 3, KPW = 32 / LPK, sub = lane / LPK, c0 = (lane % LPK) * 8;
+    float qr[GT][8];
 #pragma unroll
-    for (int g = 0; g < GT; ++g) s[g] = 0.0f;
-    const unsigned char* krow = Ks + (size_t)key * hd * 2;
-    for (int i = 0; i < hc; ++i) {
-      const int ch = half * hc + ((i + key + half * (hc >> 1)) % hc);
-      const uint4 kv = *(const uint4*)(krow + ch * 16);
+    for (int g = 0; g < GT; ++g) {
+      const float4 qa = g < G ? *(const float4*)(qs + g * hd + c0) : make_float4(0, 0, 0, 0), qb = g < G ? *(const float4*)(qs + g * hd + c0 + 4) : make_float4(0, 0, 0, 0);
+      qr[g][0] = qa.x; qr[g][1] = qa.y; qr[g][2] = qa.z; qr[g][3] = qa.w; qr[g][4] = qb.x; qr[g][5] = qb.y; qr[g][6] = qb.z; qr[g][7] = qb.w;
+    }
+    for (int key0 = warp * KPW; key0 < nk; key0 += KVM_NWARPS * KPW) {
+      const int key = key0 + sub, kk = min(key, nk - 1);
+      const uint4 kv = *(const uint4*)(Ks + (size_t)kk * hd * 2 + c0 * 2);
       const float k0 = kvm_bf16lo(kv.x), k1 = kvm_bf16hi(kv.x), k2 = kvm_bf16lo(kv.y), k3 = kvm_bf16hi(kv.y), k4 = kvm_bf16lo(kv.z), k5 = kvm_bf16hi(kv.z),
                   k6 = kvm_bf16lo(kv.w), k7 = kvm_bf16hi(kv.w);
 #pragma unroll
-      for (int g = 0; g < GT; ++g) if (g < G) {
-        const float4 qa = *(const float4*)(qs + g * hd + ch * 8), qb = *(const float4*)(qs + g * hd + ch * 8 + 4);
-        s[g] = fmaf(qa.x, k0, s[g]); s[g] = fmaf(qa.y, k1, s[g]); s[g] = fmaf(qa.z, k2, s[g]); s[g] = fmaf(qa.w, k3, s[g]);
-        s[g] = fmaf(qb.x, k4, s[g]); s[g] = fmaf(qb.y, k5, s[g]); s[g] = fmaf(qb.z, k6, s[g]); s[g] = fmaf(qb.w, k7, s[g]);
+      for (int g = 0; g < GT; ++g) {
+        float sg = qr[g][0] * k0;
+        sg = fmaf(qr[g][1], k1, sg); sg = fmaf(qr[g][2], k2, sg); sg = fmaf(qr[g][3], k3, sg); sg = fmaf(qr[g][4], k4, sg);
+        sg = fmaf(qr[g][5], k5, sg); sg = fmaf(qr[g][6], k6, sg); sg = fmaf(qr[g][7], k7, sg);
+        for (int o = LPK >> 1; o; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
+        if (g < G && key < nk && c0 == 0) ps[key * 8 + g] = sg * sc;
       }
-    }
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-      if (g < G && half == 0 && item < 2 * nk) ps[key * 8 + g] = s[g] * sc;
     }
   }
   kvm_sync();

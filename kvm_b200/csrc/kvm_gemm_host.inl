@@ -91,7 +91,7 @@ static int kvm_plan_tc(KvmExec* h, int first_task) {
   // Partner tiles: two tensor-core tiles of the same product whose rows start at m0 (a multiple of 256) and m0 + 128 and that
   // wait for no version; each records the other (index + 1) in word 3 of its path selector, the workers may then run them
   // stacked as one 256 x 256 tile.
-  if (!(h->cfg.flags & KVM_CFG_NO_PAIRING) && kvm_feature_on("KVM_B200_PAIRING", KVM_DEFAULT_PAIRING)) {
+  if (kvm_feature_on("KVM_B200_PAIRING", (h->cfg.flags & KVM_CFG_PAIR_TILES) ? 1 : 0)) {
     std::map<std::vector<int32_t>, int> even;
     auto key_of = [&](size_t i, int m0) {
       const int32_t* a = h->args.data() + h->tasks[i].args_off;

@@ -33,14 +33,11 @@ struct KvmExec {
   int* d_versions = nullptr; int* d_park_head = nullptr; int* d_ver_base = nullptr; int* d_ver_off = nullptr;
   KvmErrRec* d_err = nullptr;
   bool started = false, armed = false;
-  bool has_stream_ops = false;   // a submitted task is a gemv_bf16 / attn_decode_part (look-ahead prefetch pays only for those)
   KvmResult last{};
 };
 
-// Default of the two newest scheduler features; the environment variables KVM_B200_PREFETCH / KVM_B200_PAIRING (0 or 1)
-// override them for A/B measurements.
-#define KVM_DEFAULT_PREFETCH 0
-#define KVM_DEFAULT_PAIRING 0
+// Stacked GEMM tiles are opt-in (KVM_CFG_PAIR_TILES); the environment variable KVM_B200_PAIRING (0 or 1) overrides the
+// flag for A/B measurements, KVM_B200_PAIR_DEPTH the queue depth from which tiles are stacked.
 static bool kvm_feature_on(const char* env, int dflt) {
   const char* v = getenv(env);
   return v && *v ? atoi(v) != 0 : dflt != 0;
@@ -316,7 +313,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
   S.cfg_flags = h->cfg.flags;
   S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim;
-  S.prefetch = (h->has_stream_ops && !(h->cfg.flags & KVM_CFG_NO_PREFETCH) && kvm_feature_on("KVM_B200_PREFETCH", KVM_DEFAULT_PREFETCH)) ? 1 : 0;
+  { const char* v = getenv("KVM_B200_PAIR_DEPTH"); S.pair_depth = v && *v ? atoi(v) : 2 * h->workers; }
   return S;
 }
 
@@ -347,13 +344,11 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     if (!h->succ.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_succ, h->succ.data(), h->succ.size() * 4, cudaMemcpyHostToDevice, h->stream));
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
-    h->has_stream_ops = false;
     {   // one record per task for the workers: descriptor, argument words and path selector side by side (a single fetch per pop)
       std::vector<int32_t> recs(nt * (size_t)KVM_REC_WORDS, 0);
       for (size_t i = 0; i < nt; ++i) {
         int32_t* r = &recs[i * KVM_REC_WORDS];
         memcpy(r, &h->tasks[i], sizeof(KvmTaskDesc));
-        if (r[0] == 134 || r[0] == 135) h->has_stream_ops = true;
         const int ao = r[6], aw = r[7] < KVM_MAX_ARGS ? r[7] : KVM_MAX_ARGS;
         for (int k = 0; k < aw; ++k) r[16 + k] = h->args[(size_t)ao + k];
         memcpy(r + 16 + KVM_MAX_ARGS, &h->aux[i], sizeof(int4));

@@ -45,7 +45,7 @@ struct KvmDevState {
   const void* tmaps;          // CUtensorMap table for tensor-core tasks
   const int4* task_aux;       // per task: tensor-map indices / path selector
   const int32_t* recs;        // per task KVM_REC_WORDS words: descriptor [0,16), argument words [16,36), path selector [36,40)
-  int prefetch;               // 1: a finishing task prefetches one of its successors' streamed operands into L2
+  int pair_depth;             // tiles are stacked only while at least this many tasks are queued (wide phases; narrow ones keep their parallelism)
   int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
 };
 #define KVM_REC_WORDS 48
@@ -90,7 +90,8 @@ __device__ __forceinline__ void kvm_push_ready(const KvmDevState& S, int task) {
 // `min_depth`: a worker that is still running a task stages its next one only while at least that many tasks are queued
 // (one for every worker): with fewer, the queued tasks are left to the idle workers instead of waiting behind a running one.
 // Returns task or -1.
-__device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM_NCLASS], unsigned min_depth) {
+__device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM_NCLASS], unsigned min_depth, unsigned& depth_out) {
+  depth_out = 0;
 #pragma unroll
   for (int c = KVM_NCLASS - 1; c >= 0; --c)
     if (held[c] >= 0) {
@@ -100,12 +101,11 @@ __device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM
   unsigned t[4], h[4];
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "l"(S.head) : "memory");
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]) : "l"(S.tail) : "memory");
-  if (min_depth > 1) {
-    unsigned depth = 0;
+  unsigned depth = 0;
 #pragma unroll
-    for (int c = 0; c < KVM_NCLASS; ++c) depth += t[c] > h[c] ? t[c] - h[c] : 0u;
-    if (depth < min_depth) return -1;
-  }
+  for (int c = 0; c < KVM_NCLASS; ++c) depth += t[c] > h[c] ? t[c] - h[c] : 0u;
+  depth_out = depth;
+  if (depth < min_depth) return -1;
 #pragma unroll
   for (int c = KVM_NCLASS - 1; c >= 0; --c)
     if (held[c] < 0 && h[c] < t[c]) {
@@ -271,67 +271,6 @@ __device__ int kvm_finish_task(const KvmDevState& S, int task, int so, int sc, i
   if (lane == 0) atomicAdd(S.done, 1);
   return cont;
 }
-// ---- look-ahead for the weight-streaming decode ops ------------------------------------------------------------------------------
-// A decode step is a chain of short phases, each streaming its own weights once; between two phases HBM would sit idle while
-// the last tasks finish and the next ones are released and staged.  A worker that has just finished a task therefore asks the
-// memory system for what one task of the NEXT phase is going to stream (gemv_bf16: its weight rows; attn_decode_part: its
-// slice of the key / value cache), up to KVM_PF_BYTES, with L2 prefetches - nothing is copied, no result depends on it.
-// Which successor: entry (task mod workers) of the successor list, then every workers-th one: tasks of one phase carry
-// consecutive indices and share one successor list, so the phase covers the next one evenly.  A successor that streams nothing
-// (a merge, a join) is looked through once.  All lanes run this with the same values; lanes split the ranges.
-#define KVM_PF_BYTES (384 * 1024)
-#define KVM_PF_PIECE 16384
-__device__ __forceinline__ void kvm_prefetch_range(const char* p, long long bytes) {
-  const int lane = threadIdx.x & 31;
-  if (bytes > KVM_PF_BYTES) bytes = KVM_PF_BYTES;
-  const long long lead = (long long)((16 - ((uintptr_t)p & 15)) & 15);      // whole 16-byte units inside [p, p + bytes)
-  p += lead;
-  bytes = (bytes - lead) & ~15ll;
-  for (long long o = (long long)lane * KVM_PF_PIECE; o < bytes; o += 32ll * KVM_PF_PIECE) {
-    const unsigned n = (unsigned)min((long long)KVM_PF_PIECE, bytes - o);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + o), "r"(n) : "memory");
-  }
-}
-__device__ void kvm_prefetch_task(const KvmDevState& S, int t) {
-  const int32_t* rec = S.recs + (size_t)t * KVM_REC_WORDS;
-  const int op = rec[0];
-  const int32_t* a = rec + 16;
-  if (op == 134) {                                   // gemv_bf16: w = a[3], rows [a[6], a[7])
-    const int wi = a[3], n0 = a[6], n1 = a[7];
-    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0) return;
-    const KvmBuf w = S.bufs[wi];
-    if (!w.p || n1 > w.rows || w.dtype != KVM_BF16) return;
-    kvm_prefetch_range((const char*)w.p + (size_t)n0 * w.ld * 2, ((long long)(n1 - n0 - 1) * w.ld + w.cols) * 2);
-  } else if (op == 135) {                            // attn_decode_part: kc = a[1], vc = a[2], lens = a[3], b a[7], kvh a[8], s a[9], S a[10], Hkv a[12], Tmax a[14]
-    const int ki = a[1], vi = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], SS = a[10], Hkv = a[12], Tmax = a[14];
-    if (ki < 0 || ki >= S.nbufs || vi < 0 || vi >= S.nbufs || li < 0 || li >= S.nbufs || b < 0 || SS <= 0 || s < 0 || Hkv <= 0 || kvh < 0 || Tmax <= 0) return;
-    const KvmBuf kc = S.bufs[ki], vc = S.bufs[vi], lens = S.bufs[li];
-    if (!kc.p || !vc.p || !lens.p || lens.dtype != KVM_I32 || kc.dtype == KVM_I32 || vc.dtype == KVM_I32 || (long long)b >= (long long)lens.rows * lens.cols) return;
-    const int n = ((const volatile int*)lens.p)[b] + 1;
-    if (n <= 0 || n > Tmax) return;
-    const int chunk = (n + SS - 1) / SS, j0 = s * chunk, j1 = min(n, j0 + chunk);
-    const long long row0 = (long long)(b * Hkv + kvh) * Tmax + j0;
-    if (j1 <= j0 || row0 + (j1 - j0) > kc.rows || row0 + (j1 - j0) > vc.rows) return;
-    const int ek = kc.dtype == KVM_BF16 ? 2 : 4, ev = vc.dtype == KVM_BF16 ? 2 : 4;
-    kvm_prefetch_range((const char*)kc.p + (size_t)row0 * kc.ld * ek, ((long long)(j1 - j0 - 1) * kc.ld + kc.cols) * ek);
-    kvm_prefetch_range((const char*)vc.p + (size_t)row0 * vc.ld * ev, ((long long)(j1 - j0 - 1) * vc.ld + vc.cols) * ev);
-  }
-}
-__device__ void kvm_prefetch_next(const KvmDevState& S, int task, int so, int sc) {
-  const int W = (int)gridDim.x;
-  for (int k = task % W, n = 0; k < sc && n < 8; k += W, ++n) {
-    int t = S.succ[so + k];
-    const int32_t* rec = S.recs + (size_t)t * KVM_REC_WORDS;
-    const int op = rec[0];
-    if (op != 134 && op != 135) {                    // look through one non-streaming successor
-      const int so2 = rec[1], sc2 = rec[2], k2 = task % W;
-      if (k2 >= sc2) continue;
-      t = S.succ[so2 + k2];
-    }
-    kvm_prefetch_task(S, t);
-  }
-}
-
 __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S) {
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
   KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
@@ -366,7 +305,6 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         const bool wc = cont < 0 && ticket < 0 && !stop;
         const int c2 = kvm_finish_task(S, slots[drain].task, dd[1], dd[2], dd[10], dd[11], wc);
         if (c2 >= 0) cont = c2;
-        if (S.prefetch) kvm_prefetch_next(S, slots[drain].task, dd[1], dd[2]);
         const int pr = slots[drain].pair;
         if (pr >= 0) {                                       // the partner tile finished with it
           const int32_t w = lane < 16 ? ((const int32_t*)&S.tasks[pr])[lane] : 0;
@@ -382,12 +320,15 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       // 2. stage the next task if a slot is free
       if (!stop && inflight < 2) {
         int task = -1;
+        unsigned depth = 0;                 // tasks queued when this one was popped (0 for a continuation)
         if (cont >= 0) { task = cont; cont = -1; }
         else {
           int tk = -1, hold = 0;
-          if (lane == 0) { tk = kvm_try_pop(S, held, inflight > 0 ? gridDim.x : 1u); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
+          unsigned dp = 0;
+          if (lane == 0) { tk = kvm_try_pop(S, held, inflight > 0 ? gridDim.x : 1u, dp); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
           task = __shfl_sync(0xffffffffu, tk, 0);
           ticket = __shfl_sync(0xffffffffu, hold, 0) ? 0 : -1;      // ticket >= 0 now only means: this worker holds a ticket (no continuation then)
+          depth = __shfl_sync(0xffffffffu, dp, 0);
         }
         if (task >= 0) {
           // one fetch: the task's record holds descriptor, argument words and path selector side by side
@@ -403,7 +344,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
             int v = 0;
             if (lane == 0) {
               if (atomicCAS(&S.claim[task], 0, 1) != 0) v = -2;
-              else if (kvm_ld_acquire(&S.indeg[aw - 1]) == 0 && atomicCAS(&S.claim[aw - 1], 0, 1) == 0) v = aw;
+              else if (depth >= (unsigned)S.pair_depth && kvm_ld_acquire(&S.indeg[aw - 1]) == 0 && atomicCAS(&S.claim[aw - 1], 0, 1) == 0) v = aw;
             }
             v = __shfl_sync(0xffffffffu, v, 0);
             drop = v == -2;

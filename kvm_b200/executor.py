@@ -20,6 +20,7 @@ _lib = None
 
 INIT_FILL, INIT_VALUES, INIT_SEEDED, INIT_NONE = 0, 1, 2, 3
 CFG_NO_TENSOR_CORES = 1
+CFG_PAIR_TILES = 2
 
 
 class KvmError(RuntimeError):

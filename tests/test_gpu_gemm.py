@@ -55,6 +55,25 @@ def test_tc_epilogues(kvm_lib, case):
     ex.close()
 
 
+@pytest.mark.parametrize('flags', [0, 1, 2, 3, 8])
+def test_tc_stacked_tiles(kvm_lib, flags):
+    """KVM_CFG_PAIR_TILES: row-adjacent tiles of one product run stacked as 256 x 256 tiles (an odd tile row is left single);
+    every task still counts as executed exactly once and the result equals the oracle's."""
+    from kvm_b200.executor import CFG_PAIR_TILES
+    M, N, K = 640, 512, 448
+    b = gemm_bundle('matmul_mma_bf16', M, N, K, flags, bias=bool(flags & 8), res='f32' if flags & 8 else None)
+    ex, vm, res = run_both(b, exact_matmul=False, flags=CFG_PAIR_TILES, trace=True)
+    assert res.done == len(b.tasks)
+    execs, observed = ex.task_counts()
+    assert (execs == 1).all()
+    s, e, sm = ex.trace()
+    import collections
+    starts = collections.Counter(zip(s.tolist(), sm.tolist()))
+    assert sum(1 for v in starts.values() if v == 2) >= 1, 'no pair of tiles was stacked'
+    compare(ex, vm, 2e-5)
+    ex.close()
+
+
 def test_mma_fallback_is_bit_exact(kvm_lib):
     """f32 operands cannot take the TMA path: the SIMT fallback accumulates k-ascending like the CPU model, bit for bit."""
     b = gemm_bundle('matmul_mma_bf16', 130, 260, 72, 2, a_dt='f32', b_dt='f32', bias=True)
