@@ -274,6 +274,10 @@ def run_ours(args, rank, world, local_rank):
                 line['kernels_alone'] = run_alone(local_rank)
             except Exception as e:
                 line['kernels_alone'] = {'error': str(e)[:300]}
+            try:
+                line['small_models'] = run_small(local_rank)
+            except Exception as e:
+                line['small_models'] = {'error': str(e)[:300]}
         if cpu:
             line['cpu_baseline'] = {'value': cpu['steps_per_s'], 'unit': 'steps/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
                                     'sample': f"{cpu['tasks']} of {cpu['of_tasks']} tasks of one step, a few of each of its {cpu['kinds']} op kinds, {cpu['seconds']:.1f} s on the numpy oracle; step time = sum over kinds of count x mean task time"}
@@ -438,6 +442,29 @@ def run_alone(device):
     peak = pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])
     out['gemv_k4096'] = {'shape': [rows * ntask, K], 'tasks': ntask, 'ms': ms, 'achieved': gbs, 'unit': 'GB/s', 'peak': peak, 'frac': gbs / peak, 'bound': 'hbm'}
     out['note'] = f'whole launches (about 17 us of launch, arming and shutdown included); peaks: {kind}'
+    return out
+
+
+def run_small(device):
+    """The two small configurations of the reference's benchmark list through the generic per-op path: the tiny GPT (2 layers,
+    d 128, batch 8 x 64, f32, AdamW, 20 steps unrolled in one launch) and eight MLPs of different widths trained side by side
+    (batch 256, f32, SGD with momentum, 10 steps in one launch).  Both are latency-bound here (no fused small-model step)."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.gpt import build_training, preset as gpt_preset
+    from kvm_b200.workloads.mlp import build_mlps, params, preset as mlp_preset
+    out = {}
+    b = build_training(gpt_preset('gpt_tiny'), 20, stream_steps=80).to_bundle(check=False)
+    with Executor(device=device) as ex:
+        ex.load(b); ex.run()
+        ms = min(ex.run().ms for _ in range(2))
+        out['gpt_tiny'] = {'steps_per_s': 20 / (ms * 1e-3), 'us_per_step': ms * 1e3 / 20, 'tasks_per_step': len(b.tasks) // 20, 'loss_step0': float(ex.read_buffer('loss.0')[0, 0]),
+                           'loss_step19': float(ex.read_buffer('loss.19')[0, 0])}
+    c = mlp_preset('mlp8')
+    b = build_mlps(c, 10).to_bundle(check=False)
+    with Executor(device=device) as ex:
+        ex.load(b); ex.run()
+        ms = min(ex.run().ms for _ in range(2))
+        out['mlp8'] = {'us_per_joint_step': ms * 1e3 / 10, 'tasks_per_step': len(b.tasks) // 10, 'params': params(c), 'gflop_per_step': 6.0 * params(c) * c.batch / 1e9}
     return out
 
 

@@ -56,10 +56,11 @@ def test_tc_epilogues(kvm_lib, case):
 
 
 @pytest.mark.parametrize('flags', [0, 1, 2, 3, 8])
-def test_tc_stacked_tiles(kvm_lib, flags):
+def test_tc_stacked_tiles(kvm_lib, flags, monkeypatch):
     """KVM_CFG_PAIR_TILES: row-adjacent tiles of one product run stacked as 256 x 256 tiles (an odd tile row is left single);
     every task still counts as executed exactly once and the result equals the oracle's."""
     from kvm_b200.executor import CFG_PAIR_TILES
+    monkeypatch.setenv('KVM_B200_PAIR_DEPTH', '0')        # stack whatever is ready, however short the queue
     M, N, K = 640, 512, 448
     b = gemm_bundle('matmul_mma_bf16', M, N, K, flags, bias=bool(flags & 8), res='f32' if flags & 8 else None)
     ex, vm, res = run_both(b, exact_matmul=False, flags=CFG_PAIR_TILES, trace=True)
