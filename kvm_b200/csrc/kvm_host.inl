@@ -341,7 +341,19 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_claim, nt * 4));
     if (h->cfg.trace) { KVM_CUDA(cudaMalloc(&h->d_tstart, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tend, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tsmid, nt * 4)); }
     KVM_CUDA(cudaMemcpyAsync(h->d_tasks, h->tasks.data(), nt * sizeof(KvmTaskDesc), cudaMemcpyHostToDevice, h->stream));
-    if (!h->succ.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_succ, h->succ.data(), h->succ.size() * 4, cudaMemcpyHostToDevice, h->stream));
+    if (!h->succ.empty()) {
+      // device form of a successor entry: task index in the low 27 bits, above it the successor's priority class (2 bits) and
+      // whether it waits on a version (1 bit), so that the releasing warp needs no look at the successor's descriptor
+      if (nt >= (size_t)1 << KVM_SUCC_BITS) { h->error = "too many tasks for one launch"; return KVM_E_ARG; }
+      std::vector<int32_t> enc(h->succ.size());
+      for (size_t k = 0; k < enc.size(); ++k) {
+        const KvmTaskDesc& d = h->tasks[h->succ[k]];
+        const int cls = d.priority < 0 ? 0 : (d.priority >> 3) >= KVM_NCLASS ? KVM_NCLASS - 1 : (d.priority >> 3);
+        enc[k] = h->succ[k] | (cls << KVM_SUCC_BITS) | ((d.wait_var >= 0 ? 1 : 0) << (KVM_SUCC_BITS + 2));
+      }
+      KVM_CUDA(cudaMemcpyAsync(h->d_succ, enc.data(), enc.size() * 4, cudaMemcpyHostToDevice, h->stream));
+      KVM_CUDA(cudaStreamSynchronize(h->stream));      // `enc` is a local
+    }
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
     {   // one record per task for the workers: descriptor, argument words and path selector side by side (a single fetch per pop)

@@ -49,6 +49,7 @@ struct KvmDevState {
   int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
 };
 #define KVM_REC_WORDS 48
+#define KVM_SUCC_BITS 27          // successor entry on the device: index | class << 27 | has-version-wait << 29
 
 struct KvmSlot {
   int task;                   // -1 = leave
@@ -218,20 +219,16 @@ __device__ int kvm_finish_task(const KvmDevState& S, int task, int so, int sc, i
     for (int u = 0; u < KVM_REL_U; ++u) {
       kind[u] = -1;
       if (s[u] >= 0) {
+        const int meta = s[u] >> KVM_SUCC_BITS;
+        s[u] &= (1 << KVM_SUCC_BITS) - 1;
         const int old = atomicSub(&S.indeg[s[u]], 1);
-        if (old == 1) kind[u] = 0;
+        if (old == 1) kind[u] = (meta & 4) ? 4 : (meta & 3);
         else if (old <= 0) kvm_dev_fail(S, KVM_ERR_BAD_TASK, s[u], old);
       }
     }
     // One fence for the whole batch: whoever made a counter reach zero has seen every other predecessor's decrement, and those
     // came after their data; the ring cells below are then plain stores (their readers load with acquire).
     __threadfence();
-#pragma unroll
-    for (int u = 0; u < KVM_REL_U; ++u)
-      if (kind[u] == 0) {
-        const KvmTaskDesc& d = S.tasks[s[u]];
-        kind[u] = d.wait_var >= 0 ? 4 : kvm_class_of(d.priority);
-      }
     // the continuation: the first ready successor without a version wait (no queue hop)
 #pragma unroll
     for (int u = 0; u < KVM_REL_U; ++u) {
@@ -332,6 +329,8 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         }
         if (task >= 0) {
           // one fetch: the task's record holds descriptor, argument words and path selector side by side
+          // the exactly-once witness is taken here (its round trip overlaps the record fetch), not by the compute group
+          const int seen = lane == 0 ? atomicAdd(&S.exec_count[task], 1) : 0;
           const int32_t* rec = S.recs + (size_t)task * KVM_REC_WORDS;
           const int32_t w0 = rec[lane], w1 = lane < 8 ? rec[32 + lane] : 0;
           // Stacked GEMM tiles: a tensor-core tile whose partner (same product, rows 128 further or nearer; path selector word 3)
@@ -350,7 +349,11 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
             drop = v == -2;
             pair = v > 0 ? v - 1 : -1;
           }
-          if (drop) { progressed = true; continue; }
+          if (drop) { if (lane == 0) atomicSub(&S.exec_count[task], 1); progressed = true; continue; }      // not run here: its partner's worker runs it
+          if (lane == 0) {
+            if (seen != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, task);
+            if (pair >= 0) atomicAdd(&S.exec_count[pair], 1);      // counted only: the claim word is what makes a stacked tile run once
+          }
           KvmSlot& sl = slots[fill];
           if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
           if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
@@ -400,8 +403,6 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       if (task < 0) break;
       c.task = task; c.pair = sl.pair;
       if (tid == 0) {
-        if (atomicAdd(&S.exec_count[task], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, task);
-        if (c.pair >= 0 && atomicAdd(&S.exec_count[c.pair], 1) != 0) kvm_dev_fail(S, KVM_ERR_DOUBLE_EXEC, c.pair);
         const int wv = sl.desc[8];
         if (wv >= 0 && wv < S.nvars && kvm_ld_acquire(&S.versions[wv]) < sl.desc[9] + S.ver_off[wv]) kvm_dev_fail(S, KVM_ERR_WAIT_VIOLATION, task, wv);
         if (S.trace) {
@@ -413,8 +414,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       if (op != 0 && *(volatile int*)&S.err->code == 0) kvm_dispatch(c, op, sl.args, sl.aux);
       // this task's generic-proxy writes (global results, shared scratch) ordered before any later TMA access to them
       asm volatile("fence.proxy.async;" ::: "memory");
-      __threadfence();
-      kvm_sync();
+      kvm_sync();                       // every thread's writes happen before thread 0's fence below (barrier, then a cumulative gpu-scope fence)
       if (tid == 0) {
         if (S.trace) { S.t_end[task] = kvm_globaltimer(); if (c.pair >= 0) S.t_end[c.pair] = S.t_end[task]; }
         __threadfence();

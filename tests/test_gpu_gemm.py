@@ -63,7 +63,7 @@ def test_tc_stacked_tiles(kvm_lib, flags, monkeypatch):
     monkeypatch.setenv('KVM_B200_PAIR_DEPTH', '0')        # stack whatever is ready, however short the queue
     M, N, K = 640, 512, 448
     b = gemm_bundle('matmul_mma_bf16', M, N, K, flags, bias=bool(flags & 8), res='f32' if flags & 8 else None)
-    ex, vm, res = run_both(b, exact_matmul=False, flags=CFG_PAIR_TILES, trace=True)
+    ex, vm, res = run_both(b, exact_matmul=False, flags=CFG_PAIR_TILES, trace=True, workers=1)      # one worker: it pops a tile and finds the partner still free
     assert res.done == len(b.tasks)
     execs, observed = ex.task_counts()
     assert (execs == 1).all()
