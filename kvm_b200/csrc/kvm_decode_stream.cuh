@@ -154,10 +154,41 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
 // Keys and values (bf16, rows contiguous: ld == hd) arrive as two bulk copies.  If `newrow` >= 0 that key is the one this task
 // appends: its rotated key / value (float, hd each, in knew / vnew shared arrays) is placed in the staged tiles by the threads
 // and the copies leave it out.
-//   scores   hd/8 lanes per key, query columns in registers, shuffle sums (see below)
+//   scores   kvm_decode_scores: lanes = (key, head, pieces of the row), query values in registers, shuffle sums
 //   softmax  over the whole split at once (warp g = query head g): p = exp(s - m) kept in shared memory as [key][8]
 //   PV       thread = (key group, column pair): all G heads share one read of V; key groups are summed in group order
 // emit(g, column, m, l, acc) as in kvm_decode_group.  Returns false when the split does not fit in shared memory.
+// Scores of one split from the staged keys: s[key][g] = scale * q_g . k_key.  A key is spread over G*(hd/8)/CPL lanes: each lane
+// owns one query head g and CPL 16-byte pieces (8 columns each) of the row, with its 8*CPL query values in registers (a small,
+// fixed register footprint whatever G is); the lanes of one (key, g) are neighbours and add up by shuffles; a warp takes
+// 32 / lanes-per-key consecutive keys per step.  Needs G and hd/8 to be powers of two and lanes-per-key <= 32.
+template <int CPL>
+__device__ __forceinline__ void kvm_decode_scores(const unsigned char* Ks, const float* qs, float* ps, int nk, int G, int hd, float sc) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nch = hd >> 3, lpg = nch / CPL, lpk = G * lpg, KPW = 32 / lpk;         // lanes per (key, head), per key; keys per warp step
+  const int sub = lane / lpk, li = lane % lpk, g = li / lpg, ch0 = (li % lpg) * CPL;
+  float qr[CPL * 8];
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) {
+    const float4 qa = *(const float4*)(qs + g * hd + (ch0 + j) * 8), qb = *(const float4*)(qs + g * hd + (ch0 + j) * 8 + 4);
+    qr[8 * j] = qa.x; qr[8 * j + 1] = qa.y; qr[8 * j + 2] = qa.z; qr[8 * j + 3] = qa.w; qr[8 * j + 4] = qb.x; qr[8 * j + 5] = qb.y; qr[8 * j + 6] = qb.z; qr[8 * j + 7] = qb.w;
+  }
+  for (int key0 = warp * KPW; key0 < nk; key0 += KVM_NWARPS * KPW) {
+    const int key = key0 + sub, kk = min(key, nk - 1);
+    const unsigned char* kp = Ks + (size_t)kk * hd * 2 + ch0 * 16;
+    float sg = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) {
+      const uint4 kv = *(const uint4*)(kp + j * 16);
+      sg = fmaf(qr[8 * j], kvm_bf16lo(kv.x), sg); sg = fmaf(qr[8 * j + 1], kvm_bf16hi(kv.x), sg); sg = fmaf(qr[8 * j + 2], kvm_bf16lo(kv.y), sg);
+      sg = fmaf(qr[8 * j + 3], kvm_bf16hi(kv.y), sg); sg = fmaf(qr[8 * j + 4], kvm_bf16lo(kv.z), sg); sg = fmaf(qr[8 * j + 5], kvm_bf16hi(kv.z), sg);
+      sg = fmaf(qr[8 * j + 6], kvm_bf16lo(kv.w), sg); sg = fmaf(qr[8 * j + 7], kvm_bf16hi(kv.w), sg);
+    }
+    for (int o = lpg >> 1; o; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
+    if (key < nk && (li % lpg) == 0) ps[key * 8 + g] = sg * sc;
+  }
+}
+
 #define KVM_AS_QS 4096             // byte offsets in the op scratch: 64 barriers | qs [8][128] | inv [128] | knew [128] | vnew [128] | ml [16] | ...
 #define KVM_AS_OFF_QS 64
 #define KVM_AS_OFF_INV (64 + KVM_AS_QS)
@@ -207,41 +238,34 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
   kvm_sync();
   if (!kvm_mbar_wait_t(barK, 0)) ok = false;
 
-  // ---- scores: hd/8 lanes per key (each holds 8 columns of the queries in registers), a warp takes 32/(hd/8) consecutive keys per
-  //      step (one contiguous, conflict-free 512-byte read), partial dot products are summed over the lanes of a key by shuffles
+  // ---- scores (see kvm_decode_scores): the smallest number of pieces per lane that fits a key into one warp
   {
-    const int LPK = hd >> 3, KPW = 32 / LPK, sub = lane / LPK, c0 = (lane % LPK) * 8;
-    float qr[GT][8];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      const float4 qa = g < G ? *(const float4*)(qs + g * hd + c0) : make_float4(0, 0, 0, 0), qb = g < G ? *(const float4*)(qs + g * hd + c0 + 4) : make_float4(0, 0, 0, 0);
-      qr[g][0] = qa.x; qr[g][1] = qa.y; qr[g][2] = qa.z; qr[g][3] = qa.w; qr[g][4] = qb.x; qr[g][5] = qb.y; qr[g][6] = qb.z; qr[g][7] = qb.w;
-    }
-    for (int key0 = warp * KPW; key0 < nk; key0 += KVM_NWARPS * KPW) {
-      const int key = key0 + sub, kk = min(key, nk - 1);
-      const uint4 kv = *(const uint4*)(Ks + (size_t)kk * hd * 2 + c0 * 2);
-      const float k0 = kvm_bf16lo(kv.x), k1 = kvm_bf16hi(kv.x), k2 = kvm_bf16lo(kv.y), k3 = kvm_bf16hi(kv.y), k4 = kvm_bf16lo(kv.z), k5 = kvm_bf16hi(kv.z),
-                  k6 = kvm_bf16lo(kv.w), k7 = kvm_bf16hi(kv.w);
-#pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float sg = qr[g][0] * k0;
-        sg = fmaf(qr[g][1], k1, sg); sg = fmaf(qr[g][2], k2, sg); sg = fmaf(qr[g][3], k3, sg); sg = fmaf(qr[g][4], k4, sg);
-        sg = fmaf(qr[g][5], k5, sg); sg = fmaf(qr[g][6], k6, sg); sg = fmaf(qr[g][7], k7, sg);
-        for (int o = LPK >> 1; o; o >>= 1) sg += __shfl_xor_sync(0xffffffffu, sg, o);
-        if (g < G && key < nk && c0 == 0) ps[key * 8 + g] = sg * sc;
-      }
-    }
+    const int slots = G * (hd >> 3);
+    if (slots <= 32) kvm_decode_scores<1>(Ks, qs, ps, nk, G, hd, sc);
+    else if (slots <= 64) kvm_decode_scores<2>(Ks, qs, ps, nk, G, hd, sc);
+    else kvm_decode_scores<4>(Ks, qs, ps, nk, G, hd, sc);
   }
   kvm_sync();
-  // ---- softmax over the split: warp g
-  if (warp < G) {
+  // ---- softmax over the split: 16/G warps per query head, each a quarter (or so) of the keys; p = exp(s - m) replaces s
+  {
+    const int wpg = KVM_NWARPS / G, g = warp % G, part = warp / G;
     float m = KVM_ATTN_EMPTY_M_STREAM;
-    for (int j = lane; j < nk; j += 32) m = fmaxf(m, ps[j * 8 + warp]);
+    for (int j = part * 32 + lane; j < nk; j += wpg * 32) m = fmaxf(m, ps[j * 8 + g]);
     m = kvm_warp_max(m);
+    if (lane == 0) red[warp] = m;
+    kvm_sync();
+    m = KVM_ATTN_EMPTY_M_STREAM;
+    for (int p2 = 0; p2 < wpg; ++p2) m = fmaxf(m, red[g + G * p2]);
     float l = 0.0f;
-    for (int j = lane; j < nk; j += 32) { const float p = __expf(ps[j * 8 + warp] - m); ps[j * 8 + warp] = p; l += p; }
+    for (int j = part * 32 + lane; j < nk; j += wpg * 32) { const float p = __expf(ps[j * 8 + g] - m); ps[j * 8 + g] = p; l += p; }
     l = kvm_warp_sum(l);
-    if (lane == 0) { ml[warp] = m; ml[8 + warp] = l; }
+    if (lane == 0) red[KVM_NWARPS + warp] = l;
+    kvm_sync();
+    if (warp < G && lane == 0) {
+      float L = 0.0f;
+      for (int p2 = 0; p2 < wpg; ++p2) L += red[KVM_NWARPS + warp + G * p2];
+      ml[warp] = m; ml[8 + warp] = L;
+    }
   }
   kvm_sync();
   if (!kvm_mbar_wait_t(barV, 0)) ok = false;
@@ -251,6 +275,7 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
     float acc[GT][2];
 #pragma unroll
     for (int g = 0; g < GT; ++g) acc[g][0] = acc[g][1] = 0.0f;
+#pragma unroll 4
     for (int j = kq; j < nk; j += KQ) {
       const uint32_t vv = *(const uint32_t*)(Vs + (size_t)j * hd * 2 + c2 * 4);
       const float v0 = kvm_bf16lo(vv), v1 = kvm_bf16hi(vv);
@@ -280,7 +305,7 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
 template <class Pro, class Emit>
 __device__ bool kvm_attn_part_stream(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
                                      Pro prologue, Emit emit) {
-  if (kc.dtype != KVM_BF16 || vc.dtype != KVM_BF16 || kc.ld != hd || vc.ld != hd || !kvm_vec_ok(kc) || !kvm_vec_ok(vc) || G > 8 ||
+  if (kc.dtype != KVM_BF16 || vc.dtype != KVM_BF16 || kc.ld != hd || vc.ld != hd || !kvm_vec_ok(kc) || !kvm_vec_ok(vc) || G > 8 || (G & (G - 1)) ||
       !(hd == 16 || hd == 32 || hd == 64 || hd == 128)) return false;
   if (G <= 1) return kvm_attn_part_stream_t<1>(c, kc, vc, base, j0, j1, newrow, G, hd, sc, prologue, emit);
   if (G <= 2) return kvm_attn_part_stream_t<2>(c, kc, vc, base, j0, j1, newrow, G, hd, sc, prologue, emit);
