@@ -399,6 +399,21 @@ def run_decode(args, device):
            'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'unit': 'GB/s', 'frac': gbs / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
                         'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0])}
     ex.close()
+    try:        # the same shape with 8 independent users (one row each, as the reference serves a batch): every user streams the weights again
+        cfg8 = preset(args.decode_model, batch=8)
+        b8 = build_decode(cfg8).to_bundle(check=False)
+        with Executor(device=device) as ex8:
+            ex8.load(b8)
+            ex8.run_steps(2)
+            r8 = ex8.run_steps(6)
+        ms8 = r8.ms / 6
+        ideal = weight_bytes(cfg8) + 8 * kv_bytes(cfg8, cfg8.ctx + 5)
+        out['batch8'] = {'value': 8 / (ms8 / 1e3), 'unit': 'tok/s', 'ms_per_step': ms8, 'tasks_per_step': len(b8.tasks),
+                         'roofline': {'bound': 'hbm', 'achieved': ideal / (ms8 / 1e3) / 1e9, 'unit': 'GB/s', 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
+                                      'frac': ideal / (ms8 / 1e3) / 1e9 / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'bytes_per_step': ideal,
+                                      'note': 'algorithmic bytes count the weights once; the users are independent row tasks here and stream them 8 times'}}
+    except Exception as e:
+        out['batch8'] = {'error': str(e)[:300]}
     return out
 
 

@@ -40,6 +40,7 @@ class DecodeConfig:
     rows_per_task: int = 64  # weight rows per gemv task; 0 = balance every phase over `workers` SMs
     workers: int = 148
     join_threshold: int = 24  # fan-ins wider than this go through a join no-op (fewer edges, one more hop)
+    lockstep: bool = False    # several users: keep them in step phase by phase (see build_decode); measured slower, kept for experiments
 
 
 PRESETS = {
@@ -80,19 +81,12 @@ def build_decode(c: DecodeConfig) -> Graph:
         the phase into whole waves over the SMs, with as many waves as keep a task near 2 MB of weights."""
         if c.rows_per_task > 0:
             return c.rows_per_task
-        total = sum(ns)
+        total = sum(ns) * B                      # every user streams the rows again
         slots = c.workers * max(1, round(total * k * 2 / (c.workers * (2 << 20))))
         rows = max(8, -(-total // slots))
-        while sum(-(-n // rows) for n in ns) > slots:
+        while sum(-(-n // rows) for n in ns) * B > slots:
             rows += 1
         return rows
-
-    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20, rows=None):
-        rows = rows or phase_rows([n], k)
-        for i, n0 in enumerate(range(0, n, rows)):
-            n1 = min(n0 + rows, n)
-            g.task('gemv_bf16', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
-                   [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{i}')
 
     g.buffer('wb.embed', V, d, 'bf16', seeded('embed'))
     g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
@@ -102,50 +96,79 @@ def build_decode(c: DecodeConfig) -> Graph:
         g.buffer('w.' + p + 'ln1', 1, d, init={'kind': 'fill', 'value': 1.0}), g.buffer('w.' + p + 'ln2', 1, d, init={'kind': 'fill', 'value': 1.0})
         W(p + 'q', H * hd, d), W(p + 'k', Hkv * hd, d), W(p + 'v', Hkv * hd, d), W(p + 'o', d, H * hd), W(p + 'gate', F, d), W(p + 'up', F, d), W(p + 'down', d, F)
     # Every user is an independent one-row request with its own cache, length counter and activations (b = 0 in every op);
-    # the weights are shared.
-    for u in range(B):
-        t = f'u{u}.'
-        lens = g.buffer(t + 'lens', 1, 1, 'i32', {'kind': 'fill', 'value': c.ctx})
-        tok = g.buffer(t + 'tok', 1, 1, 'i32', {'kind': 'fill', 'value': (7 * u + 3) % V})
-        x = g.buffer(t + 'x', 1, d)
-        g.task('gather_rows', {'src': 'wb.embed', 'idx': tok, 'dst': x, 'r0': 0, 'r1': 1, 'd': d}, ['wb.embed', tok], [x], 31, t + 'embed')
-        for l in range(c.layers):
-            p, tl = f'l{l}.', f'{t}l{l}.'
-            prio = max(30 - l, 2)
-            kc = g.buffer(tl + 'kc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'kc', 1.0))
-            vc = g.buffer(tl + 'vc', Hkv * c.tmax, hd, 'bf16', seeded(tl + 'vc', 1.0))
-            q, k, v = g.buffer(tl + 'q', 1, H * hd), g.buffer(tl + 'k', 1, Hkv * hd), g.buffer(tl + 'v', 1, Hkv * hd)
-            r_qkv = phase_rows([H * hd, Hkv * hd, Hkv * hd], d)           # q, k and v run as one phase
-            gemv(tl + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
-            gemv(tl + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
-            gemv(tl + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
-            part, o = g.buffer(tl + 'part', S * H, hd + 2), g.buffer(tl + 'o', 1, H * hd)
-            G = H // Hkv
+    # the weights are shared.  Emission is layer by layer and, inside a GEMV, weight-row block by block with the users innermost:
+    # the users' tasks on one block of rows sit side by side in the ready queue, run at the same time on different SMs, and the
+    # block comes from HBM once and from L2 for the others.
+    U = range(B)
+    T = [f'u{u}.' for u in U]
+    lens = [g.buffer(T[u] + 'lens', 1, 1, 'i32', {'kind': 'fill', 'value': c.ctx}) for u in U]
+    tok = [g.buffer(T[u] + 'tok', 1, 1, 'i32', {'kind': 'fill', 'value': (7 * u + 3) % V}) for u in U]
+    x = [g.buffer(T[u] + 'x', 1, d) for u in U]
+    for u in U:
+        g.task('gather_rows', {'src': 'wb.embed', 'idx': tok[u], 'dst': x[u], 'r0': 0, 'r1': 1, 'd': d}, ['wb.embed', tok[u]], [x[u]], 31, T[u] + 'embed')
+
+    def gemv_all(tag, xs, w, outs, n, k, pro=0, x2s=None, gamma=None, ress=None, prio=20, rows=None, after=()):
+        rows = rows or phase_rows([n], k)
+        for i, n0 in enumerate(range(0, n, rows)):
+            n1 = min(n0 + rows, n)
+            for u in U:
+                x2, res = (x2s[u] if x2s else None), (ress[u] if ress else None)
+                g.task('gemv_bf16', {'x': xs[u], 'x2': x2, 'gamma': gamma, 'w': w, 'out': outs[u], 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
+                       [xs[u], x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(outs[u], (0, 1), (n0, n1))], prio, f'{T[u]}{tag}.{i}', after=after)
+
+    def lockstep(tag, bufs, prio):
+        """With several users: a no-op that waits for every user's `bufs`; the next phase's tasks are released behind it in one
+        go, block by block with the users side by side (that order is what lets the users share one HBM read of a block)."""
+        if B == 1 or not c.lockstep:
+            return ()
+        return (g.task('noop', {}, list(bufs), [], prio, 'sync.' + tag),)
+
+    G = H // Hkv
+    bar = ()
+    for l in range(c.layers):
+        p = f'l{l}.'
+        prio = max(30 - l, 2)
+        TL = [f'{T[u]}l{l}.' for u in U]
+        kc = [g.buffer(TL[u] + 'kc', Hkv * c.tmax, hd, 'bf16', seeded(TL[u] + 'kc', 1.0)) for u in U]
+        vc = [g.buffer(TL[u] + 'vc', Hkv * c.tmax, hd, 'bf16', seeded(TL[u] + 'vc', 1.0)) for u in U]
+        q, k, v = ([g.buffer(TL[u] + n, 1, cols) for u in U] for n, cols in (('q', H * hd), ('k', Hkv * hd), ('v', Hkv * hd)))
+        r_qkv = phase_rows([H * hd, Hkv * hd, Hkv * hd], d)           # q, k and v run as one phase
+        gemv_all(p + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv, after=bar)
+        gemv_all(p + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv, after=bar)
+        gemv_all(p + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv, after=bar)
+        part = [g.buffer(TL[u] + 'part', S * H, hd + 2) for u in U]
+        o = [g.buffer(TL[u] + 'o', 1, H * hd) for u in U]
+        slice_ = c.tmax // S
+        for u in U:
             for kvh in range(Hkv):
-                rows = (kvh * c.tmax, (kvh + 1) * c.tmax)
                 # Only the split that holds the newest key appends (one cache row); which one depends on the length at run time.
                 # The splits of one step never touch each other's rows, so each declares a disjoint slice of the head's rows as
                 # written (ordering against the next step comes through `lens`), and the S splits run concurrently.
-                slice_ = c.tmax // S
                 for s in range(S):
                     rows = (kvh * c.tmax + s * slice_, kvh * c.tmax + (s + 1) * slice_)
-                    g.task('attn_decode_part', {'q': q, 'kc': kc, 'vc': vc, 'lens': lens, 'part': part, 'knew': k, 'vnew': v, 'b': 0, 'kvh': kvh, 's': s, 'S': S, 'H': H,
-                                                'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
-                           [q, k, v, lens], [(kc, rows), (vc, rows), (part, (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{tl}part.{kvh}.{s}')
+                    g.task('attn_decode_part', {'q': q[u], 'kc': kc[u], 'vc': vc[u], 'lens': lens[u], 'part': part[u], 'knew': k[u], 'vnew': v[u], 'b': 0, 'kvh': kvh, 's': s,
+                                                'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
+                           [q[u], k[u], v[u], lens[u]], [(kc[u], rows), (vc[u], rows), (part[u], (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{TL[u]}part.{kvh}.{s}')
+        for u in U:
             for kvh in range(Hkv):                              # one merge per GQA group: short tasks, all concurrent
-                g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': H, 'hd': hd},
-                       [part], [(o, (0, 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{tl}merge.{kvh}')
-            x1 = g.buffer(tl + 'x1', 1, d)
-            gemv(tl + 'o', o, 'wb.' + p + 'o', x1, d, H * hd, 0, res=x, prio=prio)
-            gate, up = g.buffer(tl + 'gate', 1, F), g.buffer(tl + 'up', 1, F)
-            r_gu = phase_rows([F, F], d)
-            gemv(tl + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
-            gemv(tl + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
-            xn = g.buffer(tl + 'x2', 1, d)
-            gemv(tl + 'down', gate, 'wb.' + p + 'down', xn, d, F, 2, x2=up, res=x1, prio=prio)
-            x = xn
-        logits = g.buffer(t + 'logits', 1, V)
-        gemv(t + 'head', x, 'wb.head', logits, V, d, 1, gamma='w.lnf', prio=1)
-        g.task('argmax', {'logits': logits, 'out': tok, 'r0': 0, 'r1': 1, 'V': V}, [logits], [tok], 1, t + 'argmax')
-        g.task('counter_inc', {'x': lens, 'i0': 0, 'i1': 1, 'delta': 1}, [lens], [lens], 0, t + 'advance')
+                g.task('attn_decode_merge', {'part': part[u], 'o': o[u], 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': H, 'hd': hd},
+                       [part[u]], [(o[u], (0, 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{TL[u]}merge.{kvh}')
+        x1 = [g.buffer(TL[u] + 'x1', 1, d) for u in U]
+        bar = lockstep(p + 'o', o, prio)
+        gemv_all(p + 'o', o, 'wb.' + p + 'o', x1, d, H * hd, 0, ress=x, prio=prio, after=bar)
+        gate, up = ([g.buffer(TL[u] + n, 1, F) for u in U] for n in ('gate', 'up'))
+        r_gu = phase_rows([F, F], d)
+        bar = lockstep(p + 'gu', x1, prio)
+        gemv_all(p + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu, after=bar)
+        gemv_all(p + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu, after=bar)
+        xn = [g.buffer(TL[u] + 'x2', 1, d) for u in U]
+        bar = lockstep(p + 'down', gate + up, prio)
+        gemv_all(p + 'down', gate, 'wb.' + p + 'down', xn, d, F, 2, x2s=up, ress=x1, prio=prio, after=bar)
+        x = xn
+        bar = lockstep(p + 'next', x, prio)
+    logits = [g.buffer(T[u] + 'logits', 1, V) for u in U]
+    gemv_all('head', x, 'wb.head', logits, V, d, 1, gamma='w.lnf', prio=1, after=bar)
+    for u in U:
+        g.task('argmax', {'logits': logits[u], 'out': tok[u], 'r0': 0, 'r1': 1, 'V': V}, [logits[u]], [tok[u]], 1, T[u] + 'argmax')
+        g.task('counter_inc', {'x': lens[u], 'i0': 0, 'i1': 1, 'delta': 1}, [lens[u]], [lens[u]], 0, T[u] + 'advance')
     return g
