@@ -337,6 +337,15 @@ def run_dp(args, rank, world, local_rank):
     w0 = torch.tensor([float(np.abs(dp.bwd.read_buffer('w.lnf.g')).sum())], dtype=torch.float64, device='cuda')
     wmax, wmin = w0.clone(), w0.clone()
     dist.all_reduce(wmax, op=dist.ReduceOp.MAX); dist.all_reduce(wmin, op=dist.ReduceOp.MIN)
+    dp.close()
+    del arena
+    torch.cuda.empty_cache()
+    tp = None
+    if args.decode_tokens > 0:
+        try:
+            tp = run_decode_tp(args, rank, world, local_rank)
+        except Exception as e:          # the training line stands on its own
+            tp = {'error': str(e)[:300]}
     if rank == 0:
         gemm_fl, attn_fl = algorithmic_flops(cfg)
         pk, pk_kind = peaks()
@@ -355,9 +364,69 @@ def run_dp(args, rank, world, local_rank):
             'e2e': {'value': value, 'unit': 'steps/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0, 'note': 'multi-GPU arm keeps tokens resident; the 1-GPU line carries the host-copy arm'},
             'gpu_launches': 6 * args.steps, 'clocks': clk.summary(),
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': None,
-                         'peak_source': f'{pk_kind} bf16_tflops_sustained (per GPU, device time incl. all-reduce)'}}))
-    dp.close()
+                         'peak_source': f'{pk_kind} bf16_tflops_sustained (per GPU, device time incl. all-reduce)'},
+            'decode_tp': tp}))
     dist.destroy_process_group()
+
+
+def run_decode_tp(args, rank, world, device):
+    """Tensor-parallel greedy decode of the 8B shape over the `world` GPUs (strong scaling: the same token, weights and cache split
+    over the ranks): 2 * layers + 1 launches of the persistent kernel per token with an NCCL all-reduce of the [1, hidden] partial
+    between them, the LM head split by vocabulary.  Timed with CUDA events around whole tokens, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from kvm_b200.tp import TensorParallelDecode, pick_token
+    from kvm_b200.workloads.decode import build_decode_tp, kv_bytes, preset, weight_bytes
+    cfg = preset(args.decode_model)
+    if cfg.heads % world or cfg.kv_heads % world or cfg.ffn % world or cfg.vocab % world:
+        return {'error': f'{args.decode_model} does not split over {world} ranks'}
+    names = [f'u0.l{l}.{n}' for l in range(cfg.layers) for n in ('x1', 'x2')]
+    bufs = {n: torch.zeros(1, cfg.hidden, dtype=torch.float32, device='cuda') for n in names}
+    logits = torch.zeros(1, cfg.vocab // world, dtype=torch.float32, device='cuda')
+    tok = torch.full((1, 1), 3, dtype=torch.int32, device='cuda')
+    bind = {n: t.data_ptr() for n, t in bufs.items()}
+    bind.update({'u0.logits': logits.data_ptr(), 'u0.tok': tok.data_ptr()})
+    tpd = TensorParallelDecode(cfg, rank, world, device, bind)
+    comm = {'n': 0}
+
+    def all_reduce_sum(name):
+        dist.all_reduce(bufs[name], op=dist.ReduceOp.SUM)
+        torch.cuda.current_stream().synchronize()
+        comm['n'] += 1
+
+    def choose():
+        val, idx = logits.max(dim=1)
+        mine = torch.stack([val.double(), (idx + rank * logits.shape[1]).double()], dim=1)      # [1, 2]
+        allp = torch.zeros(world, 2, dtype=torch.float64, device='cuda')
+        dist.all_gather_into_tensor(allp, mine)
+        p = allp.cpu().numpy()
+        tok.fill_(pick_token((float(a), int(b)) for a, b in p))
+        torch.cuda.current_stream().synchronize()
+
+    ntok, warm = min(args.decode_tokens, 8), 2
+    for _ in range(warm):
+        tpd.token(all_reduce_sum, choose)
+    dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    kern_ms = 0.0
+    for _ in range(ntok):
+        kern_ms += tpd.token(all_reduce_sum, choose)
+    torch.cuda.synchronize()
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1), kern_ms], dtype=torch.float64, device='cuda')
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    last = int(tok.item())
+    tpd.close()
+    ms_tok = float(t[0]) / ntok
+    pk, kind = peaks()
+    bytes_tok = weight_bytes(cfg) + kv_bytes(cfg, cfg.ctx + warm + ntok / 2)
+    gbs = bytes_tok / (ms_tok / 1e3) / 1e9
+    return {'metric': 'decode_tokens_per_s', 'value': 1e3 / ms_tok, 'unit': 'tok/s', 'scaling': 'strong', 'n_gpus': world, 'ms_per_token': ms_tok,
+            'kernel_ms_per_token': float(t[1]) / ntok, 'launches_per_token': 3 * len(tpd.handles), 'allreduces_per_token': 2 * cfg.layers, 'tokens': ntok, 'last_token': last,
+            'workload': f'{args.decode_model} batch 1 context {cfg.ctx}, tensor parallel over {world} GPUs (heads / FFN columns / vocabulary split), seeded shards',
+            'roofline': {'bound': 'hbm', 'achieved': gbs, 'unit': 'GB/s', 'peak': world * pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
+                         'frac': gbs / (world * pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])), 'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs x {world} GPUs'}}
 
 
 def run_decode(args, device):

@@ -172,3 +172,102 @@ def build_decode(c: DecodeConfig) -> Graph:
         g.task('argmax', {'logits': logits[u], 'out': tok[u], 'r0': 0, 'r1': 1, 'V': V}, [logits[u]], [tok[u]], 1, T[u] + 'argmax')
         g.task('counter_inc', {'x': lens[u], 'i0': 0, 'i1': 1, 'delta': 1}, [lens[u]], [lens[u]], 0, T[u] + 'advance')
     return g
+
+
+def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False):
+    """Rank `rank`'s share of the one-token graph under tensor parallelism over `world` ranks, batch 1.
+
+    q / k / v / gate / up are sharded by output rows (heads, FFN columns), the o and down projections by input columns, the
+    LM head by vocabulary rows; the KV cache holds the rank's kv heads.  The o and down projections therefore produce partial
+    sums `[1, hidden]` that must be added over the ranks (the residual rides on rank 0's partial), which cuts the token into
+    2 * layers + 1 segments.  Returns (graph, cuts, exchanges): cuts[i] = first task of segment i, exchanges[i] = name of the
+    buffer to sum over the ranks after segment i (None after the last one, whose `logits` hold the rank's vocabulary slice).
+    exact=True takes every shard as a slice of the full model's seeded weights (small configurations, parity tests);
+    otherwise the shards are seeded on their own (same shapes and traffic, a different random model).
+    """
+    from .. import initgen
+    P = world
+    d, H, Hkv, hd, F, V, S = c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.splits
+    assert c.batch == 1 and H % P == 0 and Hkv % P == 0 and F % P == 0 and V % P == 0, 'heads, kv heads, ffn and vocab must divide by the ranks'
+    Hl, Hkvl, Fl, Vl, G = H // P, Hkv // P, F // P, V // P, H // Hkv
+    g = Graph('decode_tp')
+    g.join_threshold = c.join_threshold
+    seed_of = lambda name: zlib.crc32(f'{c.seed}/{name}'.encode())
+
+    def full(name, n, k, scale):
+        draws, bias, coef = initgen.seeded_params('normal', scale)
+        return initgen.seeded_values(seed_of(name), n * k, draws, bias, coef).reshape(n, k)      # rounded to bf16 where it is stored
+
+    def W(name, n, k, rows=None, cols=None):
+        """bf16 weight shard: rows / cols = slice of the full [n, k] matrix held by this rank."""
+        r0, r1 = rows or (0, n)
+        c0, c1 = cols or (0, k)
+        if exact:
+            return g.data('wb.' + name, np.ascontiguousarray(full(name, n, k, c.init_std)[r0:r1, c0:c1]), 'bf16')
+        return g.buffer('wb.' + name, r1 - r0, c1 - c0, 'bf16', {'kind': 'seeded', 'seed': seed_of(f'{name}/{rank}'), 'scale': c.init_std, 'dist': 'normal'})
+
+    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20, rows=None):
+        rows = rows or max(8, -(-n // c.workers)) if c.rows_per_task <= 0 else c.rows_per_task
+        for i, n0 in enumerate(range(0, n, rows)):
+            n1 = min(n0 + rows, n)
+            g.task('gemv_bf16', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
+                   [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{i}')
+
+    W('embed', V, d)
+    g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
+    W('head', V, d, rows=(rank * Vl, (rank + 1) * Vl))
+    lens = g.buffer('u0.lens', 1, 1, 'i32', {'kind': 'fill', 'value': c.ctx})
+    tok = g.buffer('u0.tok', 1, 1, 'i32', {'kind': 'fill', 'value': 3 % V})
+    x = g.buffer('u0.x', 1, d)
+    cuts, exchanges = [0], []
+    g.task('gather_rows', {'src': 'wb.embed', 'idx': tok, 'dst': x, 'r0': 0, 'r1': 1, 'd': d}, ['wb.embed', tok], [x], 31, 'u0.embed')
+    for l in range(c.layers):
+        p, tl = f'l{l}.', f'u0.l{l}.'
+        prio = max(30 - l, 2)
+        ln1 = g.buffer('w.' + p + 'ln1', 1, d, init={'kind': 'fill', 'value': 1.0})
+        ln2 = g.buffer('w.' + p + 'ln2', 1, d, init={'kind': 'fill', 'value': 1.0})
+        wq = W(p + 'q', H * hd, d, rows=(rank * Hl * hd, (rank + 1) * Hl * hd))
+        wk = W(p + 'k', Hkv * hd, d, rows=(rank * Hkvl * hd, (rank + 1) * Hkvl * hd))
+        wv = W(p + 'v', Hkv * hd, d, rows=(rank * Hkvl * hd, (rank + 1) * Hkvl * hd))
+        wo = W(p + 'o', d, H * hd, cols=(rank * Hl * hd, (rank + 1) * Hl * hd))
+        wg = W(p + 'gate', F, d, rows=(rank * Fl, (rank + 1) * Fl))
+        wu = W(p + 'up', F, d, rows=(rank * Fl, (rank + 1) * Fl))
+        wd = W(p + 'down', d, F, cols=(rank * Fl, (rank + 1) * Fl))
+        # the cache of the rank's kv heads: a slice (by head) of the full model's seeded cache when exact
+        if exact:
+            cache = lambda n: g.data(tl + n, np.ascontiguousarray(full(f'u0.l{l}.{n}', Hkv * c.tmax, hd, 1.0)[rank * Hkvl * c.tmax:(rank + 1) * Hkvl * c.tmax]), 'bf16')
+        else:
+            cache = lambda n: g.buffer(tl + n, Hkvl * c.tmax, hd, 'bf16', {'kind': 'seeded', 'seed': seed_of(f'{tl}{n}/{rank}'), 'scale': 1.0, 'dist': 'normal'})
+        kc, vc = cache('kc'), cache('vc')
+        q, k, v = g.buffer(tl + 'q', 1, Hl * hd), g.buffer(tl + 'k', 1, Hkvl * hd), g.buffer(tl + 'v', 1, Hkvl * hd)
+        rq = max(8, -(-(Hl + 2 * Hkvl) * hd // c.workers))
+        gemv(tl + 'q', x, wq, q, Hl * hd, d, 1, gamma=ln1, prio=prio, rows=rq)
+        gemv(tl + 'k', x, wk, k, Hkvl * hd, d, 1, gamma=ln1, prio=prio, rows=rq)
+        gemv(tl + 'v', x, wv, v, Hkvl * hd, d, 1, gamma=ln1, prio=prio, rows=rq)
+        part, o = g.buffer(tl + 'part', S * Hl, hd + 2), g.buffer(tl + 'o', 1, Hl * hd)
+        slice_ = c.tmax // S
+        for kvh in range(Hkvl):
+            for s in range(S):
+                rows = (kvh * c.tmax + s * slice_, kvh * c.tmax + (s + 1) * slice_)
+                g.task('attn_decode_part', {'q': q, 'kc': kc, 'vc': vc, 'lens': lens, 'part': part, 'knew': k, 'vnew': v, 'b': 0, 'kvh': kvh, 's': s, 'S': S, 'H': Hl,
+                                            'Hkv': Hkvl, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
+                       [q, k, v, lens], [(kc, rows), (vc, rows), (part, (s * Hl + kvh * G, s * Hl + (kvh + 1) * G))], prio, f'{tl}part.{kvh}.{s}')
+        for kvh in range(Hkvl):
+            g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': Hl, 'hd': hd},
+                   [part], [(o, (0, 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{tl}merge.{kvh}')
+        x1 = g.buffer(tl + 'x1', 1, d)               # partial sum of the o projection (+ residual on rank 0); summed over the ranks after the segment
+        gemv(tl + 'o', o, wo, x1, d, Hl * hd, 0, res=x if rank == 0 else None, prio=prio)
+        cuts.append(len(g.tasks)); exchanges.append(x1)
+        gate, up = g.buffer(tl + 'gate', 1, Fl), g.buffer(tl + 'up', 1, Fl)
+        rgu = max(8, -(-2 * Fl // c.workers))
+        gemv(tl + 'gate', x1, wg, gate, Fl, d, 1, gamma=ln2, prio=prio, rows=rgu)
+        gemv(tl + 'up', x1, wu, up, Fl, d, 1, gamma=ln2, prio=prio, rows=rgu)
+        xn = g.buffer(tl + 'x2', 1, d)
+        gemv(tl + 'down', gate, wd, xn, d, Fl, 2, x2=up, res=x1 if rank == 0 else None, prio=prio)
+        cuts.append(len(g.tasks)); exchanges.append(xn)
+        x = xn
+    logits = g.buffer('u0.logits', 1, Vl)
+    gemv('u0.head', x, 'wb.head', logits, Vl, d, 1, gamma='w.lnf', prio=1, rows=max(8, -(-Vl // (2 * c.workers))))
+    g.task('counter_inc', {'x': lens, 'i0': 0, 'i1': 1, 'delta': 1}, [lens], [lens], 0, 'u0.advance')
+    exchanges.append(None)
+    return g, cuts, exchanges

@@ -231,6 +231,19 @@ class Graph:
         second._pubs = {v: self._pubs[v] - base[v] for v in self.variables}
         return first.to_bundle(), second.to_bundle()
 
+    def to_bundles_multi(self, cuts):
+        """One bundle per segment [cuts[i], cuts[i+1]) over the same buffer table, to be run one after the other (an exchange with
+        other ranks sits between them): edges from earlier segments are dropped.  For graphs without version publishes."""
+        import copy
+        assert not any(t['pub'] for t in self.tasks), 'segments of a graph with publishes need renumbering'
+        out, ends = [], list(cuts[1:]) + [len(self.tasks)]
+        for a, b in zip(cuts, ends):
+            seg = copy.copy(self)
+            seg.tasks = [dict(t) for t in self.tasks[a:b]]
+            seg.preds = [[p - a for p in ps if p >= a] for ps in self.preds[a:b]]
+            out.append(seg.to_bundle())
+        return out
+
     def to_spec(self) -> dict:
         """The same program as workload JSON (`FRAMEWORK.md:27-60` of the reference): what its compiler takes."""
         tasks = []
