@@ -386,13 +386,17 @@ def run_decode_tp(args, rank, world, device):
     tok = torch.full((1, 1), 3, dtype=torch.int32, device='cuda')
     bind = {n: t.data_ptr() for n, t in bufs.items()}
     bind.update({'u0.logits': logits.data_ptr(), 'u0.tok': tok.data_ptr()})
-    tpd = TensorParallelDecode(cfg, rank, world, device, bind)
+    from kvm_b200.executor import CFG_CHAIN
+    tpd = TensorParallelDecode(cfg, rank, world, device, bind, flags=CFG_CHAIN)
     comm = {'n': 0}
 
-    def all_reduce_sum(name):
+    def all_reduce_sum(name):           # first tokens: launches on the handles' own streams, so the host waits for the collective
         dist.all_reduce(bufs[name], op=dist.ReduceOp.SUM)
         torch.cuda.current_stream().synchronize()
         comm['n'] += 1
+
+    def all_reduce_queued(name):        # timed tokens: everything is queued on one stream, stream order is the only synchronisation
+        dist.all_reduce(bufs[name], op=dist.ReduceOp.SUM)
 
     def choose():
         val, idx = logits.max(dim=1)
@@ -406,15 +410,16 @@ def run_decode_tp(args, rank, world, device):
     ntok, warm = min(args.decode_tokens, 8), 2
     for _ in range(warm):
         tpd.token(all_reduce_sum, choose)
+    tpd.use_stream(torch.cuda.current_stream().cuda_stream)
+    tpd.token_async(all_reduce_queued, choose)
     dist.barrier(); torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    kern_ms = 0.0
     for _ in range(ntok):
-        kern_ms += tpd.token(all_reduce_sum, choose)
-    torch.cuda.synchronize()
+        tpd.token_async(all_reduce_queued, choose)
     e1.record(); torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1), kern_ms], dtype=torch.float64, device='cuda')
+    kern_ms = sum(tpd.finish())         # kernel time of the last token's segments
+    t = torch.tensor([e0.elapsed_time(e1), kern_ms * ntok], dtype=torch.float64, device='cuda')
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     last = int(tok.item())
     tpd.close()

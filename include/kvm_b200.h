@@ -40,7 +40,8 @@ typedef struct KvmConfig {
     int32_t flags;         /* KVM_CFG_* */
 } KvmConfig;
 enum { KVM_CFG_NO_TENSOR_CORES = 1, /* run every GEMM on the SIMT reference path (debugging / bit-exact f32) */
-       KVM_CFG_PAIR_TILES = 2       /* run two row-adjacent tensor-core GEMM tiles of one product as one 256 x 256 tile when both are ready */ };
+       KVM_CFG_PAIR_TILES = 2,      /* run two row-adjacent tensor-core GEMM tiles of one product as one 256 x 256 tile when both are ready */
+       KVM_CFG_CHAIN = 4            /* kvm_start may be called again before kvm_finish: the runs queue up on the stream (first device error is kept) */ };
 
 /* Buffer initial value (mvm_exec.cu:1915-1929 buffer init kinds; `file` inits are read by the caller and passed as VALUES). */
 typedef struct KvmInit {
@@ -94,6 +95,10 @@ int kvm_submit_bundle_dir(KvmExec* h, const char* dir);
 /* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over everything submitted since the last run.
  * kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
 int kvm_start(KvmExec* h);
+/* Run on the caller's CUDA stream (a cudaStream_t) from now on, so that launches order with the caller's own work - collectives
+ * between segments of a tensor-parallel token - without host synchronisation.  No counterpart in the reference (its executor
+ * owns one non-blocking stream, mvm_exec.cu:546).  The stream is not destroyed by kvm_destroy. */
+int kvm_set_stream(KvmExec* h, void* stream);
 int kvm_finish(KvmExec* h, KvmResult* res);
 int kvm_run(KvmExec* h, KvmResult* res);
 /* Re-arm the submitted tasks (dependency counters, queue, per-task records) so the same program runs again on the current

@@ -33,6 +33,7 @@ struct KvmExec {
   int* d_versions = nullptr; int* d_park_head = nullptr; int* d_ver_base = nullptr; int* d_ver_off = nullptr;
   KvmErrRec* d_err = nullptr;
   bool started = false, armed = false;
+  bool own_stream = true;        // false after kvm_set_stream: the caller's stream is used and never destroyed here
   KvmResult last{};
 };
 
@@ -107,7 +108,7 @@ extern "C" void kvm_destroy(KvmExec* h) {
   for (void* p : {(void*)h->d_bufs, (void*)h->d_ctl, (void*)h->d_versions, (void*)h->d_park_head, (void*)h->d_ver_base, (void*)h->d_ver_off, (void*)h->d_err}) if (p) cudaFree(p);
   if (h->ev0) cudaEventDestroy(h->ev0);
   if (h->ev1) cudaEventDestroy(h->ev1);
-  if (h->stream) cudaStreamDestroy(h->stream);
+  if (h->stream && h->own_stream) cudaStreamDestroy(h->stream);
   delete h;
 }
 
@@ -391,10 +392,27 @@ extern "C" int kvm_rearm(KvmExec* h) {
   return kvm_prepare(h);
 }
 
+extern "C" int kvm_set_stream(KvmExec* h, void* stream) {
+  if (!h) return KVM_E_ARG;
+  if (h->started) { h->error = "kvm_set_stream: a run is in flight"; return KVM_E_STATE; }
+  cudaSetDevice(h->device);
+  cudaStreamSynchronize(h->stream);
+  if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
+  h->stream = (cudaStream_t)stream;
+  h->own_stream = false;
+  return 0;
+}
+
 extern "C" int kvm_start(KvmExec* h) {
   if (!h) return KVM_E_ARG;
-  if (h->started) { h->error = "kvm_start: already started"; return KVM_E_STATE; }
-  if (!h->armed) if (int r = kvm_prepare(h)) return r;
+  bool chained = false;
+  if (h->started) {
+    // KVM_CFG_CHAIN: the next run is queued behind the previous one on the same stream without reading its result back
+    // (segments of one token with collectives between them); the device's first error stays recorded across the chain.
+    if (!(h->cfg.flags & KVM_CFG_CHAIN)) { h->error = "kvm_start: already started"; return KVM_E_STATE; }
+    chained = true; h->armed = false;
+  }
+  if (!h->armed) if (int r = kvm_prepare(h, chained)) return r;
   KvmDevState S = kvm_dev_state(h);
   KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
   kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);

@@ -366,9 +366,9 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       }
       // 3. termination / failure / stall
       if (!progressed) {
-        // An idle worker mostly watches its ring cell (step 2); the global done / error words are looked at every 8th idle pass,
-        // so a newly pushed task is picked up within one cell poll rather than behind three dependent global loads.
-        if ((++polls & 7u) == 0 || stop) {
+        // An idle worker mostly watches the queue (step 2); the global done / error words are looked at every 2nd idle pass: often
+        // enough that a short launch (one segment of a tensor-parallel token) does not sit idle for microseconds before it ends.
+        if ((++polls & 1u) == 0 || stop) {
           int d = 0, e = 0;
           if (lane == 0) { d = kvm_ld_acquire(S.done); e = *(volatile int*)&S.err->code; }
           d = __shfl_sync(0xffffffffu, d, 0); e = __shfl_sync(0xffffffffu, e, 0);

@@ -21,6 +21,7 @@ _lib = None
 INIT_FILL, INIT_VALUES, INIT_SEEDED, INIT_NONE = 0, 1, 2, 3
 CFG_NO_TENSOR_CORES = 1
 CFG_PAIR_TILES = 2
+CFG_CHAIN = 4
 
 
 class KvmError(RuntimeError):
@@ -59,6 +60,7 @@ SYMBOLS = {
     'kvm_submit': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]),
     'kvm_submit_bundle_dir': (C.c_int, [C.c_void_p, C.c_char_p]),
     'kvm_start': (C.c_int, [C.c_void_p]),
+    'kvm_set_stream': (C.c_int, [C.c_void_p, C.c_void_p]),
     'kvm_finish': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
     'kvm_run': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
     'kvm_run_steps': (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(KvmResult)]),
@@ -252,6 +254,10 @@ class Executor:
 
     def start(self):
         self._check(self.L.kvm_start(self._h))
+
+    def set_stream(self, cuda_stream: int):
+        """Launch on the caller's stream (a cudaStream_t value, e.g. torch.cuda.current_stream().cuda_stream) from now on."""
+        self._check(self.L.kvm_set_stream(self._h, C.c_void_p(cuda_stream)))
 
     def finish(self, check=True) -> KvmResult:
         res = KvmResult()

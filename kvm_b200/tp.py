@@ -63,6 +63,25 @@ class TensorParallelDecode:
         choose()
         return ms
 
+    def use_stream(self, cuda_stream: int):
+        """Put every handle on the caller's stream (needs the handles created with flags=CFG_CHAIN): token_async then needs no host
+        synchronisation between segments."""
+        for ex in self.handles:
+            ex.set_stream(cuda_stream)
+
+    def token_async(self, all_reduce_sum, choose):
+        """One decode step queued on the shared stream: launches and collectives follow each other in stream order; `choose` ends
+        with whatever synchronisation the token read-back needs."""
+        for ex, name in zip(self.handles, self.exchanges):
+            ex.start()
+            if name is not None:
+                all_reduce_sum(name)
+        choose()
+
+    def finish(self):
+        """Collect the last results of every handle (raises on a recorded device error); returns their kernel times in ms."""
+        return [ex.finish().ms for ex in self.handles]
+
     def close(self):
         for ex in reversed(self.handles):
             ex.close()
