@@ -110,7 +110,22 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
     const float rs = 1.0f / sqrtf(q / K + eps);
     for (int k = tid; k < K; k += KVM_NT) vs[k] = kvm_bf16_round(vs[k] * rs * ((const float*)gm.p)[k]);
   } else {
-    for (int k = tid; k < K; k += KVM_NT) { const float t = kvm_ld(x, k); vs[k] = kvm_bf16_round(pro == 2 ? kvm_silu(t) * kvm_ld(x2, k) : t); }
+    // eight elements per thread at a time, all loads before the first store: a store to shared memory between two global loads
+    // would keep the second from being issued early (the compiler cannot prove the pointers apart), one round trip per element
+    for (int k0 = 0; k0 < K; k0 += 8 * KVM_NT) {
+      float a[8], b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + tid + u * KVM_NT;
+        a[u] = k < K ? kvm_ld(x, k) : 0.0f;
+        b[u] = (pro == 2 && k < K) ? kvm_ld(x2, k) : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + tid + u * KVM_NT;
+        if (k < K) vs[k] = kvm_bf16_round(pro == 2 ? kvm_silu(a[u]) * b[u] : a[u]);
+      }
+    }
   }
   kvm_sync();
 

@@ -60,15 +60,16 @@ PRESETS = {
     'gpt_tiny': GPTConfig(),
     'gpt_micro': GPTConfig(name='gpt_micro', layers=1, d_model=32, heads=2, d_ff=64, vocab=64, seq=16, batch=2, norm_rows=8, ce_rows=8,
                            flat_chunk=1024, col_chunk=16, key_chunk=32),
-    # BASELINE config 3
+    # BASELINE config 3.  norm_rows 64: a norm / attention-delta phase of 8192 rows is 128 tasks, one wave over the SMs (16-row tasks
+    # were mostly fixed cost: 512 tasks of 10 us per phase)
     'gpt_162m': GPTConfig(name='gpt_162m', layers=12, d_model=768, heads=12, d_ff=3072, vocab=50304, seq=1024, batch=8, tied=False,
-                          precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144),
+                          precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
     # the 162M shapes at a size an ncu capture replays in seconds (2 layers, micro-batch 4): same tiles, same op mix
     'gpt_162m_2l': GPTConfig(name='gpt_162m_2l', layers=2, d_model=768, heads=12, d_ff=3072, vocab=50304, seq=1024, batch=4, tied=False,
-                             precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144),
+                             precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
     # BASELINE config 4
     'gpt_355m': GPTConfig(name='gpt_355m', layers=24, d_model=1024, heads=16, d_ff=4096, vocab=50304, seq=1024, batch=8, tied=False,
-                          precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144),
+                          precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
 }
 
 
