@@ -75,6 +75,38 @@ __device__ void kvm_op_attn_bwd_delta(const KvmCtx& c, const int32_t* a) {
   if (r0 < 0 || r1 < r0 || T <= 0 || H <= 0 || hd <= 0 || !kvm_mat_ok(c, o, r1, H * hd) || !kvm_mat_ok(c, dO, r1, H * hd) ||
       !kvm_flat_ok(c, delta, (long long)((r1 + T - 1) / T) * H * T)) { c.fail(KVM_OPE_RANGE, r0, r1); return; }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if ((hd == 64 || hd == 128 || hd == 32) && (o.ld & 7) == 0 && (dO.ld & 7) == 0 && kvm_vec_ok(o) && kvm_vec_ok(dO)) {
+    // vector form: an item is 8 consecutive columns of one row (hd/8 neighbouring lanes make up a head); four items per thread
+    // are loaded before any of them is reduced, so the loads of a task overlap instead of queueing behind each other's stores
+    const int cpr = H * hd / 8, lph = hd / 8;                 // items per row, lanes per head
+    const long long items = (long long)(r1 - r0) * cpr;
+    for (long long i0 = 0; i0 < items; i0 += 4LL * KVM_NT) {
+      float ov[4][8], dv[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long it = i0 + (long long)u * KVM_NT + threadIdx.x;
+        if (it < items) {
+          const int r = r0 + (int)(it / cpr), cc = (int)(it % cpr) * 8;
+          kvm_ld8(o, (size_t)r * o.ld + cc, ov[u]); kvm_ld8(dO, (size_t)r * dO.ld + cc, dv[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long it = i0 + (long long)u * KVM_NT + threadIdx.x;      // KVM_NT and cpr are multiples of hd/8: a head never straddles warps or steps
+        float s = 0.0f;
+        if (it < items) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += ov[u][j] * dv[u][j];
+        }
+        for (int w = lph >> 1; w; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+        if (it < items && (lane % lph) == 0) {
+          const int r = r0 + (int)(it / cpr), h = (int)(it % cpr) / lph;
+          ((float*)delta.p)[(size_t)((r / T) * H + h) * T + r % T] = s;
+        }
+      }
+    }
+    return;
+  }
   for (int e = warp; e < (r1 - r0) * H; e += KVM_NWARPS) {
     const int r = r0 + e / H, h = e % H;
     float s = 0.0f;

@@ -126,6 +126,46 @@ __device__ void kvm_norm_fwd(const KvmCtx& c, int xi, int gi, int bi, int oi, in
   const float* gp = (const float*)g.p;
   const float* bp = (const float*)be.p;
   const bool vec = (d & 7) == 0 && (x.ld & 7) == 0 && (out.ld & 7) == 0 && kvm_vec_ok(x) && kvm_vec_ok(out) && kvm_vec_ok(g) && (RMS || kvm_vec_ok(be));
+  if (vec && d <= 1024) {
+    // the row (up to four 8-element vectors per lane) is fetched once and stays in registers over the two reductions (gamma and
+    // beta come from L1 as vectors); same per-lane summation order as the loops below
+    for (int r = r0 + warp; r < r1; r += KVM_NWARPS) {
+      const size_t xo = (size_t)r * x.ld, oo = (size_t)r * out.ld;
+      float xv[4][8], s = 0.0f, q = 0.0f;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) { const int k = lane * 8 + t * 256; if (k < d) kvm_ld8(x, xo + k, xv[t]); }
+      if (!RMS) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) if (lane * 8 + t * 256 < d) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += xv[t][j];
+        }
+        s = kvm_warp_sum(s);
+      }
+      const float mu = RMS ? 0.0f : s / d;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) if (lane * 8 + t * 256 < d) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float tt = xv[t][j] - mu; q += tt * tt; }
+      }
+      q = kvm_warp_sum(q);
+      const float rs = 1.0f / sqrtf(q / d + eps);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int k = lane * 8 + t * 256;
+        if (k < d) {
+          float ov[8], gv[8], bv[8];
+          kvm_ld8(g, k, gv);
+          if (!RMS) kvm_ld8(be, k, bv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ov[j] = (xv[t][j] - mu) * rs * gv[j] + (RMS ? 0.0f : bv[j]);
+          kvm_st8(out, oo + k, ov);
+        }
+      }
+      if (lane == 0) { ((float*)rstd.p)[r] = rs; if (!RMS) ((float*)mean.p)[r] = mu; }
+    }
+    return;
+  }
   for (int r = r0 + warp; r < r1; r += KVM_NWARPS) {
     const size_t xo = (size_t)r * x.ld, oo = (size_t)r * out.ld;
     float s = 0.0f;
