@@ -50,6 +50,8 @@ __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& 
   const int rows = n1 - n0;
   int R = KVM_GS_UNITS;
   while (R > 1 && R * K * 2 > KVM_GS_STAGE_MAX) R >>= 1;
+  // at least three stages in flight where the scratch allows: smaller stages (fewer rows each) rather than a two-deep ring
+  while (R > 1 && (c.smem_bytes - ((256 + K * 4 + 256 + ((rows + 7) & ~7) * (KVM_GS_UNITS / R) * 4 + 127) & ~127)) / ((R * K * 2 + 127) & ~127) < 3) R >>= 1;
   const int KP = KVM_GS_UNITS / R, stage_bytes = (R * K * 2 + 127) & ~127;
   const int plen = (((K + KP - 1) / KP) + 255) & ~255;                      // k extent of one part
   const int fixed = (256 + K * 4 + 256 + ((rows + 7) & ~7) * KP * 4 + 127) & ~127;

@@ -33,6 +33,7 @@ struct KvmExec {
   int* d_versions = nullptr; int* d_park_head = nullptr; int* d_ver_base = nullptr; int* d_ver_off = nullptr;
   KvmErrRec* d_err = nullptr;
   bool started = false, armed = false;
+  bool has_gemv = false;         // a submitted task is a gemv_bf16: its shared-memory ring is worth more than the buffer-table cache
   bool own_stream = true;        // false after kvm_set_stream: the caller's stream is used and never destroyed here
   KvmResult last{};
 };
@@ -313,7 +314,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.t_start = h->d_tstart; S.t_end = h->d_tend; S.t_smid = h->d_tsmid; S.trace = h->cfg.trace;
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
   S.cfg_flags = h->cfg.flags;
-  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim;
+  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim; S.buf_cache = h->has_gemv ? 0 : 1;
   { const char* v = getenv("KVM_B200_PAIR_DEPTH"); S.pair_depth = v && *v ? atoi(v) : 2 * h->workers; }
   return S;
 }
@@ -357,11 +358,13 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     }
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
+    h->has_gemv = false;
     {   // one record per task for the workers: descriptor, argument words and path selector side by side (a single fetch per pop)
       std::vector<int32_t> recs(nt * (size_t)KVM_REC_WORDS, 0);
       for (size_t i = 0; i < nt; ++i) {
         int32_t* r = &recs[i * KVM_REC_WORDS];
         memcpy(r, &h->tasks[i], sizeof(KvmTaskDesc));
+        if (r[0] == 134) h->has_gemv = true;
         const int ao = r[6], aw = r[7] < KVM_MAX_ARGS ? r[7] : KVM_MAX_ARGS;
         for (int k = 0; k < aw; ++k) r[16 + k] = h->args[(size_t)ao + k];
         memcpy(r + 16 + KVM_MAX_ARGS, &h->aux[i], sizeof(int4));

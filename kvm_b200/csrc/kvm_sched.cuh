@@ -45,6 +45,7 @@ struct KvmDevState {
   const void* tmaps;          // CUtensorMap table for tensor-core tasks
   const int4* task_aux;       // per task: tensor-map indices / path selector
   const int32_t* recs;        // per task KVM_REC_WORDS words: descriptor [0,16), argument words [16,36), path selector [36,40)
+  int buf_cache;              // 1: copy the buffer table into shared memory at launch (off for graphs of streaming GEMVs, which want the space)
   int pair_depth;             // tiles are stacked only while at least this many tasks are queued (wide phases; narrow ones keep their parallelism)
   int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
 };
@@ -187,6 +188,7 @@ __global__ void kvm_roots_kernel(KvmDevState S) {
 __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* args, const int4& aux);
 
 #define KVM_EXEC_SMEM_HDR 1024     // slots + control words at the start of dynamic shared memory
+#define KVM_BUFCACHE_BYTES 32768    // shared-memory copy of the buffer table (up to 1024 buffers), after the header
 
 // The scheduler warp's share of finishing `task`: publish its version, then release its successors.
 // The successors are taken eight per lane at a time and every step is done for all of them before the next one starts: the
@@ -279,6 +281,15 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
   unsigned dyn;
   asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   kvm_tc_init(ctl, kvm_smem);                          // TMEM allocation + mbarrier init (whole CTA)
+  // The buffer table is copied into shared memory once per launch when it fits: every task starts by looking up its buffers, and
+  // from here that is a shared-memory read instead of a round trip to L2.
+  const int cache_bytes = (int)(((size_t)S.nbufs * sizeof(KvmBuf) + 1023) & ~(size_t)1023);      // whole KB: the op scratch keeps its 1024-byte alignment
+  const bool buf_cache = S.buf_cache && cache_bytes <= KVM_BUFCACHE_BYTES && dyn >= KVM_EXEC_SMEM_HDR + KVM_BUFCACHE_BYTES + 192 * 1024;
+  if (buf_cache) {
+    const uint4* src = (const uint4*)S.bufs;
+    uint4* dst = (uint4*)(kvm_smem + KVM_EXEC_SMEM_HDR);
+    for (int i = tid; i < S.nbufs * 2; i += KVM_NT + 32) dst[i] = src[i];
+  }
   __syncthreads();
   const unsigned long long t_begin = kvm_globaltimer();
 
@@ -386,8 +397,10 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
     if (lane == 0) { slots[fill].task = -1; __threadfence_block(); slots[fill].state = 1; }
   } else {
     KvmCtx c;
-    c.bufs = S.bufs; c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps;
-    c.smem = kvm_smem + KVM_EXEC_SMEM_HDR; c.smem_bytes = (int)dyn - KVM_EXEC_SMEM_HDR;
+    c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps;
+    c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_EXEC_SMEM_HDR) : S.bufs;
+    const int used = KVM_EXEC_SMEM_HDR + (buf_cache ? cache_bytes : 0);
+    c.smem = kvm_smem + used; c.smem_bytes = (int)dyn - used;
     int cur = 0;
     while (true) {
       KvmSlot& sl = slots[cur];
