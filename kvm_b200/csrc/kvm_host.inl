@@ -314,7 +314,7 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.t_start = h->d_tstart; S.t_end = h->d_tend; S.t_smid = h->d_tsmid; S.trace = h->cfg.trace;
   S.timeout_ns = (unsigned long long)(h->cfg.timeout_ms > 0 ? h->cfg.timeout_ms : 20000) * 1000000ull;
   S.cfg_flags = h->cfg.flags;
-  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim; S.buf_cache = h->has_gemv ? 0 : 1;
+  S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim; S.buf_cache = kvm_feature_on("KVM_B200_BUFCACHE", h->has_gemv ? 0 : 1) ? 1 : 0;
   { const char* v = getenv("KVM_B200_PAIR_DEPTH"); S.pair_depth = v && *v ? atoi(v) : 2 * h->workers; }
   return S;
 }

@@ -66,7 +66,7 @@ PRESETS = {
                           precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
     # the 162M shapes at a size an ncu capture replays in seconds (2 layers, micro-batch 4): same tiles, same op mix
     'gpt_162m_2l': GPTConfig(name='gpt_162m_2l', layers=2, d_model=768, heads=12, d_ff=3072, vocab=50304, seq=1024, batch=4, tied=False,
-                             precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
+                             precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=32),
     # BASELINE config 4
     'gpt_355m': GPTConfig(name='gpt_355m', layers=24, d_model=1024, heads=16, d_ff=4096, vocab=50304, seq=1024, batch=8, tied=False,
                           precision='bf16', lr=6e-4, wd=0.1, flat_chunk=262144, norm_rows=64),
