@@ -69,3 +69,24 @@ def test_rearmed_template_equals_unrolled_steps(kvm_lib):
     for s in range(3):
         ref = float(vm.buffer(f'loss.{s}').a[0, 0])
         assert abs(losses[s] - ref) <= 1e-5 * abs(ref), (s, losses[s], ref)
+
+
+def test_device_error_first_wins_and_run_ends(kvm_lib):
+    """A task whose arguments point outside its buffer fails on the device with the op-pack range code, touches nothing, the
+    launch still ends, and the host reports code, task and detail (first error wins)."""
+    from kvm_b200.executor import Executor, KvmError
+    from kvm_b200.workloads.graph import Graph
+    g = Graph('bad')
+    x = g.buffer('x', 1, 64, init={'kind': 'fill', 'value': 1.0})
+    y = g.buffer('y', 1, 64, init={'kind': 'fill', 'value': 7.0})
+    g.task('scale_flat', {'x': x, 'out': y, 'alpha': 2.0, 'e0': 0, 'e1': 32}, [x], [(y, (0, 1), (0, 32))], 5, 'good')
+    g.task('scale_flat', {'x': x, 'out': y, 'alpha': 2.0, 'e0': 32, 'e1': 4096}, [x], [(y, (0, 1), (32, 64))], 5, 'bad')
+    b = g.to_bundle(check=False)
+    with Executor() as ex:
+        ex.load(b)
+        res = ex.run(check=False)
+        assert res.status == 1003 and res.err_task == 1, (res.status, res.err_task)       # E_RANGE at the second task
+        with pytest.raises(KvmError):
+            ex.run()
+        out = ex.read_buffer('y')
+        assert (out[0, 32:] == 7.0).all()          # the failing task wrote nothing
