@@ -145,6 +145,68 @@ __device__ __forceinline__ void kvm_tc_store32(const KvmMmArgs& g, const float (
   }
 }
 
+// Epilogue of one 128 x 256 accumulator through shared memory, so that every global access is a whole contiguous row segment:
+//   phase 1  warp (q = w & 3, cg = w >> 2) reads TMEM lanes 32q.. / columns 64cg.. and parks the raw float32 sums in a staging tile
+//            (row pitch 1040 bytes: eight rows of one 16-byte column piece fall into different banks)
+//   phase 2  thread = (row, 8 consecutive columns), a warp = one row of 256 columns: scale, bias, pre-activation / GELU, residual,
+//            accumulate and the store (f32 or bf16) all touch 512 or 1024 contiguous bytes per warp instruction
+// `stage` is the operand ring (free once the accumulator is complete).  Falls back to the element-wise epilogue for geometry the
+// vector accesses cannot take.  Whole compute group; ends with the group in step (kvm_sync).
+#define KVM_TC_EPI_PITCH 260          // floats per staged row
+__device__ __forceinline__ bool kvm_tc_epi_vec_ok(const KvmMmArgs& g) {
+  return (g.out.ld & 7) == 0 && kvm_vec_ok(g.out) && (g.n0 & 7) == 0 && (!g.res.p || ((g.res.ld & 7) == 0 && kvm_vec_ok(g.res))) &&
+         (!g.pre.p || ((g.pre.ld & 7) == 0 && kvm_vec_ok(g.pre))) && (!g.bias.p || (((uintptr_t)g.bias.p & 15) == 0));
+}
+__device__ void kvm_tc_epilogue_staged(const KvmCtx& c, const KvmMmArgs& g, uint32_t tmem_acc, int m_base, bool ok) {
+  float* T = (float*)c.smem;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = warp & 3, cgi = warp >> 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int col = cgi * 64 + h * 32;
+    float acc[32];
+    kvm_tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)col, acc);
+    float* dst = T + (size_t)(q * 32 + lane) * KVM_TC_EPI_PITCH + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+  }
+  kvm_tc_fence_before();
+  kvm_sync();
+  if (ok) {
+    const bool simple = !(g.flags & 512);
+    const float* bias = (const float*)g.bias.p;
+    for (int item = threadIdx.x; item < 128 * 32; item += KVM_NT) {
+      const int r = item >> 5, cc = (item & 31) * 8, m = m_base + r, n = g.n0 + cc;
+      if (m >= g.M || n >= g.N) continue;
+      const float* src = T + (size_t)r * KVM_TC_EPI_PITCH + cc;
+      float v[8];
+      *(float4*)v = *(const float4*)src; *(float4*)(v + 4) = *(const float4*)(src + 4);
+      if (n + 8 <= g.N && simple) {
+        float t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= g.alpha;
+        if (bias) { *(float4*)t = *(const float4*)(bias + n); *(float4*)(t + 4) = *(const float4*)(bias + n + 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+        if (g.pre.p) kvm_st8(g.pre, (size_t)m * g.pre.ld + n, v);
+        if (g.flags & 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = kvm_gelu(v[j]);
+        }
+        if (g.res.p) { kvm_ld8(g.res, (size_t)m * g.res.ld + n, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+        if (g.flags & 4) { kvm_ld8(g.out, (size_t)m * g.out.ld + n, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+        kvm_st8(g.out, (size_t)m * g.out.ld + n, v);
+      } else {
+        for (int j = 0; j < 8 && n + j < g.N; ++j) kvm_st(g.out, (size_t)m * g.out.ld + n + j, kvm_mm_epilogue(g, v[j], m, n + j));
+      }
+    }
+  }
+  kvm_sync();
+}
+
 // Two stacked tiles (rows m0.. and m0+128.., same 256 columns) as one 256 x 256 product: both read the same B stage, so a
 // k-block moves 64 KB for two tiles instead of 96 KB, which is what the L2 -> shared-memory path of an SM can feed.
 // Three 64 KB stages [A0 16K | A1 16K | B 32K]; two float32 accumulators in TMEM (columns 0..255 and 256..511).
@@ -211,20 +273,25 @@ __device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const int4& 
   if (!kvm_mbar_wait(bar(6), (uint32_t)cA & 1)) ok = false;
   kvm_tc_fence_after();
   if (!ok && atomicCAS(&c.err->code, 0, KVM_ERR_TIMEOUT) == 0) { c.err->task = c.task; c.err->a = 1122; c.err->b = (int)threadIdx.x; }
-  const int q = warp & 3, cgi = warp >> 2;
+  if (kvm_tc_epi_vec_ok(g)) {
 #pragma unroll 1
-  for (int t = 0; t < 2; ++t) {
-    const int m = g.m0 + t * 128 + q * 32 + lane;
+    for (int t = 0; t < 2; ++t) kvm_tc_epilogue_staged(c, g, tmem + t * 256, g.m0 + t * 128, ok);
+  } else {
+    const int q = warp & 3, cgi = warp >> 2;
+#pragma unroll 1
+    for (int t = 0; t < 2; ++t) {
+      const int m = g.m0 + t * 128 + q * 32 + lane;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int col = cgi * 64 + h * 32;
-      float acc[32];
-      kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 256 + col), acc);
-      if (ok && m < g.M) kvm_tc_store32(g, acc, m, g.n0 + col);
+      for (int h = 0; h < 2; ++h) {
+        const int col = cgi * 64 + h * 32;
+        float acc[32];
+        kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 256 + col), acc);
+        if (ok && m < g.M) kvm_tc_store32(g, acc, m, g.n0 + col);
+      }
     }
+    kvm_tc_fence_before();
+    kvm_sync();
   }
-  kvm_tc_fence_before();
-  kvm_sync();
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int s = 0; s < KVM_TCP_STAGES; ++s) { const int uses = (num_kb - s + KVM_TCP_STAGES - 1) / KVM_TCP_STAGES; cnt[s] += uses; cnt[3 + s] += uses; }
@@ -294,16 +361,19 @@ __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const 
   if (!kvm_mbar_wait(kvm_bar_addr(ctl, 2 * KVM_TC_STAGES), acc_ph)) ok = false;
   kvm_tc_fence_after();
   if (!ok && atomicCAS(&c.err->code, 0, KVM_ERR_TIMEOUT) == 0) { c.err->task = c.task; c.err->a = 122; c.err->b = (int)threadIdx.x; }
-  const int q = warp & 3, cgi = warp >> 2;
-  const int m = g.m0 + q * 32 + lane;
+  if (kvm_tc_epi_vec_ok(g)) kvm_tc_epilogue_staged(c, g, tmem, g.m0, ok);
+  else {
+    const int q = warp & 3, cgi = warp >> 2;
+    const int m = g.m0 + q * 32 + lane;
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int col = cgi * 64 + h * 32;
-    float acc[32];
-    kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)col, acc);
-    if (ok && m < g.M) kvm_tc_store32(g, acc, m, g.n0 + col);
+    for (int h = 0; h < 2; ++h) {
+      const int col = cgi * 64 + h * 32;
+      float acc[32];
+      kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)col, acc);
+      if (ok && m < g.M) kvm_tc_store32(g, acc, m, g.n0 + col);
+    }
+    kvm_tc_fence_before();
+    kvm_sync();
   }
-  kvm_tc_fence_before();
-  kvm_sync();
   if (threadIdx.x == 0) ctl[KVM_CTL_ACC_PH] = (int)(acc_ph ^ 1);
 }
