@@ -138,7 +138,7 @@ def cpu_sample(bundle, cfg, seconds, threads=None):
     ops = bundle.tasks['op_id']
     kinds = [int(k) for k in np.unique(ops) if k != 0]
     rng = np.random.default_rng(0)
-    budget = seconds / max(len(kinds), 1)
+    per_kind = seconds / max(len(kinds), 1)
     total, ran, t_begin = 0.0, 0, time.perf_counter()
     for k in kinds:
         idx = np.flatnonzero(ops == k)
@@ -150,7 +150,7 @@ def cpu_sample(bundle, cfg, seconds, threads=None):
             vm.run_task(int(i))
             spent += time.perf_counter() - t0
             n += 1
-            if time.perf_counter() - t_kind > budget:
+            if time.perf_counter() - t_kind > per_kind:
                 break
         total += spent / n * len(idx)
         ran += n

@@ -7,7 +7,7 @@ from oracle.vm_np import VM
 
 # The key-projection bias has an exactly zero gradient (softmax is invariant to a per-query constant added to every score),
 # so its computed gradient is pure rounding noise, which AdamW then normalises to +-lr steps: no implementation agrees with
-# another on these four buffers (the reference judges post-AdamW weights by float64 replay for the same reason,
+# another on these four buffers (the reference checks post-AdamW weights by float64 replay for the same reason,
 # tests/gptdiff/golden_check.py:5-18).
 NOISE_ONLY = ('attn.k.b',)
 
