@@ -49,6 +49,7 @@ class GPTConfig:
     flat_chunk: int = 65536
     col_chunk: int = 64
     key_chunk: int = 256
+    join_threshold: int = 24  # a read with more producers than this waits on one join no-op instead of on each of them
 
     @property
     def tokens(self):
@@ -89,6 +90,7 @@ def token_stream(cfg: GPTConfig, steps: int, rank: int = 0, world: int = 1):
 class _Emit:
     def __init__(self, cfg: GPTConfig, steps: int, rank=0, world=1, stream_steps=None):
         self.c, self.g = cfg, Graph('train')
+        self.g.join_threshold = cfg.join_threshold
         self.bf = cfg.precision == 'bf16'
         self.act = 'bf16' if self.bf else 'f32'
         self.params: dict[str, tuple] = {}
