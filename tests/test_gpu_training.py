@@ -90,3 +90,30 @@ def test_device_error_first_wins_and_run_ends(kvm_lib):
             ex.run()
         out = ex.read_buffer('y')
         assert (out[0, 32:] == 7.0).all()          # the failing task wrote nothing
+
+
+def test_chained_starts_on_a_caller_stream(kvm_lib):
+    """KVM_CFG_CHAIN + kvm_set_stream: three runs of the same batch queued on the caller's stream without a finish in between
+    execute in stream order (a counter ends at 3) and the last finish reports a clean run."""
+    import torch
+    from kvm_b200.executor import CFG_CHAIN, Executor
+    from kvm_b200.workloads.graph import Graph
+    g = Graph('chain')
+    n = g.buffer('n', 1, 4, 'i32', {'kind': 'fill', 'value': 0})
+    x = g.buffer('x', 1, 64, init={'kind': 'fill', 'value': 1.0})
+    g.task('counter_inc', {'x': n, 'i0': 0, 'i1': 4, 'delta': 1}, [n], [n], 5, 'inc')
+    g.task('scale_flat', {'x': x, 'out': x, 'alpha': 2.0, 'e0': 0, 'e1': 64}, [x, n], [x], 5, 'dbl')
+    b = g.to_bundle()
+    stream = torch.cuda.Stream()
+    with Executor(flags=CFG_CHAIN) as ex:
+        ex.load(b)
+        ex.run()                                   # uploads; counter 1, x 2
+        ex.set_stream(stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                ex.start()
+        stream.synchronize()
+        res = ex.finish()
+        assert res.status == 0 and res.done == len(b.tasks)
+        assert (ex.read_buffer('n') == 4).all()
+        assert (ex.read_buffer('x') == 16.0).all()
