@@ -87,13 +87,17 @@ int kvm_set_version(KvmExec* h, int32_t var, int32_t version);
 int kvm_get_version(KvmExec* h, int32_t var, int32_t* version);
 /* MvmBundle::validate + MvmExec::submit (mvm_exec.cu:141-208,742-793): append one compiled batch; successor indices are
  * batch-local.  The bundle is checked (op ids, arities, ranges, buffer indices, indegree == in-edges, acyclic) before any
- * of it reaches the device. */
+ * of it reaches the device.
+ * Where this differs from the reference: there a submitted batch is admitted and runs once.  Here the batches submitted since
+ * the last kvm_clear_tasks form ONE resident program, and every kvm_start / kvm_run executes that whole program (re-armed, as
+ * the next window of a template: version waits and publishes shift by what the variables have advanced since).  So
+ * submit(A); run; submit(B); run executes A, then A and B.  To run B alone: kvm_clear_tasks between the two. */
 int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na);
 /* Read tasks.bin / successors.bin / args.bin of a bundle directory (FRAMEWORK.md:62-71) and submit them; buffers must have
  * been added in metadata.json's order by the caller. */
 int kvm_submit_bundle_dir(KvmExec* h, const char* dir);
-/* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over everything submitted since the last run.
- * kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
+/* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over the resident program (every batch submitted since
+ * the last kvm_clear_tasks, see kvm_submit).  kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
 int kvm_start(KvmExec* h);
 /* Run on the caller's CUDA stream (a cudaStream_t) from now on, so that launches order with the caller's own work - collectives
  * between segments of a tensor-parallel token - without host synchronisation.  No counterpart in the reference (its executor
@@ -122,12 +126,14 @@ int kvm_tc_task_count(KvmExec* h);
 const char* kvm_last_error(KvmExec* h);
 /* Read n elements of device memory `dev_src` (storage type dtype: KVM_F32 / KVM_I32 / KVM_BF16) back as float32 WITHOUT allocating
  * anything: no counterpart in the reference (its read_buffer, like kvm_read_buffer here, may allocate).  For callers that must not
- * call cudaMalloc: a decode loop reading logits / tokens every step beside other streams (cudaMalloc and cudaFree synchronise the
- * device), or code that runs while a stream is being captured.  The widening uses a fixed scratch array inside the library,
- * KVM_NOALLOC_MAX_ELEMS floats (4 MiB) per GPU; larger n is refused with KVM_E_ARG and a message from kvm_noalloc_last_error().
- * The first call on a device looks the array's address up (do it before any stream capture).  All calls on a GPU share the
- * array: calls whose device work overlaps race, so serialise them.  `stream` is a cudaStream_t (NULL = default stream); the
- * call returns after the copy has completed. */
+ * call cudaMalloc: a decode loop that reads logits / tokens every step while other streams (or a persistent executor) keep the
+ * GPU busy - cudaMalloc and cudaFree synchronise the whole device and would stall them.  The widening uses a fixed scratch array
+ * inside the library, KVM_NOALLOC_MAX_ELEMS floats (4 MiB) per GPU; larger n is refused with KVM_E_ARG and a message from
+ * kvm_noalloc_last_error().  The first call on a device looks the array's address up (make that call before any stream capture
+ * starts).  All calls on a GPU share the array: calls whose device work overlaps race, so serialise them.  `stream` is a
+ * cudaStream_t the caller owns and that is NOT capturing (NULL = the legacy default stream, which waits for the blocking streams):
+ * the call launches on it, copies, synchronises it and returns with the data in host_out.  The caller's current device is unchanged
+ * on return. */
 #define KVM_NOALLOC_MAX_ELEMS (1u << 20)
 int kvm_read_f32_noalloc(int32_t device, const void* dev_src, int32_t dtype, size_t n, float* host_out, void* stream);
 const char* kvm_noalloc_last_error(void);

@@ -48,9 +48,14 @@ struct KvmCtx {
   const void* tmaps;          // tensor-map table of the tensor-core tasks
   int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
 
-  // First error wins (reference: mvm_fail, include/mvm_exec.cuh:260-266). Every thread may call it with the same arguments.
+  // First error wins (reference: mvm_fail, include/mvm_exec.cuh:260-266).  `fail` is for errors every thread of the group sees
+  // alike (argument checks): all call it with the same arguments and thread 0 records.  `fail_any` is for data-dependent
+  // errors that only the thread that met the bad value knows about (a token id out of range in the row it happens to own).
   __device__ void fail(int code, int a = 0, int b = 0) const {
-    if (threadIdx.x == 0 && atomicCAS(&err->code, 0, code) == 0) {
+    if (threadIdx.x == 0) fail_any(code, a, b);
+  }
+  __device__ void fail_any(int code, int a = 0, int b = 0) const {
+    if (atomicCAS(&err->code, 0, code) == 0) {
       err->task = task; err->a = a; err->b = b;
       __threadfence_system();
     }

@@ -157,9 +157,11 @@ __global__ void kvm_widen_kernel(const void* p, float* out, size_t n, int dtype)
 // ---------------------------------------------------------------------------------------------------------------- read-back without allocation
 // kvm_read_buffer widens bf16 / i32 storage to float32 in a temporary device buffer it gets from cudaMalloc and frees again.
 // A serving loop that reads logits or sampled tokens back every decode step cannot afford that: cudaMalloc and cudaFree
-// synchronise the whole device, which stalls every other stream (and any persistent executor running beside the reader), and
-// they are not allowed at all while a stream is being captured.  This variant widens into a fixed scratch array that lives in
-// the library image instead: KVM_NOALLOC_MAX_ELEMS floats (4 MiB) per GPU that loads the library, held until the process exits.
+// synchronise the whole device, which stalls every other stream (and any persistent executor running beside the reader).
+// This variant widens into a fixed scratch array that lives in the library image instead: KVM_NOALLOC_MAX_ELEMS floats (4 MiB)
+// per GPU that loads the library, held until the process exits.  It allocates nothing, but it is an ordinary blocking read:
+// it launches on `stream`, copies, and synchronises that stream before it returns, so `stream` must not be capturing (and
+// NULL means the legacy default stream: pass a non-blocking stream of your own when other streams should keep running).
 //
 // The array is shared by every call on that GPU and keeps whatever the last call left in it.  Nothing in it has to start at
 // zero: each call overwrites exactly the n elements it then copies out and never reads beyond them.  Two calls whose device work
@@ -167,7 +169,8 @@ __global__ void kvm_widen_kernel(const void* p, float* out, size_t n, int dtype)
 //
 // In host code `kvm_noalloc_scratch` is only a stand-in for the symbol, not a device address, so the address is taken with
 // cudaGetSymbolAddress, once per device, with that device current, by the first call on the device (which therefore should
-// happen before any stream capture starts); later calls reuse the cached pointer and do no set-up.
+// happen before any stream capture starts anywhere in the process); later calls reuse the cached pointer and do no set-up.
+// The caller's current device is put back before the call returns.
 static __device__ __align__(256) float kvm_noalloc_scratch[KVM_NOALLOC_MAX_ELEMS];
 #define KVM_NOALLOC_MAX_DEVICES 64
 static float* g_noalloc_ptr[KVM_NOALLOC_MAX_DEVICES];
@@ -176,32 +179,36 @@ static char g_noalloc_error[256] = "";
 extern "C" const char* kvm_noalloc_last_error(void) { return g_noalloc_error; }
 
 extern "C" int kvm_read_f32_noalloc(int32_t device, const void* dev_src, int32_t dtype, size_t n, float* host_out, void* stream) {
-  auto fail = [&](int code, const char* what, cudaError_t e) {
-    if (e != cudaSuccess) snprintf(g_noalloc_error, sizeof g_noalloc_error, "kvm_read_f32_noalloc: %s: %s", what, cudaGetErrorString(e));
+  int prev_device = -1;
+  auto done = [&](int code, const char* what, cudaError_t e) {
+    if (code == 0) g_noalloc_error[0] = 0;
+    else if (e != cudaSuccess) snprintf(g_noalloc_error, sizeof g_noalloc_error, "kvm_read_f32_noalloc: %s: %s", what, cudaGetErrorString(e));
     else snprintf(g_noalloc_error, sizeof g_noalloc_error, "kvm_read_f32_noalloc: %s", what);
+    if (prev_device >= 0 && prev_device != device) cudaSetDevice(prev_device);
     return code;
   };
-  if (device < 0 || device >= KVM_NOALLOC_MAX_DEVICES || !dev_src || !host_out || dtype < 0 || dtype > 2) return fail(KVM_E_ARG, "bad device, pointer or dtype", cudaSuccess);
+  if (device < 0 || device >= KVM_NOALLOC_MAX_DEVICES || !dev_src || !host_out || dtype < 0 || dtype > 2) return done(KVM_E_ARG, "bad device, pointer or dtype", cudaSuccess);
   if (n > (size_t)KVM_NOALLOC_MAX_ELEMS) {
     snprintf(g_noalloc_error, sizeof g_noalloc_error, "kvm_read_f32_noalloc: %zu elements exceed the fixed scratch of %u (KVM_NOALLOC_MAX_ELEMS); read in pieces or use kvm_read_buffer",
              n, (unsigned)KVM_NOALLOC_MAX_ELEMS);
     return KVM_E_ARG;
   }
-  if (n == 0) return 0;
-  cudaError_t e = cudaSetDevice(device);
-  if (e != cudaSuccess) return fail(KVM_E_CUDA, "cudaSetDevice", e);
+  if (n == 0) return done(0, "", cudaSuccess);
+  cudaError_t e = cudaGetDevice(&prev_device);
+  if (e != cudaSuccess) { prev_device = -1; return done(KVM_E_CUDA, "cudaGetDevice", e); }
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return done(KVM_E_CUDA, "cudaSetDevice", e);
   if (!g_noalloc_ptr[device]) {      // set-up, once per device, with that device current
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, kvm_noalloc_scratch);
-    if (e != cudaSuccess || !p) return fail(KVM_E_CUDA, "cudaGetSymbolAddress(kvm_noalloc_scratch)", e);
+    if (e != cudaSuccess || !p) return done(KVM_E_CUDA, "cudaGetSymbolAddress(kvm_noalloc_scratch)", e);
     g_noalloc_ptr[device] = p;
   }
   float* scratch = g_noalloc_ptr[device];
   cudaStream_t st = (cudaStream_t)stream;
   const int blocks = (int)((n + 255) / 256 < 2048 ? (n + 255) / 256 : 2048);
   kvm_widen_kernel<<<blocks, 256, 0, st>>>(dev_src, scratch, n, dtype);
-  if ((e = cudaGetLastError()) != cudaSuccess) return fail(KVM_E_CUDA, "kernel launch", e);
-  if ((e = cudaMemcpyAsync(host_out, scratch, n * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess) return fail(KVM_E_CUDA, "cudaMemcpyAsync", e);
-  if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return fail(KVM_E_CUDA, "cudaStreamSynchronize", e);
-  return 0;
+  if ((e = cudaGetLastError()) != cudaSuccess) return done(KVM_E_CUDA, "kernel launch", e);
+  if ((e = cudaMemcpyAsync(host_out, scratch, n * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess) return done(KVM_E_CUDA, "cudaMemcpyAsync", e);
+  if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return done(KVM_E_CUDA, "cudaStreamSynchronize", e);
+  return done(0, "", cudaSuccess);
 }

@@ -78,7 +78,14 @@ extern "C" int kvm_create(const KvmConfig* cfg, KvmExec** out) {
   KvmExec* h = new KvmExec();
   if (cfg) h->cfg = *cfg;
   h->device = h->cfg.device;
-  auto fail = [&](const char* what, cudaError_t e) { fprintf(stderr, "kvm_create: %s: %s\n", what, cudaGetErrorString(e)); delete h; return KVM_E_CUDA; };
+  auto fail = [&](const char* what, cudaError_t e) {
+    fprintf(stderr, "kvm_create: %s: %s\n", what, cudaGetErrorString(e));
+    if (h->ev0) cudaEventDestroy(h->ev0);
+    if (h->ev1) cudaEventDestroy(h->ev1);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return KVM_E_CUDA;
+  };
   cudaError_t e;
   if ((e = cudaSetDevice(h->device)) != cudaSuccess) return fail("cudaSetDevice", e);
   cudaDeviceProp prop;
@@ -91,10 +98,15 @@ extern "C" int kvm_create(const KvmConfig* cfg, KvmExec** out) {
   h->nvars = h->cfg.num_vars > 0 ? h->cfg.num_vars : 64;
   if ((e = cudaFuncSetAttribute(kvm_exec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_bytes)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
-  cudaEventCreate(&h->ev0); cudaEventCreate(&h->ev1);
-  if ((e = cudaMalloc(&h->d_ctl, 64 * sizeof(int))) != cudaSuccess) return fail("cudaMalloc", e);
-  cudaMalloc(&h->d_versions, h->nvars * sizeof(int)); cudaMalloc(&h->d_park_head, h->nvars * sizeof(int)); cudaMalloc(&h->d_ver_base, h->nvars * sizeof(int)); cudaMalloc(&h->d_ver_off, h->nvars * sizeof(int)); cudaMalloc(&h->d_err, sizeof(KvmErrRec));
-  cudaMemset(h->d_versions, 0, h->nvars * sizeof(int)); cudaMemset(h->d_err, 0, sizeof(KvmErrRec)); cudaMemset(h->d_ctl, 0, 64 * sizeof(int));
+  if ((e = cudaEventCreate(&h->ev0)) != cudaSuccess || (e = cudaEventCreate(&h->ev1)) != cudaSuccess) return fail("cudaEventCreate", e);
+  if ((e = cudaMalloc(&h->d_ctl, 64 * sizeof(int))) != cudaSuccess || (e = cudaMalloc(&h->d_versions, h->nvars * sizeof(int))) != cudaSuccess ||
+      (e = cudaMalloc(&h->d_park_head, h->nvars * sizeof(int))) != cudaSuccess || (e = cudaMalloc(&h->d_ver_base, h->nvars * sizeof(int))) != cudaSuccess ||
+      (e = cudaMalloc(&h->d_ver_off, h->nvars * sizeof(int))) != cudaSuccess || (e = cudaMalloc(&h->d_err, sizeof(KvmErrRec))) != cudaSuccess) {
+    for (void* p : {(void*)h->d_ctl, (void*)h->d_versions, (void*)h->d_park_head, (void*)h->d_ver_base, (void*)h->d_ver_off, (void*)h->d_err}) if (p) cudaFree(p);
+    return fail("cudaMalloc", e);
+  }
+  if ((e = cudaMemset(h->d_versions, 0, h->nvars * sizeof(int))) != cudaSuccess || (e = cudaMemset(h->d_err, 0, sizeof(KvmErrRec))) != cudaSuccess ||
+      (e = cudaMemset(h->d_ctl, 0, 64 * sizeof(int))) != cudaSuccess) return fail("cudaMemset", e);
   if ((e = cudaDeviceSynchronize()) != cudaSuccess) return fail("init", e);
   *out = h;
   return 0;
@@ -415,7 +427,9 @@ extern "C" int kvm_start(KvmExec* h) {
     if (!(h->cfg.flags & KVM_CFG_CHAIN)) { h->error = "kvm_start: already started"; return KVM_E_STATE; }
     chained = true; h->armed = false;
   }
-  if (!h->armed) if (int r = kvm_prepare(h, chained)) return r;
+  cudaSetDevice(h->device);
+  // buffers added or bound, or tasks submitted, after kvm_rearm: the device tables are stale, prepare again
+  if (!h->armed || h->bufs_dirty || h->tasks_dirty) if (int r = kvm_prepare(h, chained)) return r;
   KvmDevState S = kvm_dev_state(h);
   KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
   kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);
@@ -429,6 +443,7 @@ extern "C" int kvm_finish(KvmExec* h, KvmResult* res) {
   if (!h) return KVM_E_ARG;
   if (!h->started) { h->error = "kvm_finish: nothing started"; return KVM_E_STATE; }
   h->started = false;
+  cudaSetDevice(h->device);
   KVM_CUDA(cudaStreamSynchronize(h->stream));
   int ctl[4]; KvmErrRec er;
   KVM_CUDA(cudaMemcpy(ctl, h->d_ctl, sizeof ctl, cudaMemcpyDeviceToHost));

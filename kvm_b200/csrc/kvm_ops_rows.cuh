@@ -18,7 +18,7 @@ __device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
   for (long long e = threadIdx.x; e < n; e += KVM_NT) {
     int r = r0 + (int)(e / d), col = (int)(e % d), tok = id[r];
     float v = 0.0f;
-    if (tok < 0 || tok >= wte.rows) c.fail(KVM_OPE_TOKEN, tok, r);
+    if (tok < 0 || tok >= wte.rows) c.fail_any(KVM_OPE_TOKEN, tok, r);
     else {
       v = kvm_ld(wte, (size_t)tok * wte.ld + col);
       if (wpe.p) v = __fadd_rn(v, kvm_ld(wpe, (size_t)(r % T) * wpe.ld + col));
@@ -108,7 +108,7 @@ __device__ void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
   for (long long e = threadIdx.x; e < (long long)(r1 - r0) * d; e += KVM_NT) {
     int r = r0 + (int)(e / d), col = (int)(e % d), i = ((const int*)idx.p)[r];
     float v = 0.0f;
-    if (i < 0 || i >= src.rows) c.fail(KVM_OPE_TOKEN, i, r);
+    if (i < 0 || i >= src.rows) c.fail_any(KVM_OPE_TOKEN, i, r);
     else v = kvm_ld(src, (size_t)i * src.ld + col);
     kvm_st(dst, (size_t)r * dst.ld + col, v);
   }

@@ -56,7 +56,7 @@ struct KvmSlot {
   int task;                   // -1 = leave
   int state;                  // 0 free, 1 full, 2 finished (awaiting release)
   int pair;                   // partner task run together with `task` (stacked GEMM tiles), or -1
-  int pad;
+  int go;                     // written by compute thread 0 before the group's barrier: 0 leave, 1 run the op body, 2 skip it (an error is recorded)
   int32_t desc[16];
   int32_t args[KVM_MAX_ARGS];
   int4 aux;
@@ -404,14 +404,21 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
     int cur = 0;
     while (true) {
       KvmSlot& sl = slots[cur];
+      // Whether this slot is taken, and whether its op body runs, is decided ONCE per CTA: thread 0 looks at the slot state and at
+      // the device's error word and leaves its verdict in the slot's `go` word; after the barrier every thread branches on that
+      // shared word only.  (A per-thread look at the global error word could split the group: the op bodies contain barriers
+      // over all KVM_NT threads, so warps that skipped the body and warps that entered it would wait for each other forever.)
       if (tid == 0) {
         unsigned polls = 0;
+        bool full = true;
         while (kvm_ld_volatile_shared(&sl.state) != 1) {
-          if ((++polls & 1023u) == 0 && kvm_globaltimer() - t_begin > 2 * S.timeout_ns) break;   // the scheduler always answers first
+          if ((++polls & 1023u) == 0 && kvm_globaltimer() - t_begin > 2 * S.timeout_ns) { full = false; break; }   // the scheduler always answers first
         }
+        sl.go = !full ? 0 : (*(volatile int*)&S.err->code == 0 ? 1 : 2);      // 0 leave, 1 run the op, 2 finish the task without running it
       }
       kvm_sync();
-      if (kvm_ld_volatile_shared(&sl.state) != 1) break;
+      const int go = kvm_ld_volatile_shared(&sl.go);
+      if (go == 0) break;
       const int task = sl.task;
       if (task < 0) break;
       c.task = task; c.pair = sl.pair;
@@ -424,7 +431,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         }
       }
       const int op = sl.desc[0];
-      if (op != 0 && *(volatile int*)&S.err->code == 0) kvm_dispatch(c, op, sl.args, sl.aux);
+      if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       // this task's generic-proxy writes (global results, shared scratch) ordered before any later TMA access to them
       asm volatile("fence.proxy.async;" ::: "memory");
       kvm_sync();                       // every thread's writes happen before thread 0's fence below (barrier, then a cumulative gpu-scope fence)
