@@ -93,6 +93,11 @@ int kvm_get_version(KvmExec* h, int32_t var, int32_t* version);
  * the next window of a template: version waits and publishes shift by what the variables have advanced since).  So
  * submit(A); run; submit(B); run executes A, then A and B.  To run B alone: kvm_clear_tasks between the two. */
 int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na);
+/* MvmBundle::validate (mvm_exec.cu:141-208) on its own: the same host check kvm_submit runs, without a handle, a CUDA context
+ * or a GPU, against a buffer table of nbufs entries and nvars version variables.  Returns 0, or KVM_E_BUNDLE with the first
+ * problem as text in msg (truncated to msg_len).  A malformed bundle is rejected here, before anything reaches a device. */
+int kvm_validate_batch(const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na, int32_t nbufs, int32_t nvars,
+                       char* msg, size_t msg_len);
 /* Read tasks.bin / successors.bin / args.bin of a bundle directory (FRAMEWORK.md:62-71) and submit them; buffers must have
  * been added in metadata.json's order by the caller. */
 int kvm_submit_bundle_dir(KvmExec* h, const char* dir);

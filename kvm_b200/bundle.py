@@ -106,6 +106,9 @@ def validate(b: Bundle, nbufs: int | None = None, nvars: int | None = None) -> s
     bad = (t['priority'] < 0) | (t['priority'] >= abi.NUM_PRIORITIES)
     if bad.any():
         return f"task {int(np.argmax(bad))}: priority outside [0,{abi.NUM_PRIORITIES - 1}]"
+    bad = t['deadline_us'] < -1
+    if bad.any():
+        return f'task {int(np.argmax(bad))}: deadline_us'
     for f in ('wait_var', 'pub_var'):
         bad = (t[f] < -1) | (t[f] >= nvars)
         if bad.any():
@@ -120,22 +123,27 @@ def validate(b: Bundle, nbufs: int | None = None, nvars: int | None = None) -> s
                 w = int(b.args[ao[i] + j])
                 if (w == -1 and not a.optional) or w < -1 or w >= nbufs:
                     return f'task {i}: {op.name} arg {j} buffer index {w} out of range'
-    if len(b.succ) and ((b.succ < 0) | (b.succ >= nt)).any():
-        return 'successor out of range'
+    # the edges as the descriptors address them (succ_off / succ_cnt need not tile the successor array)
+    total = int(sc.sum())
     owner = np.repeat(np.arange(nt), sc)
-    if (b.succ == owner).any():
-        return f'task {int(owner[np.argmax(b.succ == owner)])}: successor is itself'
-    indeg = np.bincount(b.succ, minlength=nt)
+    eidx = np.repeat(so, sc) + (np.arange(total) - np.repeat(np.cumsum(sc) - sc, sc))
+    edges = b.succ[eidx].astype(np.int64) if total else np.zeros(0, np.int64)
+    bad = (edges < 0) | (edges >= nt) | (edges == owner)
+    if bad.any():
+        k = int(np.argmax(bad))
+        return f'task {int(owner[k])}: successor {int(edges[k])} out of range'
+    indeg = np.bincount(edges, minlength=nt)
     if (indeg != t['indegree']).any():
         i = int(np.argmax(indeg != t['indegree']))
         return f"task {i}: indegree {int(t['indegree'][i])} != in-edges {int(indeg[i])}"
     rem, done = indeg.copy(), 0
     frontier = np.flatnonzero(rem == 0)
+    first = np.cumsum(sc) - sc
     while len(frontier):
         done += len(frontier)
-        idx = np.concatenate([np.arange(so[u], so[u] + sc[u]) for u in frontier]) if len(frontier) < 64 else \
+        idx = np.concatenate([np.arange(first[u], first[u] + sc[u]) for u in frontier]) if len(frontier) < 64 else \
             np.flatnonzero(np.isin(owner, frontier))
-        s = b.succ[idx]
+        s = edges[idx.astype(np.int64)]
         np.subtract.at(rem, s, 1)
         frontier = np.unique(s[rem[s] == 0])
     if done != nt:

@@ -273,6 +273,16 @@ static std::string kvm_validate(const KvmTaskDesc* t, int nt, const int32_t* suc
   return "";
 }
 
+// The same check without a handle or a GPU: what a loader or a fuzzer calls before anything is created on a device.
+extern "C" int kvm_validate_batch(const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na, int32_t nbufs, int32_t nvars,
+                                  char* msg, size_t msg_len) {
+  std::string problem;
+  if (nt < 0 || ne < 0 || na < 0 || nbufs < 0 || nvars < 0 || (nt && !tasks) || (ne && !succ) || (na && !args)) problem = "bad argument";
+  else problem = kvm_validate(tasks, nt, succ, ne, args, na, nbufs, nvars);
+  if (msg && msg_len) snprintf(msg, msg_len, "%s", problem.c_str());
+  return problem.empty() ? 0 : KVM_E_BUNDLE;
+}
+
 static int kvm_plan_tc(KvmExec* h, int first_task);   // kvm_gemm_host.inl: tensor maps of the tensor-core tasks
 
 extern "C" int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na) {

@@ -58,6 +58,7 @@ SYMBOLS = {
     'kvm_set_version': (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     'kvm_get_version': (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
     'kvm_submit': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]),
+    'kvm_validate_batch': (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_char_p, C.c_size_t]),
     'kvm_submit_bundle_dir': (C.c_int, [C.c_void_p, C.c_char_p]),
     'kvm_start': (C.c_int, [C.c_void_p]),
     'kvm_set_stream': (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -91,6 +92,16 @@ def lib():
             f.restype, f.argtypes = res, args
         _lib = L
     return _lib
+
+
+def validate_batch(tasks, succ, args, nbufs, nvars=64) -> str:
+    """The C library's host check of one batch (no GPU needed): '' if well formed, else the first problem."""
+    tasks = np.ascontiguousarray(tasks, dtype=abi.TASK_DTYPE)
+    succ = np.ascontiguousarray(succ, dtype=np.int32)
+    args = np.ascontiguousarray(args, dtype=np.int32)
+    msg = C.create_string_buffer(512)
+    lib().kvm_validate_batch(tasks.ctypes.data, len(tasks), succ.ctypes.data, len(succ), args.ctypes.data, len(args), nbufs, nvars, msg, 512)
+    return msg.value.decode()
 
 
 def bf16_bits(a: np.ndarray) -> np.ndarray:

@@ -192,3 +192,71 @@ def test_decode_phases_fit_whole_waves():
     cnt = collections.Counter(n.split('.')[2] for n in names if '.l0.' in n and 'join' not in n)
     assert cnt['q'] + cnt['k'] + cnt['v'] <= c.workers and cnt['gate'] + cnt['up'] <= c.workers and cnt['o'] <= c.workers and cnt['down'] <= c.workers
     assert cnt['part'] == c.kv_heads * c.splits and cnt['merge'] == c.kv_heads
+
+
+# ---- the C library's own host check, without a GPU (what kvm_submit runs before anything reaches a device) ---------------------
+def _c_validate(b, nbufs=None, nvars=64):
+    from kvm_b200.executor import validate_batch
+    return validate_batch(b.tasks, b.succ, b.args, len(b.buffers) if nbufs is None else nbufs, nvars)
+
+
+def test_c_validate_negatives(kvm_lib):
+    b = compile_spec(_spec())
+    assert _c_validate(b) == ''
+    def broken(f, **kw):
+        c = Bundle(b.tasks.copy(), b.succ.copy(), b.args.copy(), b.metadata)
+        f(c)
+        return _c_validate(c, **kw)
+    assert 'bad op_id' in broken(lambda c: c.tasks['op_id'].__setitem__(0, 77))
+    assert 'takes' in broken(lambda c: c.tasks['args_words'].__setitem__(0, 3))
+    assert 'args range' in broken(lambda c: c.tasks['args_off'].__setitem__(0, 10 ** 6))
+    assert 'successor range' in broken(lambda c: c.tasks['succ_cnt'].__setitem__(0, 99))
+    assert 'successor' in broken(lambda c: c.succ.__setitem__(0, 17))
+    assert 'priority' in broken(lambda c: c.tasks['priority'].__setitem__(0, 32))
+    assert 'indegree' in broken(lambda c: c.tasks['indegree'].__setitem__(2, 0))
+    assert 'buffer index' in broken(lambda c: c.args.__setitem__(0, 9))
+    assert 'buffer index' in broken(lambda c: None, nbufs=1)
+    assert 'cycle' in broken(lambda c: (c.succ.__setitem__(1, 0), c.tasks['indegree'].__setitem__(0, 1), c.tasks['indegree'].__setitem__(2, 0)))
+    assert 'version variable' in broken(lambda c: c.tasks['pub_var'].__setitem__(0, 5), nvars=4)
+    assert 'wait_ver' in broken(lambda c: c.tasks['pub_ver'].__setitem__(0, 0))
+    assert 'publishes itself' in broken(lambda c: (c.tasks['wait_var'].__setitem__(0, 0), c.tasks['wait_ver'].__setitem__(0, 1)))
+    # a waiter whose only possible publisher depends on it: b waits for version 2, which c publishes, and c runs after b
+    assert 'version-wait cycle' in broken(lambda c: c.tasks['wait_ver'].__setitem__(1, 2))
+
+
+def test_corrupted_bundles_are_rejected_on_the_host(kvm_lib):
+    """Seeded corruption of a valid training bundle (the reference's tests/litmus/fuzz.py does this to bundle files): random
+    words of the descriptor table, successor list and argument words are overwritten.  The host check must answer every time
+    (no crash, no hang) and must reject every mutant that changes the graph's structure; whatever it accepts is still a
+    well-formed program (indices in range, acyclic, indegrees equal to in-edges), which the Python twin confirms."""
+    b = build_training(preset('gpt_micro'), 1).to_bundle()
+    assert _c_validate(b) == ''
+    rng = np.random.default_rng(7)
+    rejected = 0
+    for trial in range(300):
+        c = Bundle(b.tasks.copy(), b.succ.copy(), b.args.copy(), b.metadata)
+        which = trial % 3
+        if which == 0:
+            words = c.tasks.view(np.int32).reshape(-1)
+            field = int(rng.integers(0, 12))            # op_id .. pub_ver
+            i = int(rng.integers(0, len(c.tasks))) * 16 + field
+            words[i] = int(rng.choice([-1, -2, 0, 1, 77, 1 << 20, -(1 << 31), (1 << 31) - 1, int(rng.integers(-1000, 1000))]))
+            changed = True
+        elif which == 1:
+            i = int(rng.integers(0, len(c.succ)))
+            old = int(c.succ[i])
+            c.succ[i] = int(rng.choice([-1, len(c.tasks), 1 << 20, int(rng.integers(0, len(c.tasks)))]))
+            changed = int(c.succ[i]) != old
+        else:
+            i = int(rng.integers(0, len(c.args)))
+            old = int(c.args[i])
+            c.args[i] = int(rng.choice([-2, len(c.buffers), 1 << 20, -(1 << 31)]))
+            changed = False                               # a scalar argument may take any value: the device op range-checks it
+        msg = _c_validate(c, nvars=len(b.metadata['variables']))
+        py = validate(c)
+        assert (msg == '') == (py == ''), (trial, msg, py)
+        if msg:
+            rejected += 1
+        elif changed and which == 1:
+            raise AssertionError(f'trial {trial}: a rewired successor was accepted')
+    assert rejected > 150
