@@ -41,7 +41,9 @@ typedef struct KvmConfig {
 } KvmConfig;
 enum { KVM_CFG_NO_TENSOR_CORES = 1, /* run every GEMM on the SIMT reference path (debugging / bit-exact f32) */
        KVM_CFG_PAIR_TILES = 2,      /* run two row-adjacent tensor-core GEMM tiles of one product as one 256 x 256 tile when both are ready */
-       KVM_CFG_CHAIN = 4            /* kvm_start may be called again before kvm_finish: the runs queue up on the stream (first device error is kept) */ };
+       KVM_CFG_CHAIN = 4,           /* kvm_start may be called again before kvm_finish: the runs queue up on the stream (first device error is kept) */
+       KVM_CFG_STATIC = 8,          /* run the resident program as per-worker programs planned on the host (no ready queue); refused if it cannot */
+       KVM_CFG_DYNAMIC = 16         /* always the ready queue, even where the static path would be chosen */ };
 
 /* Buffer initial value (mvm_exec.cu:1915-1929 buffer init kinds; `file` inits are read by the caller and passed as VALUES). */
 typedef struct KvmInit {
@@ -101,6 +103,19 @@ int kvm_validate_batch(const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ
 /* Read tasks.bin / successors.bin / args.bin of a bundle directory (FRAMEWORK.md:62-71) and submit them; buffers must have
  * been added in metadata.json's order by the caller. */
 int kvm_submit_bundle_dir(KvmExec* h, const char* dir);
+/* What the reference CLI does with a bundle directory before it runs it (mvm_exec.cu:2055-2076, init kinds :1915-1929): read
+ * metadata.json (abi_version 2), create every buffer it lists, in index order, with its init (fill / values / seeded / file, a
+ * file path being relative to the directory), set the variables' base versions, then submit tasks.bin / successors.bin /
+ * args.bin.  Buffers an earlier bundle of this handle already declared (same index) must have the same shape and are kept.
+ * KVM_E_IO if a file cannot be read, KVM_E_BUNDLE (with the reason in kvm_last_error) if the metadata or the batch is malformed. */
+int kvm_load_bundle_dir(KvmExec* h, const char* dir);
+/* The buffer table as loaded: count, shape / dtype of an entry, and the names metadata.json gave (kvm_buffer_index: index of
+ * a name, or KVM_E_ARG; kvm_buffer_name: "" for a buffer added without a name).  kvm_variable_id: id of a named version variable. */
+int kvm_buffer_count(KvmExec* h);
+int kvm_buffer_info(KvmExec* h, int32_t idx, int32_t* rows, int32_t* cols, int32_t* dtype);
+const char* kvm_buffer_name(KvmExec* h, int32_t idx);
+int kvm_buffer_index(KvmExec* h, const char* name);
+int kvm_variable_id(KvmExec* h, const char* name);
 /* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over the resident program (every batch submitted since
  * the last kvm_clear_tasks, see kvm_submit).  kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
 int kvm_start(KvmExec* h);

@@ -9,9 +9,11 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <string>
 #include <vector>
 
+#include "kvm_json.hpp"
 #include "kvm_dev.cuh"
 #include "kvm_ops_flat.cuh"
 #include "kvm_ops_rows.cuh"

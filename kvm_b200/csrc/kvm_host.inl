@@ -35,6 +35,8 @@ struct KvmExec {
   bool started = false, armed = false;
   bool has_gemv = false;         // a submitted task is a gemv_bf16: its shared-memory ring is worth more than the buffer-table cache
   bool own_stream = true;        // false after kvm_set_stream: the caller's stream is used and never destroyed here
+  std::vector<std::string> buf_names;              // by buffer index; "" where the caller gave none (kvm_load_bundle_dir fills them from metadata.json)
+  std::map<std::string, int> var_ids;              // version variables by name (from metadata.json)
   KvmResult last{};
 };
 
@@ -315,6 +317,108 @@ extern "C" int kvm_submit_bundle_dir(KvmExec* h, const char* dir) {
   if (!kvm_read_file(d + "/tasks.bin", t) || !kvm_read_file(d + "/successors.bin", s) || !kvm_read_file(d + "/args.bin", a)) { h->error = "cannot read bundle files in " + d; return KVM_E_IO; }
   if (t.size() % sizeof(KvmTaskDesc) || s.size() % 4 || a.size() % 4) { h->error = "bundle file sizes are not whole records"; return KVM_E_BUNDLE; }
   return kvm_submit(h, (const KvmTaskDesc*)t.data(), (int)(t.size() / sizeof(KvmTaskDesc)), (const int32_t*)s.data(), (int)(s.size() / 4), (const int32_t*)a.data(), (int)(a.size() / 4));
+}
+
+// ---- bundle directory loader: what the reference CLI does with metadata.json (mvm_exec.cu:2055-2076,1915-1929) ----------------------
+static uint16_t kvm_host_bf16(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);      // NaN stays NaN
+  return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+
+extern "C" int kvm_load_bundle_dir(KvmExec* h, const char* dir) {
+  if (!h || !dir) { if (h) h->error = "kvm_load_bundle_dir: bad argument"; return KVM_E_ARG; }
+  if (h->started) { h->error = "kvm_load_bundle_dir: a run is in flight"; return KVM_E_STATE; }
+  const std::string d(dir);
+  std::vector<char> raw;
+  if (!kvm_read_file(d + "/metadata.json", raw)) { h->error = "cannot read " + d + "/metadata.json"; return KVM_E_IO; }
+  try {
+    const std::string text(raw.begin(), raw.end());
+    const KvmJson m = KvmJsonParser(text).parse();
+    if (m.type != KvmJson::Obj) throw std::runtime_error("metadata.json is not an object");
+    if (m.integer("abi_version", -1) != KVM_ABI_VERSION) throw std::runtime_error("abi_version " + std::to_string(m.integer("abi_version", -1)) + " != " + std::to_string(KVM_ABI_VERSION));
+    const long long nt = m.integer("task_count", -1), ne = m.integer("edge_count", -1), nw = m.integer("args_words", -1);
+    if (nt < 1 || ne < 0 || nw < 0) throw std::runtime_error("task_count / edge_count / args_words missing");
+    std::vector<char> t, sc, ar;
+    if (!kvm_read_file(d + "/tasks.bin", t) || !kvm_read_file(d + "/successors.bin", sc) || !kvm_read_file(d + "/args.bin", ar)) { h->error = "cannot read bundle files in " + d; return KVM_E_IO; }
+    if ((long long)t.size() != nt * (long long)sizeof(KvmTaskDesc) || (long long)sc.size() != ne * 4 || (long long)ar.size() != nw * 4)
+      throw std::runtime_error("tasks.bin / successors.bin / args.bin do not have the sizes metadata.json states");
+    if (const KvmJson* bs = m.get("buffers")) {
+      if (bs->type != KvmJson::Arr) throw std::runtime_error("buffers is not an array");
+      for (const KvmJson& jb : bs->a) {
+        const long long idx = jb.integer("index", -1), rows = jb.integer("rows", 0), cols = jb.integer("cols", 0), dtype = jb.integer("dtype", 0);
+        const std::string name = jb.str("name");
+        if (idx < 0 || rows < 1 || cols < 1 || rows * cols > 2147483647LL || dtype < 0 || dtype > 2) throw std::runtime_error("bad buffer entry '" + name + "'");
+        if (idx < (long long)h->bufs.size()) {      // a buffer an earlier bundle of this handle declared: the shapes must agree
+          const KvmBuf& b = h->bufs[idx];
+          if (b.rows != rows || b.cols != cols || b.dtype != dtype) throw std::runtime_error("buffer " + std::to_string(idx) + " differs from an earlier bundle's");
+          continue;
+        }
+        if (idx != (long long)h->bufs.size()) throw std::runtime_error("buffer indices must be dense and ascending");
+        const size_t n = (size_t)(rows * cols);
+        KvmInit init{};
+        std::vector<char> data;
+        const KvmJson* in = jb.get("init");
+        const std::string kind = in ? in->str("kind") : "fill";
+        if (!in || kind == "fill") { init.kind = KVM_INIT_FILL; init.fill = in ? in->num("value", 0.0) : 0.0; }
+        else if (kind == "values") {
+          const KvmJson& vals = in->need("values");
+          if (vals.type != KvmJson::Arr || vals.a.size() != n) throw std::runtime_error("buffer '" + name + "': values do not match rows x cols");
+          data.resize(n * kvm_elem_bytes((int)dtype));
+          for (size_t i = 0; i < n; ++i) {
+            if (vals.a[i].type != KvmJson::Num) throw std::runtime_error("buffer '" + name + "': a value is not a number");
+            if (dtype == KVM_I32) ((int32_t*)data.data())[i] = (int32_t)strtoll(vals.a[i].s.c_str(), nullptr, 10);
+            else if (dtype == KVM_BF16) ((uint16_t*)data.data())[i] = kvm_host_bf16((float)vals.a[i].n);
+            else ((float*)data.data())[i] = (float)vals.a[i].n;
+          }
+          init.kind = KVM_INIT_VALUES; init.data = data.data();
+        } else if (kind == "seeded") {
+          init.kind = KVM_INIT_SEEDED; init.seed = in->u64("seed", 0); init.draws = (int)in->integer("draws", 1);
+          init.bias = (float)in->num("bias", 0.0); init.coef = (float)in->num("coef", 1.0);
+        } else if (kind == "file") {
+          const std::string rel = in->str("path");
+          if (rel.empty() || rel[0] == '/' || rel.find("..") != std::string::npos) throw std::runtime_error("buffer '" + name + "': file init needs a path inside the bundle directory");
+          if (!kvm_read_file(d + "/" + rel, data)) { h->error = "cannot read " + d + "/" + rel; return KVM_E_IO; }
+          if (data.size() != n * kvm_elem_bytes((int)dtype)) throw std::runtime_error("buffer '" + name + "': " + rel + " does not hold rows x cols elements");
+          init.kind = KVM_INIT_VALUES; init.data = data.data();
+        } else throw std::runtime_error("buffer '" + name + "': unknown init kind '" + kind + "'");
+        const int r = kvm_add_buffer(h, (int)rows, (int)cols, (int)dtype, &init);
+        if (r < 0) return r;
+        h->buf_names.resize(h->bufs.size());
+        h->buf_names[r] = name;
+      }
+    }
+    if (const KvmJson* vs = m.get("variables")) for (const KvmJson& jv : vs->a) {
+      const long long id = jv.integer("id", -1), base = jv.integer("base_version", 0);
+      if (id < 0 || id >= h->nvars || base < 0) throw std::runtime_error("variable id or base_version out of range");
+      h->var_ids[jv.str("name")] = (int)id;
+      if (base) if (int r = kvm_set_version(h, (int)id, (int)base)) return r;
+    }
+    return kvm_submit(h, (const KvmTaskDesc*)t.data(), (int)nt, (const int32_t*)sc.data(), (int)ne, (const int32_t*)ar.data(), (int)nw);
+  } catch (const std::exception& e) {
+    h->error = d + ": " + e.what();
+    return KVM_E_BUNDLE;
+  }
+}
+
+extern "C" int kvm_buffer_count(KvmExec* h) { return h ? (int)h->bufs.size() : KVM_E_ARG; }
+extern "C" int kvm_buffer_info(KvmExec* h, int32_t idx, int32_t* rows, int32_t* cols, int32_t* dtype) {
+  if (!h || idx < 0 || idx >= (int)h->bufs.size()) { if (h) h->error = "kvm_buffer_info: index out of range"; return KVM_E_ARG; }
+  if (rows) *rows = h->bufs[idx].rows;
+  if (cols) *cols = h->bufs[idx].cols;
+  if (dtype) *dtype = h->bufs[idx].dtype;
+  return 0;
+}
+extern "C" const char* kvm_buffer_name(KvmExec* h, int32_t idx) { return (h && idx >= 0 && idx < (int)h->buf_names.size()) ? h->buf_names[idx].c_str() : ""; }
+extern "C" int kvm_buffer_index(KvmExec* h, const char* name) {
+  if (!h || !name) return KVM_E_ARG;
+  for (size_t i = 0; i < h->buf_names.size(); ++i) if (h->buf_names[i] == name) return (int)i;
+  return KVM_E_ARG;
+}
+extern "C" int kvm_variable_id(KvmExec* h, const char* name) {
+  if (!h || !name) return KVM_E_ARG;
+  auto it = h->var_ids.find(name);
+  return it == h->var_ids.end() ? KVM_E_ARG : it->second;
 }
 
 extern "C" int kvm_clear_tasks(KvmExec* h) {

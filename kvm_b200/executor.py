@@ -60,6 +60,12 @@ SYMBOLS = {
     'kvm_submit': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]),
     'kvm_validate_batch': (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_char_p, C.c_size_t]),
     'kvm_submit_bundle_dir': (C.c_int, [C.c_void_p, C.c_char_p]),
+    'kvm_load_bundle_dir': (C.c_int, [C.c_void_p, C.c_char_p]),
+    'kvm_buffer_count': (C.c_int, [C.c_void_p]),
+    'kvm_buffer_info': (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    'kvm_buffer_name': (C.c_char_p, [C.c_void_p, C.c_int32]),
+    'kvm_buffer_index': (C.c_int, [C.c_void_p, C.c_char_p]),
+    'kvm_variable_id': (C.c_int, [C.c_void_p, C.c_char_p]),
     'kvm_start': (C.c_int, [C.c_void_p]),
     'kvm_set_stream': (C.c_int, [C.c_void_p, C.c_void_p]),
     'kvm_finish': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
@@ -238,6 +244,18 @@ class Executor:
                 self.set_version(v['id'], v['base_version'])
         self.submit(b.tasks, b.succ, b.args)
         self.bundle = b
+        return self
+
+    def load_dir(self, path) -> 'Executor':
+        """The same through the C library's own loader (kvm_load_bundle_dir reads metadata.json itself): what a C++ host or the
+        kvm_exec tool does with a bundle directory."""
+        self._check(self.L.kvm_load_bundle_dir(self._h, str(path).encode()))
+        rows, cols, dt = C.c_int32(), C.c_int32(), C.c_int32()
+        for i in range(len(self.meta), self.L.kvm_buffer_count(self._h)):
+            self._check(self.L.kvm_buffer_info(self._h, i, C.byref(rows), C.byref(cols), C.byref(dt)))
+            name = self.L.kvm_buffer_name(self._h, i).decode() or f'buf{i}'
+            self.meta.append({'name': name, 'rows': rows.value, 'cols': cols.value, 'dtype': dt.value})
+            self.names[name] = i
         return self
 
     def add_bundle_buffer(self, b: Bundle, spec: dict) -> int:

@@ -11,6 +11,11 @@
   gpt_micro_golden.json this repo's gpt_micro 2-step training workload compiled by the reference compiler and run on the
                         reference CPU VM (runtime/workload_vm.py run_golden): hash of the compiled bundle bytes, losses,
                         final weights' checksums and a few whole buffers
+  ref_gpt_tiny_f32/, ref_gpt_tiny_bf16s/
+                        bundle DIRECTORIES written by the reference's own frontend and compiler (bench/vs_pytorch/gen.py --model
+                        gpt_tiny --steps 1, f32 and bf16s storage: RoPE, biases, untied head) with the final state of the reference
+                        CPU VM (--emit-golden) kept as golden.npz (golden.json is 3 MB of text per bundle; the tests write it back
+                        out as JSON where a tool wants the file)
 The fixtures are data; nothing here is imported by the product.
 """
 import hashlib
@@ -221,6 +226,30 @@ def main():
     (HERE / 'gpt_micro_golden.json').write_text(json.dumps({'bundle_sha256': sha, 'versions': gold['versions'], 'buffers': {n: gold['buffers'][n] for n in keep},
                                                             'buffer_sha256': sums}))
     print('gpt_micro_golden.json: losses', gold['buffers']['loss.0'][0], gold['buffers']['loss.1'][0])
+
+    # ---- bundle directories of the reference's own frontend (its gpt_tiny: RoPE, biases, untied head), f32 and bf16s storage
+    import shutil
+    for tag, extra in (('f32', []), ('bf16s', ['--precision', 'bf16s'])):
+        with tempfile.TemporaryDirectory() as td:
+            td = Path(td)
+            subprocess.run([sys.executable, str(REF / 'bench/vs_pytorch/gen.py'), str(td / 'w'), '--model', 'gpt_tiny', '--steps', '1', *extra], check=True, capture_output=True)
+            subprocess.run([sys.executable, str(REF / 'runtime/compile_workload.py'), str(td / 'w/workload.json'), str(td / 'b'), '--emit-golden'], check=True,
+                           capture_output=True)
+            out = HERE / f'ref_gpt_tiny_{tag}'
+            shutil.rmtree(out, ignore_errors=True)
+            out.mkdir()
+            for n in ('tasks.bin', 'successors.bin', 'args.bin', 'metadata.json'):
+                shutil.copy(td / 'b' / n, out / n)
+            meta = json.loads((td / 'b/metadata.json').read_text())
+            for b in meta['buffers']:                      # `file` inits travel with the bundle
+                if b['init']['kind'] == 'file':
+                    (out / b['init']['path']).parent.mkdir(parents=True, exist_ok=True)
+                    shutil.copy(td / 'b' / b['init']['path'], out / b['init']['path'])
+            gold = json.loads((td / 'b/golden.json').read_text())
+            arrs = {'buf.' + n: np.array(v, np.int32 if gold['dtypes'][n] == 'i32' else np.float32) for n, v in gold['buffers'].items()}
+            arrs['meta'] = np.frombuffer(json.dumps({'versions': gold['versions'], 'dtypes': gold['dtypes']}).encode(), dtype=np.uint8)
+            np.savez_compressed(out / 'golden.npz', **arrs)
+            print(f'ref_gpt_tiny_{tag}:', meta['task_count'], 'tasks, loss', gold['buffers']['loss.0'][0])
 
 
 if __name__ == '__main__':

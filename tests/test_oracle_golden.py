@@ -96,3 +96,30 @@ def test_gpt_micro_against_reference_compiler_and_vm():
         np.testing.assert_allclose(got, np.array(vals, got.dtype), rtol=2e-7, atol=1e-12, err_msg=name)
     exact = sum(hashlib.sha256(buf.a.tobytes()).hexdigest() == gold['buffer_sha256'][spec['name']] for spec, buf in zip(b.buffers, vm.bufs))
     assert exact >= 0.9 * len(b.buffers), f'only {exact} of {len(b.buffers)} buffers are bit-identical to the reference VM'
+
+
+@pytest.mark.parametrize('name', ['ref_gpt_tiny_f32', 'ref_gpt_tiny_bf16s'])
+def test_reference_frontend_bundle_on_the_oracle(name):
+    """A bundle directory written by the reference's own frontend + compiler (its gpt_tiny: RoPE, biases, untied head), run by the
+    oracle VM, against the final state of the reference CPU VM (golden.npz): every buffer to float32 rounding."""
+    from kvm_b200.bundle import load_bundle
+    from oracle.vm_np import VM
+    d = G / name
+    z = np.load(d / 'golden.npz')
+    meta = json.loads(bytes(z['meta']).decode())
+    b = load_bundle(d)
+    vm = VM(b).run()
+    assert {b.metadata['variables'][k]['name']: v for k, v in vm.versions.items()} == meta['versions']
+    worst = 0.0
+    for k in z.files:
+        if not k.startswith('buf.'):
+            continue
+        ref, got = z[k], vm.buffer(k[4:]).a.reshape(-1)
+        if ref.dtype == np.int32:
+            assert np.array_equal(got, ref), k
+            continue
+        den = float(np.sqrt((ref.astype(np.float64) ** 2).sum()))
+        err = float(np.sqrt(((got.astype(np.float64) - ref) ** 2).sum())) / max(den, 1e-30)
+        if 'attn.k.b' not in k:          # an exactly-zero gradient: what is computed is rounding noise (see tests/parity.py)
+            worst = max(worst, err)
+    assert worst <= (2e-6 if name.endswith('f32') else 4e-3), worst
