@@ -48,12 +48,19 @@ def materialize(bundle: Bundle, b: dict) -> Buf:
 
 
 class VM:
-    def __init__(self, bundle: Bundle, exact_matmul: bool = True, buffers: list | None = None, lazy: bool = False, zeros: bool = False):
+    def __init__(self, bundle: Bundle, exact_matmul: bool = True, buffers: list | None = None, lazy: bool = False, zeros: bool = False, f64: bool = False):
         self.bundle = bundle
         self.exact = exact_matmul
+        self.f64 = f64          # all-double rerun (oracle/f64.py): same ops without the float32 / bf16 rounding, float64 buffers
+        self.opsmod = ops_np
+        if f64:
+            from .f64 import ops_f64
+            self.opsmod = ops_f64()
         self.zeros = zeros      # timing-only mode: every buffer starts as zeros instead of its init (values do not change op cost)
         # lazy=True materialises a buffer at its first use (bounded timing samples touch a fraction of a large model)
         self.bufs = buffers if buffers is not None else [None if lazy else materialize(bundle, b) for b in bundle.buffers]
+        if f64:
+            self.bufs = [b if b is None or b.dtype == I32 else Buf(b.a.astype(np.float64), b.dtype) for b in self.bufs]
         self.versions = {v['id']: v['base_version'] for v in bundle.metadata.get('variables', [])}
         self.ops = abi.ops_by_id()
         nt = len(bundle.tasks)
@@ -85,7 +92,7 @@ class VM:
                 scal[a.name] = int(w)
             else:
                 scal[a.name] = float(np.array([w], '<i4').view('<f4')[0])
-        ops_np.OPS[op.name](bufs, scal, exact_matmul=self.exact)
+        self.opsmod.OPS[op.name](bufs, scal, exact_matmul=self.exact)
 
     def run(self, subset=None, time_limit=None):
         """Run every task (or stop after `subset` tasks / `time_limit` seconds, for bounded timing samples). Returns self."""

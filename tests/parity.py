@@ -62,3 +62,15 @@ def compare(ex, vm, tol, skip=(), tols=None):
             bad.append((name, e))
     assert not bad, f'{len(bad)} buffers differ from the oracle, worst first: {sorted(bad, key=lambda x: -x[1] if not isinstance(x[1], str) else -1)[:8]}'
     return errs
+
+
+def vm_from_device(ex, bundle, **vm_kw):
+    """An oracle VM whose initial buffers are read back from the device right after loading (before any run).  For large models:
+    the device materialises seeded buffers in milliseconds (bit for bit what the host generator gives, which its own test pins),
+    numpy takes a minute per 100 M elements."""
+    from oracle.ops_np import Buf
+    bufs = []
+    for spec in bundle.buffers:
+        a = ex.read_buffer(spec['name'])
+        bufs.append(Buf(np.ascontiguousarray(a), spec['dtype']))
+    return VM(bundle, buffers=bufs, **vm_kw)
