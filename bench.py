@@ -56,14 +56,16 @@ def task_flops(bundle):
             m = np.minimum(tm, w[:, 8] - w[:, 6]).astype(np.float64)
             n = np.minimum(tn, w[:, 9] - w[:, 7]).astype(np.float64)
             out[idx] = 2.0 * m * n * w[:, 10]
-    for op, q0i, Ti, hdi, f in ((45, 7, 8, 11, 4.0), (47, 9, 10, 13, 8.0), (48, 10, 11, 13, 8.0)):
+    # attention: rows x keys score elements (causal: keys up to the row), 4 FLOPs each forward (QK^T and PV) and 10 backward (2.5x,
+    # the recomputed scores counted once), split evenly over the dq and dkv tasks
+    for op, q0i, Ti, hdi, f in ((45, 7, 8, 11, 4.0), (47, 9, 10, 13, 5.0), (48, 10, 11, 13, 5.0)):
         idx = np.flatnonzero(t['op_id'] == op)
         if len(idx):
             w = a[t['args_off'][idx][:, None] + np.arange(15 if op != 45 else 13)[None, :]]
             q0, T, hd = w[:, q0i].astype(np.float64), w[:, Ti].astype(np.float64), w[:, hdi].astype(np.float64)
             rows = np.minimum(128, T - q0)
             keys = (q0 + rows / 2) if op != 48 else (T - q0 - rows / 2)
-            out[idx] = f * rows * keys * hd / 2 * (1.0 if op == 45 else 1.25)
+            out[idx] = f * rows * keys * hd
     return out
 
 
@@ -105,6 +107,12 @@ class ClockSampler:
         return {'sm_mhz': float(np.median(sm)) if sm else None, 'sm_max_mhz': max(mx) if mx else None, 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
+def workload_name(model, cfg):
+    """The configuration both arms name: BASELINE configs[2] for gpt_162m."""
+    return (f'{model} training step: {cfg.layers}L d{cfg.d_model} H{cfg.heads} F{cfg.d_ff} V{cfg.vocab} T{cfg.seq}, micro-batch {cfg.batch} x {cfg.seq} tokens per GPU, '
+            f'bf16 storage + f32 masters, AdamW lr {cfg.lr} wd {cfg.wd}, seeded weights N(0, {cfg.init_std}), uniform tokens')
+
+
 def get_bundle(model, rank, world, stream_steps, over):
     """The one-step training bundle of `model` (generated once per box, cached on local disk)."""
     from kvm_b200.bundle import load_bundle
@@ -130,9 +138,9 @@ def get_bundle(model, rank, world, stream_steps, over):
 
 def cpu_sample(bundle, cfg, seconds, threads=None):
     """Estimate the CPU oracle's time for one step from a bounded, stratified sample: for every op kind in the bundle a few of
-    its tasks (seeded choice) are executed on zero-filled buffers and timed; step time = sum over kinds of count x mean."""
+    its tasks (seeded choice) are executed on stand-in values and timed; step time = sum over kinds of count x mean."""
     from oracle.vm_np import VM
-    vm = VM(bundle, exact_matmul=False, lazy=True, zeros=True)
+    vm = VM(bundle, exact_matmul=False, lazy=True, zeros=_stand_in_values())
     step = vm.buffer('opt_step')
     step.a[:] = 1                       # AdamW wants a 1-based step; the token window must stay inside the stream
     ops = bundle.tasks['op_id']
@@ -158,22 +166,63 @@ def cpu_sample(bundle, cfg, seconds, threads=None):
     return {'steps_per_s': 1.0 / total, 'seconds': time.perf_counter() - t_begin, 'tasks': ran, 'of_tasks': int(len(ops)), 'kinds': len(kinds)}
 
 
+def _stand_in_values():
+    """Stand-in buffer contents for the bounded CPU sample: ordinary N(0, 0.02) values cut from one shared block instead of zeros
+    (exp / tanh / rounding then see ordinary operands), made when a task first touches the buffer.  Materialising the real seeded
+    values of a 162M model costs a minute of numpy, which is what the `--impl reference` arm spends; this sample must not."""
+    rng = np.random.default_rng(123)
+    pool = rng.standard_normal(1 << 24, dtype=np.float32) * np.float32(0.02)
+
+    def make(spec):
+        n, shape = spec['rows'] * spec['cols'], (spec['rows'], spec['cols'])
+        if spec['dtype'] == 1:
+            return np.zeros(shape, np.int32)
+        a = np.resize(pool, n).reshape(shape) if n > len(pool) else pool[:n].reshape(shape).copy()
+        if spec['name'].startswith('v.'):
+            a = np.abs(a)                                      # second moments are non-negative
+        if spec['dtype'] == 2:
+            from oracle.ops_np import bf16_round
+            a = bf16_round(a)
+        return np.ascontiguousarray(a)
+    return make
+
+
+def cpu_real_step(bundle, limit_s):
+    """ONE real step of the CPU oracle on the bench's own bundle (seeded weights, the same token stream), all host threads numpy's
+    BLAS takes.  Only the step is timed, not the creation of the buffers.  If the box is so slow that the step passes `limit_s`,
+    the run stops there and the step time is extrapolated from the share of tasks done (said so in the result)."""
+    from oracle.vm_np import VM
+    t0 = time.perf_counter()
+    vm = VM(bundle, exact_matmul=False)
+    t_init = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    vm.run(time_limit=limit_s)
+    dt = time.perf_counter() - t0
+    done, nt = int(vm.exec_count.sum()), len(bundle.tasks)
+    loss = float(vm.buffer('loss.0').a[0, 0]) if done == nt else None
+    return {'seconds': dt * nt / max(done, 1), 'measured_seconds': dt, 'tasks': done, 'of_tasks': nt, 'init_seconds': t_init, 'loss': loss}
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU implementation of the path (the oracle port), all host threads numpy's BLAS takes."""
     if rank != 0:
         return
     cfg, bundle = get_bundle(args.model, 0, 1, 2, {})
     cores = os.cpu_count() or 1
-    per = max(2.0, min(20.0, 60.0 / max(args.steps + args.warmup, 1)))
-    for _ in range(args.warmup):
-        cpu_sample(bundle, cfg, min(per, 3.0))
-    vals = [cpu_sample(bundle, cfg, per) for _ in range(args.steps)]
-    v = float(np.mean([x['steps_per_s'] for x in vals]))
-    sample = f"{vals[-1]['tasks']} of {vals[-1]['of_tasks']} tasks of one step, a few of each of its {vals[-1]['kinds']} op kinds, {vals[-1]['seconds']:.1f} s; step time = sum over kinds of count x mean task time"
+    # One REAL step is timed (about a minute of CPU work on this model, plus as much again to create the seeded buffers): that is
+    # the bounded sample.  `steps` in the line is the number of steps actually executed and timed, so ms_per_step x steps is the
+    # CPU time this run really spent in the timed region; the requested K / W are echoed beside it.
+    r = cpu_real_step(bundle, args.cpu_step_limit)
+    v = 1.0 / r['seconds']
+    whole = r['tasks'] == r['of_tasks']
+    sample = (f"one real step of the numpy oracle on the bench's own bundle ({r['of_tasks']} tasks, seeded weights and tokens), {r['measured_seconds']:.1f} s timed"
+              + ('' if whole else f", stopped after {r['tasks']} tasks at the time limit and extrapolated by task count")
+              + f"; creating the buffers took {r['init_seconds']:.1f} s more (untimed); requested steps {args.steps}, warmup {args.warmup}: not repeated on the CPU")
     print(json.dumps({
-        'impl': 'reference', 'metric': 'gpt162m_train_steps_per_s', 'value': v, 'unit': 'steps/s', 'n_gpus': args.gpus, 'steps': args.steps,
-        'warmup': args.warmup, 'ms_per_step': 1000.0 / v, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
-        'data': 'synthetic', 'config': {'workload': f'{args.model} training step, micro-batch {cfg.batch}x{cfg.seq} tokens, CPU oracle (numpy port of the reference ops)'},
+        'impl': 'reference', 'metric': 'gpt162m_train_steps_per_s', 'value': v, 'unit': 'steps/s', 'n_gpus': args.gpus, 'steps': 1, 'steps_requested': args.steps,
+        'warmup': 0, 'warmup_requested': args.warmup, 'ms_per_step': 1000.0 / v, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
+        'data': 'synthetic', 'config': {'workload': workload_name(args.model, cfg), 'tokens_per_step_per_gpu': cfg.tokens, 'parallelism': f'dp{args.gpus}',
+                                        'engine': 'CPU oracle: numpy port of the reference ops, all host threads BLAS takes', 'loss': r['loss']},
         'cpu_baseline': {'value': v, 'unit': 'steps/s', 'cores': cores, 'kind': 'port', 'sample': sample},
         'e2e': {'value': v, 'unit': 'steps/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0}))
 
@@ -254,9 +303,9 @@ def run_ours(args, rank, world, local_rank):
         line = {
             'metric': 'gpt162m_train_steps_per_s', 'value': value, 'unit': 'steps/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': kernel_ms, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
-            'config': {'workload': f'{args.model} training step: {cfg.layers}L d{cfg.d_model} H{cfg.heads} F{cfg.d_ff} V{cfg.vocab} T{cfg.seq}, micro-batch {cfg.batch} per GPU, '
-                                   f'bf16 storage + f32 masters, AdamW; one persistent-kernel launch per step ({len(bundle.tasks)} tasks, {len(bundle.succ)} edges)',
-                       'tokens_per_step_per_gpu': N, 'parallelism': f'dp{world}', 'l2': 'per-step working set (> 6 GB) exceeds the 126 MB L2',
+            'config': {'workload': workload_name(args.model, cfg), 'tokens_per_step_per_gpu': N, 'parallelism': f'dp{world}',
+                       'engine': f'one persistent-kernel launch per step ({len(bundle.tasks)} tasks, {len(bundle.succ)} edges)',
+                       'l2': 'per-step working set (> 6 GB) exceeds the 126 MB L2',
                        'tc_tasks': ex.tc_task_count(), 'workers': workers, 'threads_per_cta': threads, 'smem_bytes': smem, 'loss_last_step': loss},
             'e2e': {'value': e2e_value, 'unit': 'steps/s', 'h2d_bytes_per_step': 2 * N * 4, 'd2h_bytes_per_step': 8, 'loss': e2e_loss},
             'gpu_launches': 3 * args.steps,
@@ -264,8 +313,12 @@ def run_ours(args, rank, world, local_rank):
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': None,
                          'peak_source': f'{pk_kind} bf16_tflops_sustained', 'flops_per_launch': gemm_fl + attn_fl},
         }
+        ex.close()
+        try:
+            line['busy'] = trace_split(bundle, local_rank)
+        except Exception as e:
+            line['busy'] = {'error': str(e)[:300]}
         if args.decode_tokens > 0 and world == 1:
-            ex.close()
             try:
                 line['decode'] = run_decode(args, local_rank)
             except Exception as e:      # the training line stands on its own
@@ -285,6 +338,34 @@ def run_ours(args, rank, world, local_rank):
     ex.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+OP_FAMILY = {122: 'gemm_tc', 34: 'gemm_f32', 114: 'gemm_f32', 45: 'attention', 46: 'attention', 47: 'attention', 48: 'attention', 35: 'norm', 37: 'norm', 39: 'norm',
+             61: 'colsum', 127: 'cross_entropy', 52: 'cross_entropy', 54: 'adamw', 55: 'gradnorm', 56: 'gradnorm', 113: 'round_bf16', 41: 'gelu_bwd', 32: 'embedding',
+             33: 'embedding', 0: 'noop', 62: 'plumbing', 60: 'plumbing'}
+
+
+def trace_split(bundle, device, flags=0):
+    """ONE traced step, outside every timed region: the fraction of worker time spent inside tasks (sum(end - start) /
+    (workers x span), the reference's formula, results/2026-11-11-162m-ceiling/README.md:50-56) and its split by op family."""
+    from kvm_b200.executor import Executor
+    with Executor(device=device, trace=True, flags=flags) as ex:
+        ex.load(bundle)
+        ex.run()
+        res = ex.run()
+        st, en, _ = ex.trace()
+        workers = ex.launch_info()[0]
+    ok = (en > st) & (st > 0)
+    span = float(en[ok].max() - st[ok].min())
+    dur = (en - st).astype(np.float64) * ok
+    fam = {}
+    for op in np.unique(bundle.tasks['op_id']):
+        sel = bundle.tasks['op_id'] == op
+        name = OP_FAMILY.get(int(op), f'op{int(op)}')
+        fam[name] = fam.get(name, 0.0) + float(dur[sel].sum())
+    return {'busy_frac': float(dur.sum() / (workers * span)), 'busy_frac_by_family': {k: round(v / (workers * span), 4) for k, v in sorted(fam.items(), key=lambda kv: -kv[1])},
+            'idle_frac': float(1.0 - dur.sum() / (workers * span)), 'traced_step_ms': res.ms, 'span_ms': span / 1e6, 'workers': workers,
+            'note': 'one traced step after the timed region (tracing adds two timestamps and a store per task)'}
 
 
 def run_dp(args, rank, world, local_rank):
@@ -356,9 +437,9 @@ def run_dp(args, rank, world, local_rank):
         print(json.dumps({
             'metric': 'gpt162m_train_steps_per_s', 'value': value, 'unit': 'steps/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': wall_total / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
-            'config': {'workload': f'{args.model} training step, micro-batch {cfg.batch}x{cfg.seq} per GPU, bf16 storage + f32 masters, AdamW; data parallel: backward launch, '
-                                   f'NCCL all-reduce (mean) of {n_arena * 4 / 1e6:.0f} MB of f32 gradients, optimizer launch',
-                       'tokens_per_step_per_gpu': cfg.tokens, 'parallelism': f'dp{world}', 'l2': 'per-step working set (> 6 GB) exceeds the 126 MB L2',
+            'config': {'workload': workload_name(args.model, cfg), 'tokens_per_step_per_gpu': cfg.tokens, 'parallelism': f'dp{world}',
+                       'engine': f'data parallel: backward launch, NCCL all-reduce (mean) of {n_arena * 4 / 1e6:.0f} MB of f32 gradients, optimizer launch',
+                       'l2': 'per-step working set (> 6 GB) exceeds the 126 MB L2',
                        'device_ms_per_step': ms_step, 'allreduce_ms_per_step': float(np.mean(comm_ms)), 'loss_last_step_rank0': loss,
                        'replicas_equal': bool(float(wmax) == float(wmin))},
             'e2e': {'value': value, 'unit': 'steps/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0, 'note': 'multi-GPU arm keeps tokens resident; the 1-GPU line carries the host-copy arm'},
@@ -530,7 +611,113 @@ def run_alone(device):
     gbs = rows * ntask * K * 2 / (ms * 1e-3) / 1e9
     peak = pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])
     out['gemv_k4096'] = {'shape': [rows * ntask, K], 'tasks': ntask, 'ms': ms, 'achieved': gbs, 'unit': 'GB/s', 'peak': peak, 'frac': gbs / peak, 'bound': 'hbm'}
+    out.update(run_alone_more(device, pk))
     out['note'] = f'whole launches (about 17 us of launch, arming and shutdown included); peaks: {kind}'
+    return out
+
+
+def run_alone_more(device, pk):
+    """Attention (TFLOP/s) and the memory-bound families (GB/s of their algorithmic bytes) alone, at the GPT-162M step's sizes and
+    task granularity: graphs of independent tasks of one kind, operands larger than L2."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.gpt import _Emit, preset
+    out = {}
+    hbm, tfl = pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), pk.get('bf16_tflops_sustained', PEAK_FALLBACK['bf16_tflops_sustained'])
+    cfg = preset('gpt_162m')
+    N, d, F, V, T, H = cfg.tokens, cfg.d_model, cfg.d_ff, cfg.vocab, cfg.seq, cfg.heads
+    sd = lambda n, sc: {'kind': 'seeded', 'seed': n, 'scale': sc, 'dist': 'normal'}
+
+    def timed(g):
+        bundle = g.to_bundle(check=False)
+        with Executor(device=device) as ex:
+            ex.load(bundle); ex.run()
+            return min(ex.run().ms for _ in range(3)), bundle
+
+    def emitter():
+        e = _Emit.__new__(_Emit)
+        from kvm_b200.workloads.graph import Graph
+        e.c, e.g, e.bf, e.act, e.params, e.prio = cfg, Graph('alone'), True, 'bf16', {}, 5
+        e.g.join_threshold = cfg.join_threshold
+        return e
+
+    # ---- causal attention forward / dq / dkv on bf16 q, k, v (tcgen05 path), 3 independent copies
+    reps = 3
+    e = emitter(); g = e.g
+    for r in range(reps):
+        q, k, v, do = (g.buffer(f'{n}{r}', N, d, 'bf16', sd(10 * r + i, 1.0)) for i, n in enumerate(('q', 'k', 'v', 'do')))
+        o, lse = g.buffer(f'o{r}', N, d, 'bf16'), g.buffer(f'lse{r}', cfg.batch * H * T, 1)
+        e.attention(f'f{r}', q, k, v, o, lse)
+    ms, b = timed(g)
+    fl = float(task_flops(b).sum())
+    out['attention_fwd'] = {'tasks': len(b.tasks), 'ms': ms, 'achieved': fl / (ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'peak': tfl, 'frac': fl / (ms * 1e-3) / 1e12 / tfl, 'bound': 'tensor'}
+    e = emitter(); g = e.g
+    for r in range(reps):
+        q, k, v, do, o = (g.buffer(f'{n}{r}', N, d, 'bf16', sd(10 * r + i, 1.0)) for i, n in enumerate(('q', 'k', 'v', 'do', 'o')))
+        lse = g.buffer(f'lse{r}', cfg.batch * H * T, 1, init={'kind': 'fill', 'value': 5.0})
+        delta = g.buffer(f'delta{r}', cfg.batch * H * T, 1)
+        dq, dk, dv = (g.buffer(f'd{n}{r}', N, d, 'bf16') for n in 'qkv')
+        e.attention_bwd(f'b{r}', q, k, v, o, lse, do, delta, dq, dk, dv)
+    ms, b = timed(g)
+    fl = float(task_flops(b).sum())
+    out['attention_bwd'] = {'tasks': len(b.tasks), 'ms': ms, 'achieved': fl / (ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'peak': tfl, 'frac': fl / (ms * 1e-3) / 1e12 / tfl, 'bound': 'tensor',
+                            'note': 'delta, dq and dkv tasks of one layer, dq / dkv after delta'}
+
+    def mem(name, g, nbytes):
+        ms, b = timed(g)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {'tasks': len(b.tasks), 'ms': ms, 'achieved': gbs, 'unit': 'GB/s', 'peak': hbm, 'frac': gbs / hbm, 'bound': 'hbm', 'algorithmic_bytes': nbytes}
+
+    # ---- layernorm forward: x f32 -> out bf16 (+ mean, rstd), 4 copies of the [N, d] activation
+    reps = 6
+    e = emitter(); g = e.g
+    gam, bet = g.buffer('gam', 1, d, init={'kind': 'fill', 'value': 1.0}), g.buffer('bet', 1, d)
+    for r in range(reps):
+        x = g.buffer(f'x{r}', N, d, init=sd(r + 1, 1.0))
+        e.layernorm(f'ln{r}', x, gam, bet, g.buffer(f'h{r}', N, d, 'bf16'), g.buffer(f'mu{r}', N, 1), g.buffer(f'rs{r}', N, 1))
+    mem('layernorm_fwd', g, reps * N * (d * 6 + 8))
+    # ---- layernorm backward dx (acc = 1): x f32, dy bf16, dx f32 read + written
+    e = emitter(); g = e.g
+    e.params = {}
+    g.buffer('w.p.g', 1, d, init={'kind': 'fill', 'value': 1.0})
+    for r in range(reps):
+        x, dy = g.buffer(f'x{r}', N, d, init=sd(r + 1, 1.0)), g.buffer(f'dy{r}', N, d, 'bf16', sd(r + 50, 1.0))
+        mu, rs = g.buffer(f'mu{r}', N, 1), g.buffer(f'rs{r}', N, 1, init={'kind': 'fill', 'value': 1.0})
+        dx = g.buffer(f'dx{r}', N, d)
+        e._rowwise = {x, dy, dx}
+        e.rows('layernorm_bwd_dx', f'lnb{r}', N, cfg.norm_rows, {'x': x, 'dy': dy, 'gamma': 'w.p.g', 'mean': mu, 'rstd': rs, 'dx': dx, 'd': d, 'acc': 1},
+               [x, dy, 'w.p.g', dx], [dx], vec_r=[mu, rs])
+    mem('layernorm_bwd_dx', g, reps * N * (d * 14 + 8))
+    # ---- fused cross entropy over bf16 logits: one read + one write of [N, V] (the second read of a row comes from cache)
+    e = emitter(); g = e.g
+    logits, dlog = g.buffer('logits', N, V, 'bf16', sd(1, 1.0)), g.buffer('dlogits', N, V, 'bf16')
+    tgt = g.buffer('tgt', N, 1, 'i32')
+    e._rowwise = {logits}
+    e.rows('softmax_ce_fused', 'ce', N, cfg.ce_rows, {'logits': logits, 'tgt': tgt, 'rowloss': g.buffer('rl', N, 1), 'lse': g.buffer('ls', N, 1), 'dlogits': dlog, 'V': V,
+                                                       'ignore': -1, 'N': N, 'scale': 1.0}, [logits], [dlog], vec_r=[tgt], vec_w=['rl', 'ls'])
+    mem('softmax_ce_fused', g, N * V * 4)
+    # ---- AdamW over 64 M parameters: p, g, m, v read, p, m, v written
+    e = emitter(); g = e.g
+    n_par = 64 << 20
+    for nm, init in (('p', sd(1, 0.02)), ('gr', sd(2, 0.01)), ('m', None), ('v', None)):
+        g.buffer(nm, n_par // 4096, 4096, init=init)
+    g.buffer('clip', 1, 2, init={'kind': 'fill', 'value': 1.0}); g.buffer('step', 1, 1, 'i32', {'kind': 'fill', 'value': 1})
+    for i, (e0, e1) in enumerate(g.flat_chunks('p', cfg.flat_chunk)):
+        rr = g.region_of('p', e0, e1)
+        g.task('adamw', {'p': 'p', 'g': 'gr', 'm': 'm', 'v': 'v', 'gscale': 'clip', 'step': 'step', 'e0': e0, 'e1': e1, 'lr': 6e-4, 'b1': 0.9, 'b2': 0.999, 'eps': 1e-8, 'wd': 0.1},
+               [('gr', *rr), 'clip', 'step'], [('p', *rr), ('m', *rr), ('v', *rr)], 1, f'adamw.{i}')
+    mem('adamw', g, n_par * 28)
+    # ---- residual add (f32 a + b -> out) and the f32 -> bf16 operand copy, over [N, F]-sized flats
+    for name, op, outdt, per in (('residual_add', 'residual_add', 'f32', 12), ('round_bf16', 'round_bf16', 'bf16', 6)):
+        e = emitter(); g = e.g
+        for r in range(4):
+            a = g.buffer(f'a{r}', N, F, init=sd(r + 1, 1.0))
+            o = g.buffer(f'o{r}', N, F, outdt)
+            if op == 'residual_add':
+                bb = g.buffer(f'b{r}', N, F, init=sd(r + 9, 1.0))
+                e.flat(op, [a, bb], [o], N * F, {'a': a, 'b': bb, 'out': o}, f'{op}{r}')
+            else:
+                e.flat(op, [a], [o], N * F, {'x': a, 'out': o}, f'{op}{r}')
+        mem(name, g, 4 * N * F * per)
     return out
 
 
@@ -567,6 +754,7 @@ def main():
     ap.add_argument('--decode-model', default='qwen3_8b')
     ap.add_argument('--decode-tokens', type=int, default=32, help='tokens of the decode measurement appended to the line (0 = skip)')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='length of the CPU-oracle sample behind cpu_baseline (0 = skip)')
+    ap.add_argument('--cpu-step-limit', type=float, default=240.0, help='--impl reference: time limit of the one real CPU step')
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get('RANK', 0)), int(os.environ.get('WORLD_SIZE', 1)), int(os.environ.get('LOCAL_RANK', 0))
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup

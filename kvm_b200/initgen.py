@@ -28,8 +28,8 @@ def splitmix64(seed: int, j: np.ndarray) -> np.ndarray:
         return z ^ (z >> np.uint64(31))
 
 
-def seeded_values(seed: int, n: int, draws: int, bias: float, coef: float) -> np.ndarray:
-    i = np.arange(n, dtype=np.uint64)
+def _seeded_range(seed: int, lo: int, hi: int, draws: int, bias: float, coef: float) -> np.ndarray:
+    i = np.arange(lo, hi, dtype=np.uint64)
     u = lambda j: (splitmix64(seed, j) >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
     if draws == 1:
         acc = u(i)
@@ -37,3 +37,21 @@ def seeded_values(seed: int, n: int, draws: int, bias: float, coef: float) -> np
         j = i * np.uint64(draws)
         acc = (u(j) + u(j + np.uint64(1))) + (u(j + np.uint64(2)) + u(j + np.uint64(3)))
     return ((acc - np.float32(bias)) * np.float32(coef)).astype(np.float32)
+
+
+def seeded_values(seed: int, n: int, draws: int, bias: float, coef: float) -> np.ndarray:
+    """Elements 0..n-1 of the seeded buffer.  Every element depends on its own index only, so large buffers are generated in
+    cache-sized pieces on all host threads (numpy releases the interpreter lock inside its loops)."""
+    chunk = 1 << 18
+    if n <= 2 * chunk:
+        return _seeded_range(seed, 0, n, draws, bias, coef)
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    out = np.empty(n, np.float32)
+
+    def fill(lo):
+        hi = min(lo + chunk, n)
+        out[lo:hi] = _seeded_range(seed, lo, hi, draws, bias, coef)
+    with ThreadPoolExecutor(max_workers=os.cpu_count() or 1) as pool:
+        list(pool.map(fill, range(0, n, chunk)))
+    return out

@@ -56,7 +56,7 @@ class VM:
         if f64:
             from .f64 import ops_f64
             self.opsmod = ops_f64()
-        self.zeros = zeros      # timing-only mode: every buffer starts as zeros instead of its init (values do not change op cost)
+        self.zeros = zeros      # timing-only mode: True = every buffer starts as zeros instead of its init; a callable(spec) -> array supplies other stand-in values
         # lazy=True materialises a buffer at its first use (bounded timing samples touch a fraction of a large model)
         self.bufs = buffers if buffers is not None else [None if lazy else materialize(bundle, b) for b in bundle.buffers]
         if f64:
@@ -85,8 +85,12 @@ class VM:
             if a.type == 'buf':
                 if w != abi.ABSENT_BUF and self.bufs[int(w)] is None:
                     spec = self.bundle.buffers[int(w)]
-                    self.bufs[int(w)] = Buf(np.zeros((spec['rows'], spec['cols']), np.int32 if spec['dtype'] == I32 else np.float32), spec['dtype']) \
-                        if self.zeros else materialize(self.bundle, spec)
+                    if callable(self.zeros):
+                        self.bufs[int(w)] = Buf(self.zeros(spec), spec['dtype'])
+                    elif self.zeros:
+                        self.bufs[int(w)] = Buf(np.zeros((spec['rows'], spec['cols']), np.int32 if spec['dtype'] == I32 else np.float32), spec['dtype'])
+                    else:
+                        self.bufs[int(w)] = materialize(self.bundle, spec)
                 bufs[a.name] = None if w == abi.ABSENT_BUF else self.bufs[int(w)]
             elif a.type == 'i32':
                 scal[a.name] = int(w)
