@@ -536,6 +536,7 @@ def run_decode(args, device):
     ex.load(bundle)
     ntok, warm = args.decode_tokens, 3
     ex.run_steps(warm)
+    path = ex.plan_info()
     res = ex.run_steps(ntok)
     tok_s = ntok / (res.ms / 1e3)
     ctx_mid = cfg.ctx + warm + ntok / 2
@@ -552,7 +553,8 @@ def run_decode(args, device):
                                                       f'vocab {cfg.vocab}, bf16 weights, batch {cfg.batch}, context {cfg.ctx}, greedy; {len(bundle.tasks)} tasks per token, no QK-norm',
            'value': tok_s, 'unit': 'tok/s', 'ms_per_token': res.ms / ntok, 'tokens': ntok, 'e2e': {'value': e2e, 'unit': 'tok/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 4},
            'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'unit': 'GB/s', 'frac': gbs / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
-                        'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0])}
+                        'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0]),
+           'path': {'static_schedule': path[0], 'stream_ring': path[1], 'planned_us_per_token': path[2]}}
     ex.close()
     try:        # the same shape with 8 independent users (one row each, as the reference serves a batch): every user streams the weights again
         cfg8 = preset(args.decode_model, batch=8)

@@ -141,6 +141,10 @@ int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t 
 int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32_t* smid, int32_t n);
 /* Launch geometry of the persistent kernel: worker CTAs, threads per CTA, dynamic shared memory bytes. */
 int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes);
+/* Which path runs the prepared program: the ready queue (0) or per-worker lists planned on the host (1: the reference's static
+ * path, include/mvm_static.h:1-17, mvm_exec.cu:1364-1502), whether that launch carries the shared-memory stream ring of the
+ * decode ops, and the planner's estimate of one run in microseconds (0 on the ready-queue path).  Valid after kvm_rearm or a run. */
+int kvm_plan_info(KvmExec* h, int32_t* is_static, int32_t* stream_ring, float* planned_us);
 /* Number of submitted tasks the host planned onto the tcgen05 / TMA path (the rest run SIMT bodies). */
 int kvm_tc_task_count(KvmExec* h);
 const char* kvm_last_error(KvmExec* h);

@@ -12,7 +12,8 @@ LIB = PKG / 'libkvm_b200.so'
 CLI = PKG / 'kvm_exec'
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 CXX = os.environ.get('CXX', 'g++')
-FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-std=c++17', '-lineinfo', '-shared', '-Xcompiler', '-fPIC',
+UNITS = ('kvm_exec', 'kvm_static')
+FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-std=c++17', '-lineinfo', '-Xcompiler', '-fPIC',
          '--expt-relaxed-constexpr', '--extended-lambda', '-Xcudafe', '--diag_suppress=177']
 
 
@@ -28,14 +29,26 @@ def stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Two translation units (the ready-queue kernel + host code, the static-schedule kernel), compiled side by side, then linked."""
     if not force and not stale():
         return LIB
-    cmd = [NVCC, *FLAGS, *(['-Xptxas', '-v'] if verbose else []), str(CSRC / 'kvm_exec.cu'), '-o', str(LIB), '-lcudart']
+    objs, procs = [], []
+    for unit in UNITS:
+        obj = PKG / f'_{unit}.o'
+        objs.append(obj)
+        cmd = [NVCC, *FLAGS, *(['-Xptxas', '-v'] if verbose else []), '-c', str(CSRC / f'{unit}.cu'), '-o', str(obj)]
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    for cmd, p in procs:
+        out, err = p.communicate()
+        if verbose or p.returncode:
+            sys.stderr.write(out + err)
+        if p.returncode:
+            raise RuntimeError(f'nvcc failed ({p.returncode}): {" ".join(cmd)}')
+    cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', *map(str, objs), '-o', str(LIB), '-lcudart']
     r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or r.returncode:
-        sys.stderr.write(r.stdout + r.stderr)
     if r.returncode:
-        raise RuntimeError(f'nvcc failed ({r.returncode}): {" ".join(cmd)}')
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError(f'link failed ({r.returncode}): {" ".join(cmd)}')
     return LIB
 
 

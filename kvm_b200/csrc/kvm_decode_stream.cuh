@@ -45,7 +45,7 @@ __device__ __forceinline__ float kvm_bf16hi(uint32_t u) { return __uint_as_float
 // 256-wide block; the other warps only help with the prologue.  Per row the KP partial sums are added in part order.
 // The activation row v = bf16(prologue(x)) is staged once as floats.  Returns false when the ring does not fit in the scratch
 // (the caller then uses the register-load form).
-__device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& x2, const KvmBuf& gm, const KvmBuf& w, const KvmBuf& out, const KvmBuf& res,
+static __device__ bool kvm_gemv_stream(const KvmCtx& c, const KvmBuf& x, const KvmBuf& x2, const KvmBuf& gm, const KvmBuf& w, const KvmBuf& out, const KvmBuf& res,
                                 int n0, int n1, int K, int pro, float eps) {
   const int rows = n1 - n0;
   int R = KVM_GS_UNITS;
@@ -214,46 +214,32 @@ __device__ __forceinline__ void kvm_decode_scores(const unsigned char* Ks, const
 #define KVM_AS_OFF_ML (KVM_AS_OFF_INV + 1536)
 #define KVM_AS_OFF_SC (KVM_AS_OFF_ML + 64)
 #define KVM_ATTN_EMPTY_M_STREAM (-3.4028234663852886e38f)
-template <int GT, class Pro, class Emit>
-__device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
-                                       Pro prologue, Emit emit) {
-  const int nk = max(j1 - j0, 0), ncp = hd >> 1, KQ = KVM_NT / ncp;
-  const int off_sc = KVM_AS_OFF_SC, off_red = off_sc + ((nk + 3) & ~3) * 32, off_k = (off_red + KQ * G * hd * 4 + 127) & ~127;
-  const int tile = (nk * hd * 2 + 127) & ~127;
-  if (off_k + 2 * tile > c.smem_bytes) return false;
-  unsigned char* sm = c.smem;
-  const uint32_t barK = kvm_smem_addr(sm), barV = barK + 8;
+// The part of the split attention that runs once the key / value tiles are on their way into shared memory: prologue (rotated
+// queries, the appended key / value), scores, softmax over the split, PV, emit.  `sm` is the op scratch (queries, scores and
+// reduction space at the KVM_AS_OFF_* offsets), Ks / Vs the staged tiles [nk][hd] bf16 wherever the caller keeps them;
+// waitK() / waitV() block until the respective tile has landed and return false if the wait ran out.  Whole compute group;
+// returns false if a wait ran out (the results are then not meaningful, the caller records the timeout).
+template <int GT, class Pro, class WaitK, class WaitV, class Emit>
+static __device__ bool kvm_attn_part_core(unsigned char* sm, unsigned char* Ks, unsigned char* Vs, int nk, int newrow, int G, int hd, float sc, Pro prologue, WaitK waitK,
+                                   WaitV waitV, Emit emit) {
+  const int ncp = hd >> 1, KQ = KVM_NT / ncp;
+  const int off_sc = KVM_AS_OFF_SC, off_red = off_sc + ((nk + 3) & ~3) * 32;
   const float* qs = (const float*)(sm + KVM_AS_OFF_QS);
   const float* knew = (const float*)(sm + KVM_AS_OFF_KNEW);
   const float* vnew = (const float*)(sm + KVM_AS_OFF_VNEW);
   float* ml = (float*)(sm + KVM_AS_OFF_ML);                // m[8], l[8]
   float* ps = (float*)(sm + off_sc);
   float* red = (float*)(sm + off_red);
-  unsigned char* Ks = sm + off_k;
-  unsigned char* Vs = Ks + tile;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int ncopy = newrow >= 0 ? nk - 1 : nk;             // the appended key is the last one of its split
   bool ok = true;
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // earlier plain accesses to this scratch come before the copies
-  kvm_sync();
-  if (tid == 0) {
-    kvm_mbar_init(barK, 1); kvm_mbar_init(barV, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async;" ::: "memory");       // rows appended by earlier tasks were written with plain stores
-    const uint32_t bytes = (uint32_t)(ncopy * hd * 2);
-    kvm_mbar_expect_tx(barK, bytes);
-    if (bytes) kvm_bulk_g2s(kvm_smem_addr(Ks), (const __nv_bfloat16*)kc.p + (base + j0) * kc.ld, bytes, barK);
-    kvm_mbar_expect_tx(barV, bytes);
-    if (bytes) kvm_bulk_g2s(kvm_smem_addr(Vs), (const __nv_bfloat16*)vc.p + (base + j0) * vc.ld, bytes, barV);
-  }
   prologue();                                                      // queries (and the appended key / value) while the copies fly
   kvm_sync();
-  if (newrow >= 0) for (int cc = tid; cc < hd; cc += KVM_NT) {
+  if (newrow >= 0) for (int cc = tid; cc < hd; cc += KVM_NT) {     // the copies leave the appended row out: these bytes are the threads' alone
     ((__nv_bfloat16*)Ks)[(size_t)(nk - 1) * hd + cc] = __float2bfloat16_rn(knew[cc]);
     ((__nv_bfloat16*)Vs)[(size_t)(nk - 1) * hd + cc] = __float2bfloat16_rn(vnew[cc]);
   }
   kvm_sync();
-  if (!kvm_mbar_wait_t(barK, 0)) ok = false;
+  if (!waitK()) ok = false;
 
   // ---- scores (see kvm_decode_scores): the smallest number of pieces per lane that fits a key into one warp
   {
@@ -285,7 +271,7 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
     }
   }
   kvm_sync();
-  if (!kvm_mbar_wait_t(barV, 0)) ok = false;
+  if (!waitV()) ok = false;
   // ---- PV
   {
     const int kq = tid / ncp, c2 = tid % ncp;
@@ -312,6 +298,40 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
     for (int q = 0; q < KQ; ++q) A += red[((size_t)q * G + g) * hd + cc];
     emit(g, cc, ml[g], ml[8 + g], A);
   }
+  return ok;
+}
+// Scratch bytes the core needs ahead of the tiles for a split of nk keys.
+__device__ __forceinline__ int kvm_attn_part_scratch(int nk, int G, int hd) {
+  const int KQ = KVM_NT / (hd >> 1);
+  return (KVM_AS_OFF_SC + ((nk + 3) & ~3) * 32 + KQ * G * hd * 4 + 127) & ~127;
+}
+
+template <int GT, class Pro, class Emit>
+static __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
+                                       Pro prologue, Emit emit) {
+  const int nk = max(j1 - j0, 0);
+  const int off_k = kvm_attn_part_scratch(nk, G, hd);
+  const int tile = (nk * hd * 2 + 127) & ~127;
+  if (off_k + 2 * tile > c.smem_bytes) return false;
+  unsigned char* sm = c.smem;
+  const uint32_t barK = kvm_smem_addr(sm), barV = barK + 8;
+  unsigned char* Ks = sm + off_k;
+  unsigned char* Vs = Ks + tile;
+  const int tid = threadIdx.x;
+  const int ncopy = newrow >= 0 ? nk - 1 : nk;             // the appended key is the last one of its split
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // earlier plain accesses to this scratch come before the copies
+  kvm_sync();
+  if (tid == 0) {
+    kvm_mbar_init(barK, 1); kvm_mbar_init(barV, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async;" ::: "memory");       // rows appended by earlier tasks were written with plain stores
+    const uint32_t bytes = (uint32_t)(ncopy * hd * 2);
+    kvm_mbar_expect_tx(barK, bytes);
+    if (bytes) kvm_bulk_g2s(kvm_smem_addr(Ks), (const __nv_bfloat16*)kc.p + (base + j0) * kc.ld, bytes, barK);
+    kvm_mbar_expect_tx(barV, bytes);
+    if (bytes) kvm_bulk_g2s(kvm_smem_addr(Vs), (const __nv_bfloat16*)vc.p + (base + j0) * vc.ld, bytes, barV);
+  }
+  const bool ok = kvm_attn_part_core<GT>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, [&]() { return kvm_mbar_wait_t(barK, 0); }, [&]() { return kvm_mbar_wait_t(barV, 0); }, emit);
   if (!ok) kvm_stream_timeout(c, 135);
   kvm_sync();
   if (tid == 0) { kvm_mbar_inval(barK); kvm_mbar_inval(barV); }
@@ -320,7 +340,7 @@ __device__ bool kvm_attn_part_stream_t(const KvmCtx& c, const KvmBuf& kc, const 
 
 // Dispatch on the group size; false = not taken (layout, size or dtype outside what the streaming form handles).
 template <class Pro, class Emit>
-__device__ bool kvm_attn_part_stream(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
+static __device__ bool kvm_attn_part_stream(const KvmCtx& c, const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int newrow, int G, int hd, float sc,
                                      Pro prologue, Emit emit) {
   if (kc.dtype != KVM_BF16 || vc.dtype != KVM_BF16 || kc.ld != hd || vc.ld != hd || !kvm_vec_ok(kc) || !kvm_vec_ok(vc) || G > 8 || (G & (G - 1)) ||
       !(hd == 16 || hd == 32 || hd == 64 || hd == 128)) return false;

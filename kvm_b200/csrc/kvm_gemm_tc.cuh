@@ -157,7 +157,7 @@ __device__ __forceinline__ bool kvm_tc_epi_vec_ok(const KvmMmArgs& g) {
   return (g.out.ld & 7) == 0 && kvm_vec_ok(g.out) && (g.n0 & 7) == 0 && (!g.res.p || ((g.res.ld & 7) == 0 && kvm_vec_ok(g.res))) &&
          (!g.pre.p || ((g.pre.ld & 7) == 0 && kvm_vec_ok(g.pre))) && (!g.bias.p || (((uintptr_t)g.bias.p & 15) == 0));
 }
-__device__ void kvm_tc_epilogue_staged(const KvmCtx& c, const KvmMmArgs& g, uint32_t tmem_acc, int m_base, bool ok) {
+static __device__ void kvm_tc_epilogue_staged(const KvmCtx& c, const KvmMmArgs& g, uint32_t tmem_acc, int m_base, bool ok) {
   float* T = (float*)c.smem;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = warp & 3, cgi = warp >> 2;
 #pragma unroll
@@ -213,7 +213,7 @@ __device__ void kvm_tc_epilogue_staged(const KvmCtx& c, const KvmMmArgs& g, uint
 // Barriers: the attention set (full 0..2, empty 3..5, accumulator 6) with their completed-phase counts in ctl[KVM_CTL_ACNT + i].
 #define KVM_TCP_STAGES 3
 #define KVM_TCP_STAGE_BYTES (2 * KVM_TC_A_BYTES + KVM_TC_B_BYTES)
-__device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const int4& aux) {
+static __device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const int4& aux) {
   int* ctl = c.ctl;
   int* cnt = ctl + KVM_CTL_ACNT;
   auto bar = [&](int i) { return kvm_bar_addr(ctl, KVM_CTL_ABAR + i); };
@@ -300,7 +300,7 @@ __device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const int4& 
 }
 
 // aux.x = 1: tensor-core path planned by the host (aux.y / aux.z = tensor-map indices of A / B); else SIMT fallback.
-__device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
+static __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmMmArgs g;
   if (!kvm_mm_args(c, a, 2, g)) return;
   if (aux.x != 1 || (c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) { kvm_mm_simt(c, g); return; }

@@ -8,6 +8,14 @@
 
 struct KvmOwned { void* p; size_t bytes; };
 
+// Result of the host planner of the static-schedule path (kvm_static_host.inl).
+struct KvmStaticPlan {
+  std::vector<int> prog, prog_off, waits;
+  std::vector<int> wait_off, wait_cnt, stream;      // per task
+  bool ring = false;                                // the program streams (decode GEMVs / split attention): launch with the stage ring
+  double makespan_us = 0.0;                         // the planner's estimate of one run
+};
+
 struct KvmExec {
   KvmConfig cfg{};
   int device = 0, sms = 0, workers = 0, smem_bytes = 0, nvars = 64;
@@ -35,6 +43,9 @@ struct KvmExec {
   bool started = false, armed = false;
   bool has_gemv = false;         // a submitted task is a gemv_bf16: its shared-memory ring is worth more than the buffer-table cache
   bool own_stream = true;        // false after kvm_set_stream: the caller's stream is used and never destroyed here
+  bool use_static = false;       // the resident program runs as per-worker lists (kvm_static.cuh); decided when the tasks are uploaded
+  KvmStaticPlan splan;
+  int *d_prog = nullptr, *d_prog_off = nullptr, *d_waits = nullptr, *d_progress = nullptr;
   std::vector<std::string> buf_names;              // by buffer index; "" where the caller gave none (kvm_load_bundle_dir fills them from metadata.json)
   std::map<std::string, int> var_ids;              // version variables by name (from metadata.json)
   KvmResult last{};
@@ -49,8 +60,10 @@ static bool kvm_feature_on(const char* env, int dflt) {
 
 static void kvm_free_tasks(KvmExec* h) {
   for (void* p : {(void*)h->d_tasks, (void*)h->d_succ, (void*)h->d_args, (void*)h->d_aux, (void*)h->d_tmaps, (void*)h->d_indeg, (void*)h->d_exec, (void*)h->d_ring,
-                  (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend, (void*)h->d_recs, (void*)h->d_claim})
+                  (void*)h->d_park_next, (void*)h->d_tsmid, (void*)h->d_tstart, (void*)h->d_tend, (void*)h->d_recs, (void*)h->d_claim, (void*)h->d_prog, (void*)h->d_prog_off,
+                  (void*)h->d_waits, (void*)h->d_progress})
     if (p) cudaFree(p);
+  h->d_prog = h->d_prog_off = h->d_waits = h->d_progress = nullptr;
   h->d_tasks = nullptr; h->d_succ = nullptr; h->d_args = nullptr; h->d_aux = nullptr; h->d_tmaps = nullptr; h->d_indeg = h->d_exec = h->d_ring = h->d_park_next = h->d_tsmid = nullptr;
   h->d_tstart = h->d_tend = nullptr; h->d_recs = nullptr; h->d_claim = nullptr; h->task_cap = 0;
 }
@@ -99,6 +112,7 @@ extern "C" int kvm_create(const KvmConfig* cfg, KvmExec** out) {
   h->smem_bytes = (int)prop.sharedMemPerBlockOptin;
   h->nvars = h->cfg.num_vars > 0 ? h->cfg.num_vars : 64;
   if ((e = cudaFuncSetAttribute(kvm_exec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_bytes)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = kvm_static_set_smem(h->smem_bytes)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
   if ((e = cudaEventCreate(&h->ev0)) != cudaSuccess || (e = cudaEventCreate(&h->ev1)) != cudaSuccess) return fail("cudaEventCreate", e);
   if ((e = cudaMalloc(&h->d_ctl, 64 * sizeof(int))) != cudaSuccess || (e = cudaMalloc(&h->d_versions, h->nvars * sizeof(int))) != cudaSuccess ||
@@ -286,6 +300,7 @@ extern "C" int kvm_validate_batch(const KvmTaskDesc* tasks, int32_t nt, const in
 }
 
 static int kvm_plan_tc(KvmExec* h, int first_task);   // kvm_gemm_host.inl: tensor maps of the tensor-core tasks
+static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, KvmStaticPlan& plan);   // kvm_static_host.inl
 
 extern "C" int kvm_submit(KvmExec* h, const KvmTaskDesc* tasks, int32_t nt, const int32_t* succ, int32_t ne, const int32_t* args, int32_t na) {
   if (!h || !tasks || nt <= 0 || ne < 0 || na < 0 || (ne && !succ) || (na && !args)) { if (h) h->error = "kvm_submit: bad argument"; return KVM_E_ARG; }
@@ -445,6 +460,28 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   return S;
 }
 
+static KvmStaticState kvm_static_state(KvmExec* h) {
+  KvmStaticState T{};
+  T.D = kvm_dev_state(h);
+  T.prog = h->d_prog; T.prog_off = h->d_prog_off; T.waits = h->d_waits; T.progress = h->d_progress;
+  T.ring = h->splan.ring ? 1 : 0;
+  return T;
+}
+
+// Which path runs the resident program.  KVM_CFG_STATIC / KVM_CFG_DYNAMIC force one; otherwise the static path is taken for
+// programs of streaming decode tasks (gemv_bf16), where knowing a worker's next task lets the weights stream ahead of the
+// dependencies.  The environment variable KVM_B200_STATIC (0 / 1) overrides the default for measurements.
+static bool kvm_wants_static(KvmExec* h, bool has_gemv) {
+  if (h->cfg.flags & KVM_CFG_STATIC) return true;
+  if (h->cfg.flags & KVM_CFG_DYNAMIC) return false;
+  return kvm_feature_on("KVM_B200_STATIC", has_gemv ? 1 : 0);
+}
+
+static void kvm_launch(KvmExec* h) {
+  if (h->use_static) kvm_static_launch(kvm_static_state(h), h->workers, h->smem_bytes, h->stream);
+  else { KvmDevState S = kvm_dev_state(h); kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S); }
+}
+
 // Upload whatever changed since the last run, arm the counters and enqueue the roots.
 static int kvm_prepare(KvmExec* h, bool keep_error = false) {
   cudaSetDevice(h->device);
@@ -485,15 +522,33 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
     h->has_gemv = false;
+    for (const KvmTaskDesc& d : h->tasks) if (d.op_id == 134) h->has_gemv = true;
+    h->use_static = false;
+    if (kvm_wants_static(h, h->has_gemv)) {
+      std::vector<int> base(h->nvars, 0);
+      KVM_CUDA(cudaStreamSynchronize(h->stream));
+      KVM_CUDA(cudaMemcpy(base.data(), h->d_versions, h->nvars * sizeof(int), cudaMemcpyDeviceToHost));
+      const int r = kvm_plan_static(h, base, h->splan);
+      if (r == 0) h->use_static = true;
+      else if (h->cfg.flags & KVM_CFG_STATIC) return r;      // asked for explicitly: say why it cannot be done
+    }
+    if (h->use_static) {
+      const KvmStaticPlan& P = h->splan;
+      KVM_CUDA(cudaMalloc(&h->d_prog, (P.prog.size() + 1) * 4)); KVM_CUDA(cudaMalloc(&h->d_prog_off, P.prog_off.size() * 4));
+      KVM_CUDA(cudaMalloc(&h->d_waits, (P.waits.size() + 1) * 4)); KVM_CUDA(cudaMalloc(&h->d_progress, (size_t)h->workers * 4));
+      KVM_CUDA(cudaMemcpyAsync(h->d_prog, P.prog.data(), P.prog.size() * 4, cudaMemcpyHostToDevice, h->stream));
+      KVM_CUDA(cudaMemcpyAsync(h->d_prog_off, P.prog_off.data(), P.prog_off.size() * 4, cudaMemcpyHostToDevice, h->stream));
+      if (!P.waits.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_waits, P.waits.data(), P.waits.size() * 4, cudaMemcpyHostToDevice, h->stream));
+    }
     {   // one record per task for the workers: descriptor, argument words and path selector side by side (a single fetch per pop)
       std::vector<int32_t> recs(nt * (size_t)KVM_REC_WORDS, 0);
       for (size_t i = 0; i < nt; ++i) {
         int32_t* r = &recs[i * KVM_REC_WORDS];
         memcpy(r, &h->tasks[i], sizeof(KvmTaskDesc));
-        if (r[0] == 134) h->has_gemv = true;
         const int ao = r[6], aw = r[7] < KVM_MAX_ARGS ? r[7] : KVM_MAX_ARGS;
         for (int k = 0; k < aw; ++k) r[16 + k] = h->args[(size_t)ao + k];
         memcpy(r + 16 + KVM_MAX_ARGS, &h->aux[i], sizeof(int4));
+        if (h->use_static) { r[KVM_REC_WAIT_OFF] = h->splan.wait_off[i]; r[KVM_REC_WAIT_CNT] = h->splan.wait_cnt[i]; r[KVM_REC_STREAM] = h->splan.stream[i]; }
       }
       KVM_CUDA(cudaMalloc(&h->d_recs, recs.size() * 4));
       KVM_CUDA(cudaMemcpyAsync(h->d_recs, recs.data(), recs.size() * 4, cudaMemcpyHostToDevice, h->stream));
@@ -507,9 +562,14 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
   KVM_CUDA(cudaMemsetAsync(h->d_ctl, 0, 64 * sizeof(int), h->stream));
   if (!keep_error) KVM_CUDA(cudaMemsetAsync(h->d_err, 0, sizeof(KvmErrRec), h->stream));
   if (h->cfg.trace) { cudaMemsetAsync(h->d_tstart, 0, nt * 8, h->stream); cudaMemsetAsync(h->d_tend, 0, nt * 8, h->stream); }
-  const int blocks = (int)((nt > (size_t)h->nvars ? nt : (size_t)h->nvars) + 255) / 256;
-  kvm_arm_kernel<<<blocks, 256, 0, h->stream>>>(S);
-  kvm_roots_kernel<<<blocks, 256, 0, h->stream>>>(S);
+  size_t arm_n = nt > (size_t)h->nvars ? nt : (size_t)h->nvars;
+  if ((size_t)h->workers > arm_n) arm_n = h->workers;
+  const int blocks = (int)((arm_n + 255) / 256);
+  if (h->use_static) kvm_static_arm(kvm_static_state(h), h->workers, blocks, h->stream);
+  else {
+    kvm_arm_kernel<<<blocks, 256, 0, h->stream>>>(S);
+    kvm_roots_kernel<<<blocks, 256, 0, h->stream>>>(S);
+  }
   KVM_CUDA(cudaGetLastError());
   h->armed = true;
   return 0;
@@ -544,9 +604,8 @@ extern "C" int kvm_start(KvmExec* h) {
   cudaSetDevice(h->device);
   // buffers added or bound, or tasks submitted, after kvm_rearm: the device tables are stale, prepare again
   if (!h->armed || h->bufs_dirty || h->tasks_dirty) if (int r = kvm_prepare(h, chained)) return r;
-  KvmDevState S = kvm_dev_state(h);
   KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
-  kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);
+  kvm_launch(h);
   KVM_CUDA(cudaGetLastError());
   KVM_CUDA(cudaEventRecord(h->ev1, h->stream));
   h->started = true; h->armed = false;
@@ -598,8 +657,7 @@ extern "C" int kvm_run_steps(KvmExec* h, int32_t steps, KvmResult* res) {
   KVM_CUDA(cudaEventRecord(h->ev0, h->stream));
   for (int s = 0; s < steps; ++s) {
     if (s) if (int r = kvm_prepare(h, true)) return r;
-    KvmDevState S = kvm_dev_state(h);
-    kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S);
+    kvm_launch(h);
     KVM_CUDA(cudaGetLastError());
   }
   KVM_CUDA(cudaEventRecord(h->ev1, h->stream));
@@ -634,6 +692,15 @@ extern "C" int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, i
   return 0;
 }
 
+extern "C" int kvm_plan_info(KvmExec* h, int32_t* is_static, int32_t* stream_ring, float* planned_us) {
+  if (!h) return KVM_E_ARG;
+  if (h->tasks_dirty) { h->error = "kvm_plan_info: the program has not been prepared yet (kvm_rearm or a run does it)"; return KVM_E_STATE; }
+  if (is_static) *is_static = h->use_static ? 1 : 0;
+  if (stream_ring) *stream_ring = h->use_static && h->splan.ring ? 1 : 0;
+  if (planned_us) *planned_us = h->use_static ? (float)h->splan.makespan_us : 0.0f;
+  return 0;
+}
+
 extern "C" int kvm_tc_task_count(KvmExec* h) {
   if (!h) return KVM_E_ARG;
   int n = 0;
@@ -642,3 +709,4 @@ extern "C" int kvm_tc_task_count(KvmExec* h) {
 }
 
 #include "kvm_gemm_host.inl"
+#include "kvm_static_host.inl"

@@ -10,7 +10,7 @@
 
 #define KVM_ATTN_EMPTY_M (-3.4028234663852886e38f)
 
-__device__ void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
   KvmBuf kn, vn, kc, vc, lens;
   if (!kvm_buf(c, a[0], KVM_M_FLT, kn) || !kvm_buf(c, a[1], KVM_M_FLT, vn) || !kvm_buf(c, a[2], KVM_M_FLT, kc) || !kvm_buf(c, a[3], KVM_M_FLT, vc) ||
       !kvm_buf(c, a[4], KVM_M_I32, lens)) return;
@@ -32,7 +32,7 @@ __device__ void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
 // the 16 warps in warp order through shared memory, then handed to `emit(g, m, l, acc_of_column)` per head.
 //   qs: G*hd floats in shared memory (the query rows, already rotated)       ws: scratch of 16*G*(hd+2) floats
 template <class Emit>
-__device__ void kvm_decode_group(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+static __device__ void kvm_decode_group(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nc = (hd + 31) / 32;
   float m[8], l[8], acc[8][4];
 #pragma unroll
@@ -89,7 +89,7 @@ __device__ void kvm_decode_group(const KvmBuf& kc, const KvmBuf& vc, size_t base
 // keys per step; two steps of loads are in flight before the first is consumed.  Every lane group keeps its own online-softmax
 // state per head; groups are merged by shuffles, warps through shared memory as in kvm_decode_group, same emit contract.
 template <int GT, class Emit>
-__device__ void kvm_decode_group_vec_t(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+static __device__ void kvm_decode_group_vec_t(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int LPK = hd >> 3, KPI = 32 / LPK, slot = lane / LPK, c0 = (lane % LPK) * 8;
   float m[GT], l[GT], acc[GT][8];
@@ -164,7 +164,7 @@ __device__ void kvm_decode_group_vec_t(const KvmBuf& kc, const KvmBuf& vc, size_
   }
 }
 template <class Emit>
-__device__ void kvm_decode_group_vec(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
+static __device__ void kvm_decode_group_vec(const KvmBuf& kc, const KvmBuf& vc, size_t base, int j0, int j1, int G, int hd, float sc, const float* qs, float* ws, Emit emit) {
   if (G <= 1) kvm_decode_group_vec_t<1>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
   else if (G <= 2) kvm_decode_group_vec_t<2>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
   else if (G <= 4) kvm_decode_group_vec_t<4>(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
@@ -174,7 +174,7 @@ __device__ __forceinline__ bool kvm_decode_vec_ok(const KvmBuf& kc, const KvmBuf
   return hd >= 8 && hd <= 128 && (hd & (hd - 1)) == 0 && (kc.ld & 7) == 0 && (vc.ld & 7) == 0 && kvm_vec_ok(kc) && kvm_vec_ok(vc);
 }
 
-__device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, kc, vc, lens, o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
       !kvm_buf(c, a[4], KVM_M_FLT, o)) return;
@@ -196,7 +196,7 @@ __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   else kvm_decode_group(kc, vc, base, 0, n, 1, hd, sc, qs, ws, emit);
 }
 
-__device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, kc, vc, lens, part, kn, vn;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
       !kvm_buf(c, a[4], KVM_M_F32, part) || !kvm_buf(c, a[5], KVM_M_FLT, kn, true) || !kvm_buf(c, a[6], KVM_M_FLT, vn, true)) return;
@@ -264,7 +264,7 @@ __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
   else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
 }
 
-__device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, o;
   if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   const int b = a[2], h0 = a[3], h1 = a[4], S = a[5], H = a[6], hd = a[7];
@@ -295,7 +295,7 @@ __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
 // out[0,n] = sum_k v[k] w[n,k] (+ res[0,n]), v = bf16(prologue(x)); w bf16 [>=n1, K], rows contiguous in K.
 // The activation row is staged once per task in shared memory (as float); each warp then streams four weight rows at a
 // time with 16-byte loads, two k-steps in flight, float32 accumulation in a fixed order, warp-shuffle reduction.
-__device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, x2, gm, w, out, res;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, x2, true) || !kvm_buf(c, a[2], KVM_M_F32, gm, true) || !kvm_buf(c, a[3], KVM_M_BF16, w) ||
       !kvm_buf(c, a[4], KVM_M_FLT, out) || !kvm_buf(c, a[5], KVM_M_FLT, res, true)) return;
@@ -386,7 +386,7 @@ __device__ __forceinline__ unsigned kvm_order_key(float x) { const unsigned b = 
 
 // temp <= 0: argmax. Otherwise inverse-CDF over softmax(logits/temp) restricted to the topk largest (ties kept), weights and
 // running sum in double in index order by one thread (the reference's order; rows are short-lived serving rows).
-__device__ void kvm_op_sample(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_sample(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, out, ctr;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, out) || !kvm_buf(c, a[2], KVM_M_I32, ctr, true)) return;
   const int r0 = a[3], r1 = a[4], V = a[5], topk = a[7];

@@ -30,7 +30,7 @@ __device__ __forceinline__ float kvm_mm_epilogue(const KvmMmArgs& g, float acc, 
 }
 
 // Decode and check the 13 argument words shared by matmul_tile / matmul_tile_bf16 / matmul_mma_bf16.
-__device__ bool kvm_mm_args(const KvmCtx& c, const int32_t* a, int kind /*0 f32 tile, 1 bf16 tile, 2 mma 128x256*/, KvmMmArgs& g) {
+static __device__ bool kvm_mm_args(const KvmCtx& c, const int32_t* a, int kind /*0 f32 tile, 1 bf16 tile, 2 mma 128x256*/, KvmMmArgs& g) {
   const int opmask = kind == 0 ? KVM_M_F32 : KVM_M_FLT, omask = kind == 0 ? KVM_M_F32 : KVM_M_FLT;
   if (!kvm_buf(c, a[0], opmask, g.a) || !kvm_buf(c, a[1], opmask, g.b) || !kvm_buf(c, a[2], omask, g.out) || !kvm_buf(c, a[3], KVM_M_F32, g.bias, true) ||
       !kvm_buf(c, a[4], omask, g.res, true) || !kvm_buf(c, a[5], omask, g.pre, true)) return false;
@@ -52,7 +52,7 @@ __device__ bool kvm_mm_args(const KvmCtx& c, const int32_t* a, int kind /*0 f32 
 }
 
 // SIMT tile: 64x64 sub-tiles, K staged through shared memory 32 at a time; thread = (row, 8 columns).
-__device__ void kvm_mm_simt(const KvmCtx& c, const KvmMmArgs& g) {
+static __device__ void kvm_mm_simt(const KvmCtx& c, const KvmMmArgs& g) {
   float (*As)[65] = (float (*)[65])c.smem;                  // [32][65]: As[k][m]
   float (*Bs)[64] = (float (*)[64])(c.smem + 32 * 65 * 4);  // [32][64]: Bs[k][n]
   const bool ta = g.flags & 1, tb = g.flags & 2;
@@ -101,16 +101,16 @@ __device__ void kvm_mm_simt(const KvmCtx& c, const KvmMmArgs& g) {
     }
 }
 
-__device__ void kvm_op_matmul_tile(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_matmul_tile(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g;
   if (kvm_mm_args(c, a, 0, g)) kvm_mm_simt(c, g);
 }
-__device__ void kvm_op_matmul_tile_bf16(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_matmul_tile_bf16(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g;
   if (kvm_mm_args(c, a, 1, g)) kvm_mm_simt(c, g);
 }
 // out[m,n] = a[m,k] @ b[k,n] from element 0, contiguous (include/mvm_ops.def:14; runtime/ref_ops.py:55-64).
-__device__ void kvm_op_matmul(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_matmul(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g{};
   if (!kvm_buf(c, a[0], KVM_M_F32, g.a) || !kvm_buf(c, a[1], KVM_M_F32, g.b) || !kvm_buf(c, a[2], KVM_M_F32, g.out)) return;
   const int m = a[3], n = a[4], k = a[5];

@@ -6,7 +6,7 @@
 #include "kvm_dev.cuh"
 
 // ---- embeddings --------------------------------------------------------------------------------------------------------------
-__device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf ids, wte, wpe, out;
   if (!kvm_buf(c, a[0], KVM_M_I32, ids) || !kvm_buf(c, a[1], KVM_M_FLT, wte) || !kvm_buf(c, a[2], KVM_M_FLT, wpe, true) ||
       !kvm_buf(c, a[3], KVM_M_FLT, out)) return;
@@ -30,7 +30,7 @@ __device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
 // One task owns keys [v0,v1): rows with a key in range are compacted in ascending order into shared memory (block-wide
 // ordered scan), then added row by row, each thread owning columns, so every element sums its rows in ascending order
 // with one float32 add each (runtime/ref_gpt.py:55-66).
-__device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf ids, dout, dt;
   if (!kvm_buf(c, a[0], KVM_M_I32, ids, true) || !kvm_buf(c, a[1], KVM_M_FLT, dout) || !kvm_buf(c, a[2], KVM_M_F32, dt)) return;
   int N = a[3], mod = a[4], v0 = a[5], v1 = a[6], d = a[7], acc = a[8];
@@ -87,7 +87,7 @@ __device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-__device__ void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, pos, out;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, pos) || !kvm_buf(c, a[2], KVM_M_FLT, out)) return;
   int r0 = a[3], r1 = a[4], T = a[5], d = a[6];
@@ -99,7 +99,7 @@ __device__ void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-__device__ void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
   KvmBuf src, idx, dst;
   if (!kvm_buf(c, a[0], KVM_M_FLT, src) || !kvm_buf(c, a[1], KVM_M_I32, idx) || !kvm_buf(c, a[2], KVM_M_FLT, dst)) return;
   int r0 = a[3], r1 = a[4], d = a[5];
@@ -116,7 +116,7 @@ __device__ void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
 
 // ---- normalisation: one warp per row -----------------------------------------------------------------------------------------
 template <bool RMS>
-__device__ void kvm_norm_fwd(const KvmCtx& c, int xi, int gi, int bi, int oi, int mi, int ri, int r0, int r1, int d, float eps) {
+static __device__ void kvm_norm_fwd(const KvmCtx& c, int xi, int gi, int bi, int oi, int mi, int ri, int r0, int r1, int d, float eps) {
   KvmBuf x, g, be, out, mean, rstd;
   if (!kvm_buf(c, xi, KVM_M_FLT, x) || !kvm_buf(c, gi, KVM_M_F32, g) || !kvm_buf(c, bi, KVM_M_F32, be, RMS) || !kvm_buf(c, oi, KVM_M_FLT, out) ||
       !kvm_buf(c, mi, KVM_M_F32, mean, RMS) || !kvm_buf(c, ri, KVM_M_F32, rstd)) return;
@@ -193,15 +193,15 @@ __device__ void kvm_norm_fwd(const KvmCtx& c, int xi, int gi, int bi, int oi, in
     if (lane == 0) { ((float*)rstd.p)[r] = rs; if (!RMS) ((float*)mean.p)[r] = mu; }
   }
 }
-__device__ void kvm_op_layernorm_fwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_layernorm_fwd(const KvmCtx& c, const int32_t* a) {
   kvm_norm_fwd<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], kvm_bits_f32(a[9]));
 }
-__device__ void kvm_op_rmsnorm_fwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_rmsnorm_fwd(const KvmCtx& c, const int32_t* a) {
   kvm_norm_fwd<true>(c, a[0], a[1], -1, a[2], -1, a[3], a[4], a[5], a[6], kvm_bits_f32(a[7]));
 }
 
 template <bool RMS>
-__device__ void kvm_norm_bwd_dx(const KvmCtx& c, int xi, int dyi, int gi, int mi, int ri, int dxi, int r0, int r1, int d, int acc) {
+static __device__ void kvm_norm_bwd_dx(const KvmCtx& c, int xi, int dyi, int gi, int mi, int ri, int dxi, int r0, int r1, int d, int acc) {
   KvmBuf x, dy, g, mean, rstd, dx;
   if (!kvm_buf(c, xi, KVM_M_FLT, x) || !kvm_buf(c, dyi, KVM_M_FLT, dy) || !kvm_buf(c, gi, KVM_M_F32, g) || !kvm_buf(c, mi, KVM_M_F32, mean, RMS) ||
       !kvm_buf(c, ri, KVM_M_F32, rstd) || !kvm_buf(c, dxi, KVM_M_FLT, dx)) return;
@@ -254,13 +254,13 @@ __device__ void kvm_norm_bwd_dx(const KvmCtx& c, int xi, int dyi, int gi, int mi
     }
   }
 }
-__device__ void kvm_op_layernorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9]); }
-__device__ void kvm_op_rmsnorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<true>(c, a[0], a[1], a[2], -1, a[3], a[4], a[5], a[6], a[7], a[8]); }
+static __device__ void kvm_op_layernorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9]); }
+static __device__ void kvm_op_rmsnorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<true>(c, a[0], a[1], a[2], -1, a[3], a[4], a[5], a[6], a[7], a[8]); }
 
 // Column sums over R rows for columns [c0,c1): thread = (row group, column), row groups reduced in fixed order through
 // shared memory.  MODE 0: colsum of x; MODE 1: dgamma / dbeta of a norm layer.
 template <int MODE>
-__device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy, const KvmBuf& mean, const KvmBuf& rstd, float* o1, float* o2,
+static __device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy, const KvmBuf& mean, const KvmBuf& rstd, float* o1, float* o2,
                               int R, int c0, int c1, int acc) {
   float* red = (float*)c.smem;                    // [2][KVM_NT]
   for (int cb = c0; cb < c1; cb += 64) {
@@ -288,14 +288,14 @@ __device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy
     }
   }
 }
-__device__ void kvm_op_colsum(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_colsum(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, out, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_F32, out)) return;
   int R = a[2], c0 = a[3], c1 = a[4];
   if (R < 0 || c0 < 0 || c1 < c0 || !kvm_mat_ok(c, x, R, c1) || !kvm_flat_ok(c, out, c1)) { c.fail(KVM_OPE_RANGE, c0, c1); return; }
   kvm_colreduce<0>(c, x, none, none, none, (float*)out.p, nullptr, R, c0, c1, a[5]);
 }
-__device__ void kvm_op_norm_bwd_params(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_norm_bwd_params(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, dy, mean, rstd, dg, db;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, dy) || !kvm_buf(c, a[2], KVM_M_F32, mean, true) || !kvm_buf(c, a[3], KVM_M_F32, rstd) ||
       !kvm_buf(c, a[4], KVM_M_F32, dg) || !kvm_buf(c, a[5], KVM_M_F32, db, true)) return;
@@ -307,7 +307,7 @@ __device__ void kvm_op_norm_bwd_params(const KvmCtx& c, const int32_t* a) {
 
 // ---- rotary embedding (pairs (i, i+hd/2); ang = f32(f32(pos) * f32(theta^(-2i/hd))), runtime/ref_gpt.py:250-262) ------------------
 __device__ __forceinline__ float kvm_rope_inv(float theta, int i, int hd) { return (float)pow((double)theta, -(double)(float)(2 * i) / hd); }
-__device__ void kvm_rope(const KvmCtx& c, const int32_t* a, float sign) {
+static __device__ void kvm_rope(const KvmCtx& c, const int32_t* a, float sign) {
   KvmBuf x, out, pos;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, out) || !kvm_buf(c, a[2], KVM_M_I32, pos, true)) return;
   int r0 = a[3], r1 = a[4], T = a[5], H = a[6], hd = a[7];
@@ -331,13 +331,13 @@ __device__ void kvm_rope(const KvmCtx& c, const int32_t* a, float sign) {
     kvm_st(out, w1 + half, x1 * s + x2 * co);
   }
 }
-__device__ void kvm_op_rope_fwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, 1.0f); }
-__device__ void kvm_op_rope_bwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, -1.0f); }
+static __device__ void kvm_op_rope_fwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, 1.0f); }
+static __device__ void kvm_op_rope_bwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, -1.0f); }
 
 // ---- cross entropy: the block walks rows; per row one pass for (max, sum) and one for the gradient -------------------------------------
 // MODE bit 0: forward (rowloss, lse); bit 1: backward (dlogits).
 template <int MODE>
-__device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V,
+static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V,
                        int ignore, float f) {
   float* red = (float*)c.smem;
   const bool vec = (V & 7) == 0 && (lg.ld & 7) == 0 && kvm_vec_ok(lg) && (!(MODE & 2) || ((dl.ld & 7) == 0 && kvm_vec_ok(dl)));
@@ -382,25 +382,25 @@ __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, cons
     }
   }
 }
-__device__ bool kvm_ce_args(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V) {
+static __device__ bool kvm_ce_args(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V) {
   if (r0 < 0 || r1 < r0 || V <= 0 || !kvm_mat_ok(c, lg, r1, V) || !kvm_flat_ok(c, tg, r1) || !kvm_flat_ok(c, rl, r1) || !kvm_flat_ok(c, ls, r1) ||
       !kvm_mat_ok(c, dl, r1, V)) { c.fail(KVM_OPE_RANGE, r0, r1); return false; }
   return true;
 }
-__device__ void kvm_op_softmax_ce_fwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_softmax_ce_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, rl, ls, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, rl) || !kvm_buf(c, a[3], KVM_M_F32, ls)) return;
   if (!kvm_ce_args(c, lg, tg, rl, ls, none, a[4], a[5], a[6])) return;
   kvm_ce<1>(c, lg, tg, rl, ls, none, a[4], a[5], a[6], a[7], 0.0f);
 }
-__device__ void kvm_op_softmax_ce_bwd(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_softmax_ce_bwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, ls, loss, dl, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, ls) || !kvm_buf(c, a[3], KVM_M_F32, loss) ||
       !kvm_buf(c, a[4], KVM_M_FLT, dl)) return;
   if (!kvm_ce_args(c, lg, tg, none, ls, dl, a[5], a[6], a[7]) || !kvm_flat_ok(c, loss, 2)) return;
   kvm_ce<2>(c, lg, tg, none, ls, dl, a[5], a[6], a[7], a[8], __fmul_rn(((const float*)loss.p)[1], kvm_bits_f32(a[9])));
 }
-__device__ void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, rl, ls, dl;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, rl) || !kvm_buf(c, a[3], KVM_M_F32, ls) ||
       !kvm_buf(c, a[4], KVM_M_FLT, dl)) return;
@@ -409,7 +409,7 @@ __device__ void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a) {
   kvm_ce<3>(c, lg, tg, rl, ls, dl, a[5], a[6], a[7], -1, __fmul_rn((float)(1.0 / (double)a[9]), kvm_bits_f32(a[10])));
 }
 // loss[0] = mean rowloss over non-ignored rows, loss[1] = 1/count (runtime/ref_gpt.py:430-437); double sums, fixed tree.
-__device__ void kvm_op_softmax_ce_reduce(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_softmax_ce_reduce(const KvmCtx& c, const int32_t* a) {
   KvmBuf rl, tg, loss;
   if (!kvm_buf(c, a[0], KVM_M_F32, rl) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, loss)) return;
   int N = a[3], ign = a[4];
@@ -429,7 +429,7 @@ __device__ void kvm_op_softmax_ce_reduce(const KvmCtx& c, const int32_t* a) {
 // ---- optimiser ---------------------------------------------------------------------------------------------------------------------
 // AdamW in the reference's strict float32 step order (runtime/ref_gpt.py:457-471): every operation below is one rounded
 // float32 operation with no fused multiply-add, so p, m, v come out bit-identical to the CPU model.
-__device__ void kvm_adamw(const KvmCtx& c, const int32_t* a, bool lr_buf) {
+static __device__ void kvm_adamw(const KvmCtx& c, const int32_t* a, bool lr_buf) {
   KvmBuf p, g, m, v, gs, st, lrb;
   if (!kvm_buf(c, a[0], KVM_M_F32, p) || !kvm_buf(c, a[1], KVM_M_FLT, g) || !kvm_buf(c, a[2], KVM_M_F32, m) || !kvm_buf(c, a[3], KVM_M_F32, v) ||
       !kvm_buf(c, a[4], KVM_M_F32, gs, true) || !kvm_buf(c, a[5], KVM_M_I32, st)) return;
@@ -469,10 +469,10 @@ __device__ void kvm_adamw(const KvmCtx& c, const int32_t* a, bool lr_buf) {
   }
   for (long long i = e0 + body + threadIdx.x; i < e1; i += KVM_NT) upd(pp[i], kvm_ld(g, i), mp[i], vp[i], pp[i], mp[i], vp[i]);
 }
-__device__ void kvm_op_adamw(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, false); }
-__device__ void kvm_op_adamw_lr(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, true); }
+static __device__ void kvm_op_adamw(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, false); }
+static __device__ void kvm_op_adamw_lr(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, true); }
 
-__device__ void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
   KvmBuf st, lr;
   if (!kvm_buf(c, a[0], KVM_M_I32, st) || !kvm_buf(c, a[1], KVM_M_F32, lr)) return;
   int kind = a[2], warmup = a[4], total = a[5];
@@ -487,7 +487,7 @@ __device__ void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-__device__ void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a) {
   KvmBuf g, part;
   if (!kvm_buf(c, a[0], KVM_M_FLT, g) || !kvm_buf(c, a[1], KVM_M_F32, part)) return;
   int slot = a[2];
@@ -507,7 +507,7 @@ __device__ void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a) {
   s = kvm_block_sum(s, (double*)c.smem);
   if (threadIdx.x == 0) ((float*)part.p)[slot] = (float)s;
 }
-__device__ void kvm_op_gradnorm_finish(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_gradnorm_finish(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, out;
   if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[2], KVM_M_F32, out)) return;
   int ns = a[1];
@@ -524,7 +524,7 @@ __device__ void kvm_op_gradnorm_finish(const KvmCtx& c, const int32_t* a) {
 }
 
 // ---- argmax (lowest index on ties, NaN never wins; runtime/ref_gpt.py:508-514) -------------------------------------------------------
-__device__ void kvm_argmax_rows(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& out, int r0, int r1, int V) {
+static __device__ void kvm_argmax_rows(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& out, int r0, int r1, int V) {
   float* rv = (float*)c.smem;
   int* ri = (int*)(rv + KVM_NWARPS);
   for (int r = r0; r < r1; ++r) {
@@ -547,7 +547,7 @@ __device__ void kvm_argmax_rows(const KvmCtx& c, const KvmBuf& lg, const KvmBuf&
     }
   }
 }
-__device__ void kvm_op_argmax(const KvmCtx& c, const int32_t* a) {
+static __device__ void kvm_op_argmax(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, out;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, out)) return;
   if (a[2] < 0 || a[3] < a[2] || a[4] <= 0 || !kvm_mat_ok(c, lg, a[3], a[4]) || !kvm_flat_ok(c, out, a[3])) { c.fail(KVM_OPE_RANGE, a[2], a[3]); return; }

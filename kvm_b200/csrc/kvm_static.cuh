@@ -1,0 +1,502 @@
+// The static-schedule path: the resident program runs as per-worker task lists planned on the host (kvm_static_host.inl), with
+// no ready queue, no dependency counters and no atomics on the task path.  What it implements of the reference: the static path
+// of include/mvm_static.h:1-17,43-51 (list schedule -> per-worker records, cross-worker watermark waits) and its worker loop
+// include/mvm_static.cuh:161-229 (fetch the next record ahead, poll the watermarks, dispatch, publish own progress).
+//
+// One CTA per SM as in the dynamic kernel: 16 compute warps + one FRONT warp.  The front warp walks the worker's list ahead of the
+// compute group: it fetches task records into a four-slot shared-memory ring, polls the task's dependencies (pairs of
+// (worker, tasks that worker must have finished), lanes in parallel over the pairs), and marks the slot ready.  A worker's
+// progress word is one release store per finished task; nothing else is written to global memory for scheduling.
+//
+// Because a worker knows its next tasks, the front warp also STREAMS AHEAD: for decode GEMVs and split decode attention it
+// issues the bulk copies of the task's weight rows / cache rows into a shared-memory stage ring as soon as stages are free,
+// BEFORE the task's dependencies are resolved (weights and old cache rows do not change during a launch; the host marks a task
+// whose streamed operand is written by some task of the batch, and its copies then wait for the dependencies like everything
+// else).  The dependency wait then only gates the prologue and the arithmetic, so HBM keeps streaming across phase boundaries.
+//
+// Every wait is bounded (time limit); on expiry KVM_ERR_TIMEOUT is recorded, every CTA leaves, copies in flight are awaited.
+#pragma once
+#include "kvm_dispatch.cuh"
+#include "kvm_static_api.h"
+
+#define KVM_ST_SLOTS 4                 // record ring depth (tasks fetched ahead)
+#define KVM_ST_HDR 2048                // header bytes: slots, control words, barriers
+#define KVM_ST_RING (KVM_ST_NSTAGE * KVM_ST_STAGE)
+#define KVM_ST_ARRIVALS 8              // consumer arrivals that free a stage
+
+struct KvmStSlot {
+  int task;
+  int state;                  // 0 free, 1 fetched, 2 ready, 3 leave
+  int go;
+  int kind;                   // 0 generic op, 1 streamed gemv, 2 streamed split attention
+  int nchunks;                // stage uses of this task
+  int R;                      // gemv: weight rows per stage
+  int wait_off, wait_cnt;
+  int32_t desc[16];
+  int32_t args[KVM_MAX_ARGS];
+  int4 aux;
+  int prefetch;               // 1: copies may be issued before the dependencies are met
+  int j0, j1, newrow;         // attention: key range of the split, index of the appended key inside it (-1 none)
+};
+static_assert(sizeof(KvmStSlot) * KVM_ST_SLOTS + 128 * 4 + 64 <= KVM_ST_HDR, "static header too small");
+
+__device__ __forceinline__ bool kvm_mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+struct KvmRing {
+  uint32_t bar0;              // full[s] at bar0 + 8 s, empty[s] at bar0 + 64 + 8 s
+  unsigned char* base;        // stage s at base + s * KVM_ST_STAGE
+  uint32_t base_addr;
+};
+__device__ __forceinline__ uint32_t kvm_ring_full(const KvmRing& r, unsigned it) { return r.bar0 + 8 * (it % KVM_ST_NSTAGE); }
+__device__ __forceinline__ uint32_t kvm_ring_empty(const KvmRing& r, unsigned it) { return r.bar0 + 64 + 8 * (it % KVM_ST_NSTAGE); }
+__device__ __forceinline__ uint32_t kvm_ring_parity(unsigned it) { return (it / KVM_ST_NSTAGE) & 1u; }
+
+// ---- streamed GEMV, consumer side --------------------------------------------------------------------------------------------
+// Stage use `cit + ci` holds rows n0 + ci*R .. of the weight matrix in full (R*K*2 bytes).  Warps 0..7 consume: warp = (row r of the
+// stage, part of K); the activation row v = bf16(prologue(x)) is staged once as bf16.  Partial sums are added in part order.
+// Semantics as kvm_op_gemv_bf16 (runtime/ref_extra.py:398-415).  Always consumes its nchunks stage uses, also after an error.
+static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline) {
+  KvmBuf x, x2, gm, w, out, res;
+  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
+  const float eps = kvm_bits_f32(a[10]);
+  bool ok = kvm_buf(c, a[0], KVM_M_FLT, x) && kvm_buf(c, a[1], KVM_M_FLT, x2, true) && kvm_buf(c, a[2], KVM_M_F32, gm, true) && kvm_buf(c, a[3], KVM_M_BF16, w) &&
+            kvm_buf(c, a[4], KVM_M_FLT, out) && kvm_buf(c, a[5], KVM_M_FLT, res, true);
+  const int rows = n1 - n0;
+  const int KP = KVM_ST_ARRIVALS / R;
+  const int fixed = ((K * 2 + 127) & ~127) + 256 + ((rows + 7) & ~7) * KP * 4;
+  if (ok && (pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || fixed > c.smem_bytes)) { c.fail(KVM_OPE_SHAPE, K, pro); ok = false; }
+  if (ok) ok = kvm_mat_ok(c, x, 1, K) && kvm_mat_ok(c, x2, 1, K) && kvm_flat_ok(c, gm, K) && kvm_mat_ok(c, out, 1, n1) && kvm_mat_ok(c, res, 1, n1);
+  __nv_bfloat16* vs = (__nv_bfloat16*)c.smem;
+  float* red = (float*)(c.smem + ((K * 2 + 127) & ~127));
+  float* parts = red + 64;                                 // [rows][KP]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  kvm_sync();                                              // the previous task is done with the scratch
+  if (ok) {
+    // ---- prologue: v = bf16(pro(x)) (all 16 warps)
+    if (pro == 1 && K <= 16 * KVM_NT) {
+      float xr[16], gr[16], q = 0.0f;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int k = tid + u * KVM_NT;
+        xr[u] = k < K ? kvm_ld(x, k) : 0.0f;
+        gr[u] = k < K ? ((const float*)gm.p)[k] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) q += xr[u] * xr[u];
+      q = kvm_block_sum(q, red);
+      const float rs = 1.0f / sqrtf(q / K + eps);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { const int k = tid + u * KVM_NT; if (k < K) vs[k] = __float2bfloat16_rn(xr[u] * rs * gr[u]); }
+    } else if (pro == 1) {
+      float q = 0.0f;
+      for (int k = tid; k < K; k += KVM_NT) { const float t = kvm_ld(x, k); q += t * t; }
+      q = kvm_block_sum(q, red);
+      const float rs = 1.0f / sqrtf(q / K + eps);
+      for (int k = tid; k < K; k += KVM_NT) vs[k] = __float2bfloat16_rn(kvm_ld(x, k) * rs * ((const float*)gm.p)[k]);
+    } else {
+      for (int k0 = 0; k0 < K; k0 += 8 * KVM_NT) {
+        float p[8], q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = k0 + tid + u * KVM_NT;
+          p[u] = k < K ? kvm_ld(x, k) : 0.0f;
+          q[u] = (pro == 2 && k < K) ? kvm_ld(x2, k) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = k0 + tid + u * KVM_NT;
+          if (k < K) vs[k] = __float2bfloat16_rn(pro == 2 ? kvm_silu(p[u]) * q[u] : p[u]);
+        }
+      }
+    }
+  }
+  kvm_sync();
+  bool waited = true;
+  if (warp < KVM_ST_ARRIVALS) {
+    const int r = warp / KP, part = warp % KP;
+    const int plen = (((K + KP - 1) / KP) + 255) & ~255, kb = part * plen, ke = min(K, kb + plen);
+    for (int ci = 0; ci < NC; ++ci) {
+      const unsigned it = cit + ci;
+      // bounded wait for the stage
+      {
+        const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
+        unsigned spins = 0;
+        while (!kvm_mbar_test(bar, par)) {
+          if ((++spins & 1023u) == 0 && (kvm_globaltimer() > deadline || *(volatile int*)&c.err->code != 0)) { waited = false; break; }      // an error elsewhere: the copies may never come
+        }
+      }
+      if (!waited) break;
+      if (ok && r < R && ci * R + r < rows) {
+        const unsigned char* st = ring.base + (it % KVM_ST_NSTAGE) * KVM_ST_STAGE + (size_t)r * K * 2;
+        float acc0 = 0.0f, acc1 = 0.0f;
+        for (int k = kb + lane * 8; k < ke; k += 256) {
+          const uint4 wv = *(const uint4*)(st + k * 2);
+          const uint4 xv = *(const uint4*)(vs + k);
+          acc0 = fmaf(kvm_bf16lo(xv.x), kvm_bf16lo(wv.x), acc0); acc1 = fmaf(kvm_bf16hi(xv.x), kvm_bf16hi(wv.x), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.y), kvm_bf16lo(wv.y), acc0); acc1 = fmaf(kvm_bf16hi(xv.y), kvm_bf16hi(wv.y), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.z), kvm_bf16lo(wv.z), acc0); acc1 = fmaf(kvm_bf16hi(xv.z), kvm_bf16hi(wv.z), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.w), kvm_bf16lo(wv.w), acc0); acc1 = fmaf(kvm_bf16hi(xv.w), kvm_bf16hi(wv.w), acc1);
+        }
+        const float sum = kvm_warp_sum(acc0 + acc1);
+        if (lane == 0) parts[(ci * R + r) * KP + part] = sum;
+      }
+      __syncwarp();
+      if (lane == 0) kvm_mbar_arrive(kvm_ring_empty(ring, it));
+    }
+  }
+  __syncwarp();
+  if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1134);
+  kvm_sync();
+  if (ok && waited)
+    for (int i = tid; i < rows; i += KVM_NT) {
+      float sum = 0.0f;
+      for (int p = 0; p < KP; ++p) sum += parts[i * KP + p];
+      kvm_st(out, n0 + i, res.p ? __fadd_rn(sum, kvm_ld(res, n0 + i)) : sum);
+    }
+}
+
+// ---- streamed split attention, consumer side ----------------------------------------------------------------------------------
+// Stage use `cit` holds the split's keys, `cit + 1` its values (the appended row left out).  Semantics as kvm_op_attn_decode_part
+// (runtime/ref_extra.py:421-498); the front warp has validated the geometry before it issued the copies.
+static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow, unsigned long long deadline) {
+  KvmBuf q, kc, vc, lens, part, kn, vn;
+  bool ok = kvm_buf(c, a[0], KVM_M_FLT, q) && kvm_buf(c, a[1], KVM_M_FLT, kc) && kvm_buf(c, a[2], KVM_M_FLT, vc) && kvm_buf(c, a[3], KVM_M_I32, lens) &&
+            kvm_buf(c, a[4], KVM_M_F32, part) && kvm_buf(c, a[5], KVM_M_FLT, kn, true) && kvm_buf(c, a[6], KVM_M_FLT, vn, true);
+  const int b = a[7], kvh = a[8], s = a[9], S = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
+  const float sc = kvm_bits_f32(a[15]), theta = kvm_bits_f32(a[16]);
+  const int G = H / Hkv, half = hd / 2;
+  if (ok) ok = kvm_mat_ok(c, q, b + 1, H * hd) && kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) && kvm_mat_ok(c, kn, b + 1, Hkv * hd) && kvm_mat_ok(c, vn, b + 1, Hkv * hd);
+  if (ok && ((fl & 1) && (!kn.p || !vn.p))) { c.fail(KVM_OPE_SHAPE, hd, fl); ok = false; }
+  const int p0 = ok ? ((const int*)lens.p)[b] : 0, n = p0 + 1, nk = max(j1 - j0, 0);
+  const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
+  unsigned char* sm = c.smem;
+  float* qs = (float*)(sm + KVM_AS_OFF_QS);
+  float* inv = (float*)(sm + KVM_AS_OFF_INV);
+  float* kns = (float*)(sm + KVM_AS_OFF_KNEW);
+  float* vns = (float*)(sm + KVM_AS_OFF_VNEW);
+  const bool appends = newrow >= 0;
+  unsigned char* Ks = ring.base + (cit % KVM_ST_NSTAGE) * KVM_ST_STAGE;
+  unsigned char* Vs = ring.base + ((cit + 1) % KVM_ST_NSTAGE) * KVM_ST_STAGE;
+  auto wait_use = [&](unsigned it) {
+    const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
+    unsigned spins = 0;
+    while (!kvm_mbar_test(bar, par)) if ((++spins & 1023u) == 0 && (kvm_globaltimer() > deadline || *(volatile int*)&c.err->code != 0)) return false;
+    return true;
+  };
+  kvm_sync();                                              // the previous task is done with the scratch
+  bool waited = true;
+  if (ok) {
+    auto prologue = [&]() {
+      if (fl & 1) {
+        for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
+        kvm_sync();
+      }
+      if (appends) {
+        for (int i = threadIdx.x; i < half; i += KVM_NT) {
+          float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+          const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
+          const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+          kns[i] = y1; kns[i + half] = y2;
+          kvm_st(kc, (base + n - 1) * kc.ld + i, y1);
+          kvm_st(kc, (base + n - 1) * kc.ld + i + half, y2);
+        }
+        for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) {
+          const float t = kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc);
+          vns[cc] = t;
+          kvm_st(vc, (base + n - 1) * vc.ld + cc, t);
+        }
+      }
+      for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
+        const int g = e / half, i = e % half, h = kvh * G + g;
+        float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
+        if (fl & 1) {
+          float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
+          const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+          x1 = y1; x2 = y2;
+          if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
+        }
+        qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
+      }
+    };
+    float* pp = (float*)part.p;
+    auto emit = [&](int g, int cc, float M, float Lsum, float A) {
+      const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
+      pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
+      if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M_STREAM; pp[row + hd + 1] = Lsum; }
+    };
+    auto wk = [&]() { return wait_use(cit); };
+    auto wv = [&]() { return wait_use(cit + 1); };
+    if (G <= 1) waited = kvm_attn_part_core<1>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
+    else if (G <= 2) waited = kvm_attn_part_core<2>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
+    else if (G <= 4) waited = kvm_attn_part_core<4>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
+    else waited = kvm_attn_part_core<8>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
+  } else {
+    waited = wait_use(cit) && wait_use(cit + 1);
+  }
+  if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1135);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the appended row was written by threads; the next copies into these stages come after it
+  kvm_sync();
+  if (waited && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) < KVM_ST_ARRIVALS) { kvm_mbar_arrive(kvm_ring_empty(ring, cit)); kvm_mbar_arrive(kvm_ring_empty(ring, cit + 1)); }
+}
+
+// ---- front warp: stream geometry of a fetched task (lane 0) ---------------------------------------------------------------------
+// Decides whether the task streams through the ring and with which chunking; every bound the copies rely on is checked here,
+// a task that fails one runs as a generic op (whose own checks then report the error).
+static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, int scratch_bytes) {
+  sl.kind = 0; sl.nchunks = 0; sl.R = 1; sl.j0 = sl.j1 = 0; sl.newrow = -1;
+  const int op = sl.desc[0];
+  const int32_t* a = sl.args;
+  if (op == 134) {
+    const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8];
+    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || K <= 0 || (K & 255) || K * 2 > KVM_ST_STAGE) return;
+    const KvmBuf w = S.bufs[wi];
+    if (!w.p || w.dtype != KVM_BF16 || (w.ld & 7) || ((uintptr_t)w.p & 15) || n1 > w.rows || K > w.cols) return;
+    int R = KVM_ST_STAGE / (K * 2);
+    if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
+    if (((K * 2 + 127) & ~127) + 256 + ((n1 - n0 + 7) & ~7) * (KVM_ST_ARRIVALS / R) * 4 > scratch_bytes) return;
+    sl.kind = 1; sl.R = R; sl.nchunks = (n1 - n0 + R - 1) / R;
+  } else if (op == 135) {
+    const int kci = a[1], vci = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], Sp = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
+    if (kci < 0 || kci >= S.nbufs || vci < 0 || vci >= S.nbufs || li < 0 || li >= S.nbufs) return;
+    if (b < 0 || Hkv <= 0 || H <= 0 || H % Hkv || kvh < 0 || kvh >= Hkv || s < 0 || Sp <= 0 || s >= Sp || Tmax <= 0 || !(fl == 0 || fl == 1 || fl == 3)) return;
+    const int G = H / Hkv;
+    if (G > 8 || (G & (G - 1)) || !(hd == 16 || hd == 32 || hd == 64 || hd == 128)) return;
+    const KvmBuf kc = S.bufs[kci], vc = S.bufs[vci], lens = S.bufs[li];
+    if (!kc.p || !vc.p || !lens.p || kc.dtype != KVM_BF16 || vc.dtype != KVM_BF16 || lens.dtype != KVM_I32 || kc.ld != hd || vc.ld != hd || ((uintptr_t)kc.p & 15) || ((uintptr_t)vc.p & 15)) return;
+    if ((long long)(b + 1) * Hkv * Tmax > kc.rows || (long long)(b + 1) * Hkv * Tmax > vc.rows || hd > kc.cols || hd > vc.cols || lens.ld != lens.cols || b >= lens.rows * lens.cols) return;
+    const int p0 = ((const int*)lens.p)[b], n = p0 + 1;
+    if (p0 < 0 || n > Tmax) return;
+    const int chunk = (n + Sp - 1) / Sp, j0 = s * chunk, j1 = min(n, s * chunk + chunk), nk = max(j1 - j0, 0);
+    if (nk * hd * 2 > KVM_ST_STAGE || kvm_attn_part_scratch(nk, G, hd) > scratch_bytes) return;
+    sl.kind = 2; sl.nchunks = 2; sl.j0 = j0; sl.j1 = j1;
+    sl.newrow = ((fl & 1) && j0 <= n - 1 && n - 1 < j1) ? n - 1 - j0 : -1;
+  }
+}
+
+// Issue the copies of chunk `ci` of the task in `sl` as stage use `it` (front warp, lane 0; the stage is known to be free).
+static __device__ void kvm_static_issue(const KvmDevState& S, const KvmStSlot& sl, const KvmRing& ring, unsigned it, int ci) {
+  const uint32_t full = kvm_ring_full(ring, it), dst = ring.base_addr + (it % KVM_ST_NSTAGE) * KVM_ST_STAGE;
+  const int32_t* a = sl.args;
+  if (sl.kind == 1) {
+    const KvmBuf w = S.bufs[a[3]];
+    const int n0 = a[6], n1 = a[7], K = a[8], R = sl.R;
+    const int r0 = n0 + ci * R, nr = min(R, n1 - r0);
+    const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p;
+    kvm_mbar_expect_tx(full, (uint32_t)(nr * K * 2));
+    if (w.ld == K) kvm_bulk_g2s(dst, wp + (size_t)r0 * w.ld, (uint32_t)(nr * K * 2), full);
+    else for (int r = 0; r < nr; ++r) kvm_bulk_g2s(dst + r * K * 2, wp + (size_t)(r0 + r) * w.ld, (uint32_t)(K * 2), full);
+  } else {
+    const KvmBuf cb = S.bufs[a[ci == 0 ? 1 : 2]];
+    const int b = a[7], kvh = a[8], Hkv = a[12], hd = a[13], Tmax = a[14];
+    const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
+    const int nk = max(sl.j1 - sl.j0, 0), ncopy = sl.newrow >= 0 ? nk - 1 : nk;
+    const uint32_t bytes = (uint32_t)(ncopy * hd * 2);
+    kvm_mbar_expect_tx(full, bytes);
+    if (bytes) kvm_bulk_g2s(dst, (const __nv_bfloat16*)cb.p + (base + sl.j0) * cb.ld, bytes, full);
+  }
+}
+
+__global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticState T) {
+  extern __shared__ __align__(1024) unsigned char kvm_smem[];
+  const KvmDevState& S = T.D;
+  KvmStSlot* slots = (KvmStSlot*)kvm_smem;
+  int* ctl = (int*)(kvm_smem + KVM_ST_SLOTS * sizeof(KvmStSlot));          // as in the dynamic kernel: ctl[0] = TMEM base, tensor-core barriers from ctl[8]
+  int* sctl = ctl + 96;                                                     // static path's own words: [0] consumer stage-use count, [1] tasks finished
+  const uint32_t sbar = kvm_smem_addr(kvm_smem + KVM_ST_HDR - 128);         // stream ring barriers: full[3] | empty[3]
+  const int tid = threadIdx.x;
+  const bool is_front = tid >= KVM_NT;
+  const int w = blockIdx.x;
+  unsigned dyn;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+  if (tid < KVM_ST_SLOTS) { slots[tid].state = 0; slots[tid].task = -1; }
+  if (tid == 0) { sctl[0] = 0; sctl[1] = 0; }
+  kvm_tc_init(ctl, kvm_smem);
+  const bool use_ring = T.ring && dyn >= KVM_ST_HDR + KVM_ST_RING + 32768;
+  if (tid == 64 && use_ring) {
+    for (int s = 0; s < KVM_ST_NSTAGE; ++s) { kvm_mbar_init(sbar + 8 * s, 1); kvm_mbar_init(sbar + 64 + 8 * s, KVM_ST_ARRIVALS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  const int cache_bytes = (int)(((size_t)S.nbufs * sizeof(KvmBuf) + 1023) & ~(size_t)1023);
+  const bool buf_cache = !use_ring && S.buf_cache && cache_bytes <= KVM_BUFCACHE_BYTES && dyn >= KVM_ST_HDR + KVM_BUFCACHE_BYTES + 192 * 1024;
+  if (buf_cache) {
+    const uint4* src = (const uint4*)S.bufs;
+    uint4* dst = (uint4*)(kvm_smem + KVM_ST_HDR);
+    for (int i = tid; i < S.nbufs * 2; i += KVM_NT + 32) dst[i] = src[i];
+  }
+  __syncthreads();
+  const unsigned long long t_begin = kvm_globaltimer();
+  const unsigned long long deadline = t_begin + S.timeout_ns;
+  KvmRing ring;
+  ring.bar0 = sbar;
+  ring.base = kvm_smem + (use_ring ? dyn - KVM_ST_RING : 0);
+  ring.base_addr = kvm_smem_addr(ring.base);
+  const int p_lo = T.prog_off[w], n = T.prog_off[w + 1] - p_lo;
+
+  if (is_front) {
+    const int lane = tid & 31;
+    int fi = 0, ri = 0, ii = 0, ic = 0;        // next position to fetch / to mark ready / to stream; chunk inside the streamed task
+    unsigned pit = 0;                          // stage uses issued
+    bool stop = false;
+    unsigned idle = 0;
+    while (!stop && (ri < n || ii < n)) {
+      bool progressed = false;
+      // 1. fetch the next record into a free slot
+      if (fi < n && kvm_ld_volatile_shared(&slots[fi % KVM_ST_SLOTS].state) == 0) {
+        KvmStSlot& sl = slots[fi % KVM_ST_SLOTS];
+        const int task = T.prog[p_lo + fi];
+        const int32_t* rec = S.recs + (size_t)task * KVM_REC_WORDS;
+        const int32_t w0 = rec[lane], w1 = lane < 16 ? rec[32 + lane] : 0;
+        if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
+        if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
+        if (lane == 8) sl.wait_off = w1;
+        if (lane == 9) sl.wait_cnt = w1;
+        if (lane == 10) sl.prefetch = w1 & 1;
+        if (lane == 31) sl.task = task;
+        __syncwarp();
+        if (lane == 0) {
+          if (use_ring) kvm_static_geometry(S, sl, (int)dyn - KVM_ST_HDR - KVM_ST_RING); else { sl.kind = 0; sl.nchunks = 0; }
+          sl.state = 1;
+        }
+        __syncwarp();
+        ++fi; progressed = true;
+      }
+      // 2. stream ahead: the next chunk of the oldest task that still has copies to issue
+      if (ii < fi) {
+        KvmStSlot& sl = slots[ii % KVM_ST_SLOTS];
+        const int kind = kvm_ld_volatile_shared(&sl.kind);
+        if (kind == 0) { ++ii; ic = 0; progressed = true; }
+        else if (sl.prefetch || ii < ri) {                 // constants may run ahead; anything else waits until the task is ready
+          int issued = 0;
+          if (lane == 0) {
+            const bool free_stage = pit < KVM_ST_NSTAGE || kvm_mbar_test(kvm_ring_empty(ring, pit), kvm_ring_parity(pit) ^ 1u);
+            if (free_stage) {
+              if (!sl.prefetch) asm volatile("fence.proxy.async;" ::: "memory");      // data other workers wrote with plain stores, read here by bulk copies
+              kvm_static_issue(S, sl, ring, pit, ic);
+              issued = 1;
+            }
+          }
+          issued = __shfl_sync(0xffffffffu, issued, 0);
+          if (issued) { ++pit; ++ic; progressed = true; if (ic >= sl.nchunks) { ++ii; ic = 0; } }
+        }
+      }
+      // 3. dependencies of the next task to become ready
+      if (ri < fi) {
+        KvmStSlot& sl = slots[ri % KVM_ST_SLOTS];
+        const int off = sl.wait_off, cnt = sl.wait_cnt;
+        bool met = true;
+        for (int k = lane; k < cnt; k += 32) {
+          const int e = T.waits[off + k];
+          if (kvm_ld_acquire(&T.progress[e >> KVM_ST_WAIT_BITS]) < (e & ((1 << KVM_ST_WAIT_BITS) - 1))) met = false;
+        }
+        if (__all_sync(0xffffffffu, met)) {
+          __threadfence();                                   // what the finished predecessors wrote is visible to this CTA's compute group
+          if (lane == 0) { S.indeg[sl.task] = 0; sl.state = 2; }     // every predecessor's completion was observed
+          __syncwarp();
+          ++ri; progressed = true;
+        }
+      }
+      // 4. failure / stall
+      if (!progressed) {
+        if ((++idle & 63u) == 0) {
+          int e = 0;
+          if (lane == 0) e = *(volatile int*)&S.err->code;
+          e = __shfl_sync(0xffffffffu, e, 0);
+          if (e != 0) stop = true;
+          else if (kvm_globaltimer() > deadline) {
+            if (lane == 0) kvm_dev_fail(S, KVM_ERR_TIMEOUT, ri < n ? T.prog[p_lo + ri] : -1, ri, fi);
+            stop = true;
+          }
+        }
+      } else idle = 0;
+    }
+    // leave: the compute group takes slots in order; the first one that is not ready tells it to go
+    if (stop) {
+      if (lane == 0) {
+        for (int k = 0; k < KVM_ST_SLOTS; ++k) {
+          KvmStSlot& sl = slots[(ri + k) % KVM_ST_SLOTS];
+          if (kvm_ld_volatile_shared(&sl.state) != 2) { sl.state = 3; break; }
+        }
+      }
+    }
+    sctl[2] = (int)pit;
+  } else {
+    KvmCtx c;
+    c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps; c.pair = -1;
+    c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_ST_HDR) : S.bufs;
+    const int used = KVM_ST_HDR + (buf_cache ? cache_bytes : 0);
+    c.smem = kvm_smem + used;
+    c.smem_bytes = (int)dyn - used - (use_ring ? KVM_ST_RING : 0);
+    unsigned cit = 0;
+    int finished = 0;
+    for (int i = 0; i < n; ++i) {
+      KvmStSlot& sl = slots[i % KVM_ST_SLOTS];
+      if (tid == 0) {
+        unsigned polls = 0;
+        int st;
+        while ((st = kvm_ld_volatile_shared(&sl.state)) < 2) {
+          if ((++polls & 1023u) == 0 && kvm_globaltimer() > deadline + S.timeout_ns) { st = 3; break; }      // the front warp always answers first
+        }
+        sl.go = st == 3 ? 0 : (*(volatile int*)&S.err->code == 0 ? 1 : 2);
+      }
+      kvm_sync();
+      const int go = kvm_ld_volatile_shared(&sl.go);
+      if (go == 0) break;
+      const int task = sl.task;
+      c.task = task;
+      if (tid == 0 && S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
+      const int op = sl.desc[0], kind = sl.kind, nch = sl.nchunks;
+      if (kind == 1) kvm_gemv_ring(c, sl.args, ring, cit, sl.R, nch, deadline);
+      else if (kind == 2) kvm_attn_part_ring(c, sl.args, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
+      else if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
+      cit += (unsigned)nch;
+      asm volatile("fence.proxy.async;" ::: "memory");
+      kvm_sync();
+      if (tid == 0) {
+        if (S.trace) S.t_end[task] = kvm_globaltimer();
+        S.exec_count[task] += 1;
+        __threadfence();
+        const int pv = sl.desc[10];
+        if (pv >= 0) {                                       // publish (include/mvm_task_abi.h:20-23): old + 1, else VERSION_GAP
+          if (pv >= S.nvars) kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, pv);
+          else {
+            const int ver = sl.desc[11] + S.ver_off[pv];
+            if (atomicCAS(&S.versions[pv], ver - 1, ver) != ver - 1) kvm_dev_fail(S, KVM_ERR_VERSION_GAP, task, pv, ver);
+            __threadfence();
+          }
+        }
+        kvm_st_release(&T.progress[w], i + 1);
+        sctl[0] = (int)cit;
+        sl.state = 0;
+      }
+      ++finished;
+    }
+    if (tid == 0) { sctl[1] = finished; atomicAdd(S.done, finished); }
+  }
+  __syncthreads();
+  // copies issued but never consumed (an early exit): wait for them, bounded, before the shared memory goes away
+  if (use_ring && tid == KVM_NT) {
+    const unsigned pit = (unsigned)sctl[2], cit = (unsigned)sctl[0];
+    for (unsigned it = cit; it < pit; ++it) {
+      const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
+      const unsigned long long t0 = kvm_globaltimer();
+      unsigned spins = 0;
+      while (!kvm_mbar_test(bar, par)) if ((++spins & 63u) == 0 && kvm_globaltimer() - t0 > 50000000ull) break;      // 50 ms: a bulk copy lands in microseconds
+    }
+  }
+  __syncthreads();
+  kvm_tc_fini(ctl);
+}
+
+// Arm kernel of the static path: progress words and witnesses cleared, version offsets taken.
+__global__ void kvm_static_arm_kernel(KvmStaticState T, int workers) {
+  const KvmDevState& S = T.D;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < S.nt) { S.indeg[i] = S.tasks[i].indegree; S.exec_count[i] = 0; }
+  if (i < workers) T.progress[i] = 0;
+  if (i < S.nvars) S.ver_off[i] = S.versions[i] - S.ver_base[i];
+}

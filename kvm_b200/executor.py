@@ -22,6 +22,8 @@ INIT_FILL, INIT_VALUES, INIT_SEEDED, INIT_NONE = 0, 1, 2, 3
 CFG_NO_TENSOR_CORES = 1
 CFG_PAIR_TILES = 2
 CFG_CHAIN = 4
+CFG_STATIC = 8
+CFG_DYNAMIC = 16
 
 
 class KvmError(RuntimeError):
@@ -76,6 +78,7 @@ SYMBOLS = {
     'kvm_task_counts': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_trace': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_launch_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    'kvm_plan_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     'kvm_tc_task_count': (C.c_int, [C.c_void_p]),
     'kvm_last_error': (C.c_char_p, [C.c_void_p]),
     'kvm_read_f32_noalloc': (C.c_int, [C.c_int32, C.c_void_p, C.c_int32, C.c_size_t, C.POINTER(C.c_float), C.c_void_p]),
@@ -320,6 +323,12 @@ class Executor:
         s, e, sm = np.empty(n, np.uint64), np.empty(n, np.uint64), np.empty(n, np.int32)
         self._check(self.L.kvm_trace(self._h, s.ctypes.data, e.ctypes.data, sm.ctypes.data, n))
         return s, e, sm
+
+    def plan_info(self):
+        """(runs on the static path?, with the stream ring?, planner's estimate of one run in us) of the prepared program."""
+        a, b, us = C.c_int32(), C.c_int32(), C.c_float()
+        self._check(self.L.kvm_plan_info(self._h, C.byref(a), C.byref(b), C.byref(us)))
+        return bool(a.value), bool(b.value), us.value
 
     def tc_task_count(self) -> int:
         return self.L.kvm_tc_task_count(self._h)

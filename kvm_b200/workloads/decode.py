@@ -45,11 +45,12 @@ class DecodeConfig:
 
 PRESETS = {
     'decode_tiny': DecodeConfig(),
-    # BASELINE config 5 (Qwen3-8B shape), 4K context
+    # BASELINE config 5 (Qwen3-8B shape), 4K context.  17 context splits: a split's keys (at most 256 of 128 bf16 values) fit one 64 KB
+    # stage of the stream ring, and 8 kv heads x 17 splits = 136 tasks are one wave over the SMs
     'qwen3_8b': DecodeConfig(name='qwen3_8b', layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                             splits=16, rows_per_task=0, join_threshold=1000),
+                             splits=17, rows_per_task=0, join_threshold=1000),
     'qwen3_8b_4l': DecodeConfig(name='qwen3_8b_4l', layers=4, hidden=4096, heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936, ctx=4096, tmax=4096 + 256,
-                                splits=16, rows_per_task=0, join_threshold=1000),
+                                splits=17, rows_per_task=0, join_threshold=1000),
 }
 
 

@@ -57,7 +57,7 @@ def test_qwen3_8b_shapes_32_greedy_tokens(kvm_lib):
     from kvm_b200.executor import Executor
     from kvm_b200.workloads.decode import build_decode, preset
     from oracle.vm_np import VM
-    cfg = preset('qwen3_8b_4l', vocab=32768)
+    cfg = preset('qwen3_8b_4l', vocab=32768, seed=SEED)
     b = build_decode(cfg).to_bundle(check=False)
     got, ref = [], []
     with Executor() as ex:

@@ -1,0 +1,165 @@
+"""The static-schedule path (per-worker task lists planned on the host, cross-worker progress waits, decode operands streamed
+ahead of the dependencies) through the C ABI: the same programs the ready-queue path runs must give the same results.
+
+What this mirrors in the reference: tests/static/test_static_plan.cpp (every task placed once, dependencies ordered) and the
+static legs of tests/gpu/test_exec.cu; the decode cases additionally compare the streamed GEMV / split attention against the CPU
+oracle and against the ready-queue path of the same library.
+"""
+import numpy as np
+import pytest
+
+from kvm_b200 import abi
+from tests.parity import compare, rel_err
+from tests.test_gpu_executor import raw_bundle, scale_task
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize('workers', [1, 7, 148])
+def test_random_dag_on_the_static_path(kvm_lib, workers):
+    from kvm_b200.executor import CFG_STATIC, Executor
+    rng = np.random.default_rng(77)
+    n = 1500
+    with Executor(trace=True, workers=workers, flags=CFG_STATIC) as ex:
+        cells = ex.add_buffer(1, n, 1, None)
+        x = ex.add_buffer(1, n, 0, 1.0)
+        tasks = []
+        for i in range(n):
+            width = int(rng.choice([0, 1, 2, 3, 8, 40]))
+            lo = max(0, i - int(rng.choice([4, 60, 600])))
+            after = sorted(set(int(p) for p in rng.integers(lo, i, size=min(width, i - lo)))) if i > lo else []
+            kind = int(rng.integers(0, 3))
+            prio = int(rng.integers(0, 32))
+            if kind == 0:
+                tasks.append({'op': 'noop', 'args': [], 'after': after, 'priority': prio})
+            elif kind == 1:
+                tasks.append({'op': 'counter_inc', 'args': [cells, i, i + 1, 1], 'after': after, 'priority': prio})
+            else:
+                tasks.append(scale_task(x, x, 2.0, i, i + 1, after=after, priority=prio))
+        t, s, a = raw_bundle(tasks)
+        ex.submit(t, s, a)
+        for run in range(2):
+            res = ex.run()
+            assert res.done == n
+            assert ex.plan_info()[0], 'KVM_CFG_STATIC must take the static path'
+            execs, observed = ex.task_counts(n)
+            assert (execs == 1).all() and np.array_equal(observed, t['indegree'])
+            st, en, _ = ex.trace(n)
+            assert (en >= st).all() and (st > 0).all()
+            for i, tk in enumerate(tasks):
+                for p in tk['after']:
+                    assert st[i] >= en[p], f'task {i} started before its predecessor {p} ended'
+        kinds = np.array([{'noop': 0, 'counter_inc': 1, 'scale_flat': 2}[tk['op']] for tk in tasks])
+        assert np.array_equal(ex.read_buffer(cells)[0], np.where(kinds == 1, 2, 0))
+        assert np.array_equal(ex.read_buffer(x)[0], np.where(kinds == 2, 4.0, 1.0).astype(np.float32))
+
+
+def test_version_waits_become_edges_and_unmet_waits_are_refused(kvm_lib):
+    from kvm_b200.executor import CFG_STATIC, Executor, KvmError
+    with Executor(flags=CFG_STATIC, trace=True) as ex:
+        x = ex.add_buffer(1, 512, 0, None)
+        y = ex.add_buffer(1, 512, 0, None)
+        tasks = [{'op': 'spin', 'args': [100]}, {'op': 'fill', 'args': [x, abi.f32_word(3.0), 512], 'after': [0], 'pub': (2, 1)}]
+        tasks += [scale_task(x, y, 2.0, i, i + 1, wait=(2, 1)) for i in range(200)]
+        t, s, a = raw_bundle(tasks)
+        ex.submit(t, s, a)
+        res = ex.run()
+        assert res.done == len(tasks) and ex.get_version(2) == 1 and ex.plan_info()[0]
+        assert (ex.read_buffer(y)[0, :200] == 6.0).all()
+        st, en, _ = ex.trace(len(tasks))
+        assert st[2:].min() >= en[1]
+        assert ex.run().done == len(tasks) and ex.get_version(2) == 2          # the next window of the template
+    with Executor(flags=CFG_STATIC) as ex:
+        x = ex.add_buffer(1, 64, 0, 1.0)
+        ex.submit(*raw_bundle([scale_task(x, x, 2.0, 0, 64, wait=(1, 1))]))      # nobody publishes variable 1: only the ready queue can park it
+        with pytest.raises(KvmError, match='static path'):
+            ex.run()
+
+
+def test_device_error_on_the_static_path_ends_the_launch(kvm_lib):
+    from kvm_b200.executor import CFG_STATIC, Executor
+    with Executor(flags=CFG_STATIC) as ex:
+        x = ex.add_buffer(1, 64, 0, 1.0)
+        y = ex.add_buffer(1, 64, 0, 7.0)
+        tasks = [scale_task(x, y, 2.0, 0, 32), scale_task(x, y, 2.0, 32, 4096, after=[0])] + [scale_task(x, x, 1.0, 0, 64, after=[1]) for _ in range(300)]
+        ex.submit(*raw_bundle(tasks))
+        res = ex.run(check=False)
+        assert res.status == 1003 and res.err_task == 1
+        assert (ex.read_buffer(y)[0, 32:] == 7.0).all()
+
+
+@pytest.mark.parametrize('precision', ['f32', 'bf16'])
+def test_training_step_on_the_static_path(kvm_lib, precision):
+    from kvm_b200.executor import CFG_STATIC
+    from kvm_b200.workloads.gpt import build_training, preset
+    from tests.parity import run_both
+    b = build_training(preset('gpt_tiny', precision=precision, layers=1, seq=32), 1).to_bundle()
+    ex, vm, res = run_both(b, flags=CFG_STATIC)
+    assert res.done == len(b.tasks) and ex.plan_info()[0] and not ex.plan_info()[1]
+    execs, observed = ex.task_counts()
+    assert (execs == 1).all() and np.array_equal(observed, b.tasks['indegree'])
+    compare(ex, vm, 2e-5 if precision == 'f32' else 1e-2)
+    assert ex.get_version(0) == 2
+    ex.close()
+
+
+@pytest.mark.parametrize('batch', [1, 2])
+def test_decode_streams_ahead_and_matches_both_the_oracle_and_the_ready_queue(kvm_lib, batch):
+    """Decode programs take the static path by default, with the shared-memory stream ring; 32 greedy tokens equal the oracle's
+    and the ready-queue path's, every hidden state of the last token agrees with the ready-queue path's."""
+    from kvm_b200.executor import CFG_DYNAMIC, Executor
+    from kvm_b200.workloads.decode import build_decode, preset
+    from oracle.vm_np import VM
+    cfg = preset('decode_tiny', batch=batch, init_std=0.08)
+    b = build_decode(cfg).to_bundle()
+    vm, ref = VM(b), []
+    for s in range(32):
+        vm.run()
+        ref.append([int(vm.buffer(f'u{u}.tok').a[0, 0]) for u in range(batch)])
+        vm = VM(b, buffers=vm.bufs)
+    runs = {}
+    for name, flags in (('static', 0), ('queue', CFG_DYNAMIC)):
+        with Executor(flags=flags) as ex:
+            ex.load(b)
+            toks = []
+            for s in range(32):
+                res = ex.run()
+                assert res.done == len(b.tasks)
+                toks.append([int(ex.read_buffer(f'u{u}.tok')[0, 0]) for u in range(batch)])
+            is_static, ring, _ = ex.plan_info()
+            assert is_static == (name == 'static') and ring == (name == 'static')
+            execs, observed = ex.task_counts()
+            assert (execs == 1).all() and np.array_equal(observed, b.tasks['indegree'])
+            assert int(ex.read_buffer('u0.lens')[0, 0]) == cfg.ctx + 32
+            runs[name] = (toks, {n: ex.read_buffer(n) for n in ('u0.logits', f'u0.l{cfg.layers - 1}.x2', 'u0.l0.kc')})
+    assert runs['static'][0] == ref and runs['queue'][0] == ref
+    for n, a in runs['static'][1].items():
+        assert rel_err(a, runs['queue'][1][n]) <= 2e-5, n
+
+
+@pytest.mark.parametrize('case', [dict(K=4096, N=300, pro=1), dict(K=12288, N=70, pro=2), dict(K=1024, N=37, pro=0), dict(K=2048, N=64, pro=1, ld=2304)])
+def test_streamed_gemv_shapes(kvm_lib, case):
+    """The ring form of gemv_bf16 at the 8B-shape row lengths (8 rows of 8 KB per stage, 2 rows of 24 KB), a ragged row count, a
+    strided weight matrix (one copy per row), with every prologue, against the oracle."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.graph import Graph
+    from oracle.vm_np import VM
+    K, N, pro, ld = case['K'], case['N'], case['pro'], case.get('ld')
+    rng = np.random.default_rng(3)
+    g = Graph('gemv')
+    g.data('x', rng.standard_normal((1, K)).astype(np.float32))
+    g.data('x2', rng.standard_normal((1, K)).astype(np.float32))
+    g.data('gamma', 1.0 + 0.1 * rng.standard_normal((1, K)).astype(np.float32))
+    g.data('w', (rng.standard_normal((N, ld or K)) * 0.05).astype(np.float32), 'bf16')
+    g.data('res', rng.standard_normal((1, N)).astype(np.float32))
+    g.buffer('out', 1, N)
+    for n0 in range(0, N, 23):
+        g.task('gemv_bf16', {'x': 'x', 'x2': 'x2' if pro == 2 else None, 'gamma': 'gamma' if pro == 1 else None, 'w': 'w', 'out': 'out', 'res': 'res',
+                             'n0': n0, 'n1': min(n0 + 23, N), 'K': K, 'pro': pro, 'eps': 1e-6})
+    b = g.to_bundle()
+    vm = VM(b).run()
+    with Executor() as ex:
+        ex.load(b)
+        assert ex.run().done == len(b.tasks)
+        assert ex.plan_info()[:2] == (True, True)
+        assert rel_err(ex.read_buffer('out'), vm.buffer('out').a) <= 2e-5
