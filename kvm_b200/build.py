@@ -17,15 +17,25 @@ FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-std=c++17', '-li
          '--expt-relaxed-constexpr', '--extended-lambda', '-Xcudafe', '--diag_suppress=177']
 
 
-def sources():
-    return sorted(CSRC.glob('*')) + [PKG.parent / 'include' / 'kvm_b200.h', PKG.parent / 'include' / 'kvm_ops.def']
+# files that only one of the two translation units reads (everything else under csrc/ and include/ feeds both)
+ONLY = {'kvm_exec': {'kvm_exec.cu', 'kvm_sched.cuh', 'kvm_host.inl', 'kvm_gemm_host.inl', 'kvm_static_host.inl', 'kvm_json.hpp'},
+        'kvm_static': {'kvm_static.cu', 'kvm_static.cuh'}}
+
+
+def sources(unit=None):
+    skip = {'kvm_cli.cpp'} | (set().union(*(v for k, v in ONLY.items() if k != unit)) if unit else set())
+    return [p for p in sorted(CSRC.glob('*')) if p.name not in skip] + [PKG.parent / 'include' / 'kvm_b200.h', PKG.parent / 'include' / 'kvm_ops.def']
+
+
+def unit_stale(unit) -> bool:
+    obj = PKG / f'_{unit}.o'
+    return not obj.exists() or any(s.stat().st_mtime > obj.stat().st_mtime for s in sources(unit))
 
 
 def stale() -> bool:
     if not LIB.exists():
         return True
-    t = LIB.stat().st_mtime
-    return any(s.stat().st_mtime > t for s in sources())
+    return any(unit_stale(u) for u in UNITS) or any((PKG / f'_{u}.o').stat().st_mtime > LIB.stat().st_mtime for u in UNITS)
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
@@ -36,6 +46,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for unit in UNITS:
         obj = PKG / f'_{unit}.o'
         objs.append(obj)
+        if not force and not unit_stale(unit):
+            continue
         cmd = [NVCC, *FLAGS, *(['-Xptxas', '-v'] if verbose else []), '-c', str(CSRC / f'{unit}.cu'), '-o', str(obj)]
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
     for cmd, p in procs:

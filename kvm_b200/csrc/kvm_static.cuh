@@ -20,7 +20,7 @@
 #include "kvm_static_api.h"
 
 #define KVM_ST_SLOTS 4                 // record ring depth (tasks fetched ahead)
-#define KVM_ST_HDR 2048                // header bytes: slots, control words, barriers
+#define KVM_ST_HDR 3072                // header bytes: slots, control words, barriers
 #define KVM_ST_RING (KVM_ST_NSTAGE * KVM_ST_STAGE)
 #define KVM_ST_ARRIVALS 8              // consumer arrivals that free a stage
 
@@ -37,6 +37,7 @@ struct KvmStSlot {
   int4 aux;
   int prefetch;               // 1: copies may be issued before the dependencies are met
   int j0, j1, newrow;         // attention: key range of the split, index of the appended key inside it (-1 none)
+  KvmBuf lb[7];               // streamed tasks: the buffer-table entries of the task's buffer arguments (argument j -> lb[j]), looked up once by the front warp
 };
 static_assert(sizeof(KvmStSlot) * KVM_ST_SLOTS + 128 * 4 + 64 <= KVM_ST_HDR, "static header too small");
 
@@ -55,16 +56,31 @@ __device__ __forceinline__ uint32_t kvm_ring_full(const KvmRing& r, unsigned it)
 __device__ __forceinline__ uint32_t kvm_ring_empty(const KvmRing& r, unsigned it) { return r.bar0 + 64 + 8 * (it % KVM_ST_NSTAGE); }
 __device__ __forceinline__ uint32_t kvm_ring_parity(unsigned it) { return (it / KVM_ST_NSTAGE) & 1u; }
 
+// Buffer argument j of a streamed task from the slot's own copy of the table entries (same checks as kvm_buf).
+__device__ __forceinline__ bool kvm_buf_local(const KvmCtx& c, const KvmBuf* lb, const int32_t* a, int j, int mask, KvmBuf& out, bool optional = false) {
+  const int idx = a[j];
+  if (idx == -1 && optional) { out.p = nullptr; out.rows = out.cols = out.ld = 0; out.dtype = 0; return true; }
+  if (idx < 0 || idx >= c.nbufs) { c.fail(KVM_OPE_BUF, idx); return false; }
+  out = lb[j];
+  if (out.p == nullptr || !((1 << out.dtype) & mask)) { c.fail(KVM_OPE_DTYPE, idx, out.dtype); return false; }
+  return true;
+}
+__device__ __forceinline__ int kvm_ld_relaxed(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- streamed GEMV, consumer side --------------------------------------------------------------------------------------------
 // Stage use `cit + ci` holds rows n0 + ci*R .. of the weight matrix in full (R*K*2 bytes).  Warps 0..7 consume: warp = (row r of the
 // stage, part of K); the activation row v = bf16(prologue(x)) is staged once as bf16.  Partial sums are added in part order.
 // Semantics as kvm_op_gemv_bf16 (runtime/ref_extra.py:398-415).  Always consumes its nchunks stage uses, also after an error.
-static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline) {
+static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline) {
   KvmBuf x, x2, gm, w, out, res;
   const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
   const float eps = kvm_bits_f32(a[10]);
-  bool ok = kvm_buf(c, a[0], KVM_M_FLT, x) && kvm_buf(c, a[1], KVM_M_FLT, x2, true) && kvm_buf(c, a[2], KVM_M_F32, gm, true) && kvm_buf(c, a[3], KVM_M_BF16, w) &&
-            kvm_buf(c, a[4], KVM_M_FLT, out) && kvm_buf(c, a[5], KVM_M_FLT, res, true);
+  bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, x) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, x2, true) && kvm_buf_local(c, lb, a, 2, KVM_M_F32, gm, true) &&
+            kvm_buf_local(c, lb, a, 3, KVM_M_BF16, w) && kvm_buf_local(c, lb, a, 4, KVM_M_FLT, out) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, res, true);
   const int rows = n1 - n0;
   const int KP = KVM_ST_ARRIVALS / R;
   const int fixed = ((K * 2 + 127) & ~127) + 256 + ((rows + 7) & ~7) * KP * 4;
@@ -162,10 +178,12 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
 // ---- streamed split attention, consumer side ----------------------------------------------------------------------------------
 // Stage use `cit` holds the split's keys, `cit + 1` its values (the appended row left out).  Semantics as kvm_op_attn_decode_part
 // (runtime/ref_extra.py:421-498); the front warp has validated the geometry before it issued the copies.
-static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow, unsigned long long deadline) {
+static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow,
+                                          unsigned long long deadline) {
   KvmBuf q, kc, vc, lens, part, kn, vn;
-  bool ok = kvm_buf(c, a[0], KVM_M_FLT, q) && kvm_buf(c, a[1], KVM_M_FLT, kc) && kvm_buf(c, a[2], KVM_M_FLT, vc) && kvm_buf(c, a[3], KVM_M_I32, lens) &&
-            kvm_buf(c, a[4], KVM_M_F32, part) && kvm_buf(c, a[5], KVM_M_FLT, kn, true) && kvm_buf(c, a[6], KVM_M_FLT, vn, true);
+  bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, q) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, kc) && kvm_buf_local(c, lb, a, 2, KVM_M_FLT, vc) &&
+            kvm_buf_local(c, lb, a, 3, KVM_M_I32, lens) && kvm_buf_local(c, lb, a, 4, KVM_M_F32, part) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, kn, true) &&
+            kvm_buf_local(c, lb, a, 6, KVM_M_FLT, vn, true);
   const int b = a[7], kvh = a[8], s = a[9], S = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
   const float sc = kvm_bits_f32(a[15]), theta = kvm_bits_f32(a[16]);
   const int G = H / Hkv, half = hd / 2;
@@ -253,7 +271,7 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
   if (op == 134) {
     const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8];
     if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || K <= 0 || (K & 255) || K * 2 > KVM_ST_STAGE) return;
-    const KvmBuf w = S.bufs[wi];
+    const KvmBuf w = sl.lb[3];
     if (!w.p || w.dtype != KVM_BF16 || (w.ld & 7) || ((uintptr_t)w.p & 15) || n1 > w.rows || K > w.cols) return;
     int R = KVM_ST_STAGE / (K * 2);
     if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
@@ -265,7 +283,7 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
     if (b < 0 || Hkv <= 0 || H <= 0 || H % Hkv || kvh < 0 || kvh >= Hkv || s < 0 || Sp <= 0 || s >= Sp || Tmax <= 0 || !(fl == 0 || fl == 1 || fl == 3)) return;
     const int G = H / Hkv;
     if (G > 8 || (G & (G - 1)) || !(hd == 16 || hd == 32 || hd == 64 || hd == 128)) return;
-    const KvmBuf kc = S.bufs[kci], vc = S.bufs[vci], lens = S.bufs[li];
+    const KvmBuf kc = sl.lb[1], vc = sl.lb[2], lens = sl.lb[3];
     if (!kc.p || !vc.p || !lens.p || kc.dtype != KVM_BF16 || vc.dtype != KVM_BF16 || lens.dtype != KVM_I32 || kc.ld != hd || vc.ld != hd || ((uintptr_t)kc.p & 15) || ((uintptr_t)vc.p & 15)) return;
     if ((long long)(b + 1) * Hkv * Tmax > kc.rows || (long long)(b + 1) * Hkv * Tmax > vc.rows || hd > kc.cols || hd > vc.cols || lens.ld != lens.cols || b >= lens.rows * lens.cols) return;
     const int p0 = ((const int*)lens.p)[b], n = p0 + 1;
@@ -282,7 +300,7 @@ static __device__ void kvm_static_issue(const KvmDevState& S, const KvmStSlot& s
   const uint32_t full = kvm_ring_full(ring, it), dst = ring.base_addr + (it % KVM_ST_NSTAGE) * KVM_ST_STAGE;
   const int32_t* a = sl.args;
   if (sl.kind == 1) {
-    const KvmBuf w = S.bufs[a[3]];
+    const KvmBuf w = sl.lb[3];
     const int n0 = a[6], n1 = a[7], K = a[8], R = sl.R;
     const int r0 = n0 + ci * R, nr = min(R, n1 - r0);
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p;
@@ -290,7 +308,7 @@ static __device__ void kvm_static_issue(const KvmDevState& S, const KvmStSlot& s
     if (w.ld == K) kvm_bulk_g2s(dst, wp + (size_t)r0 * w.ld, (uint32_t)(nr * K * 2), full);
     else for (int r = 0; r < nr; ++r) kvm_bulk_g2s(dst + r * K * 2, wp + (size_t)(r0 + r) * w.ld, (uint32_t)(K * 2), full);
   } else {
-    const KvmBuf cb = S.bufs[a[ci == 0 ? 1 : 2]];
+    const KvmBuf cb = sl.lb[ci == 0 ? 1 : 2];
     const int b = a[7], kvh = a[8], Hkv = a[12], hd = a[13], Tmax = a[14];
     const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
     const int nk = max(sl.j1 - sl.j0, 0), ncopy = sl.newrow >= 0 ? nk - 1 : nk;
@@ -341,6 +359,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
     const int lane = tid & 31;
     int fi = 0, ri = 0, ii = 0, ic = 0;        // next position to fetch / to mark ready / to stream; chunk inside the streamed task
     unsigned pit = 0;                          // stage uses issued
+    int dep[5] = {-1, -1, -1, -1, -1}, dep_pos = -1;     // dependency entries of the task at `ri`
     bool stop = false;
     unsigned idle = 0;
     while (!stop && (ri < n || ii < n)) {
@@ -358,6 +377,16 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
         if (lane == 10) sl.prefetch = w1 & 1;
         if (lane == 31) sl.task = task;
         __syncwarp();
+        if (use_ring) {                                      // table entries of the buffer arguments of a streaming op, lanes in parallel
+          const int op = sl.desc[0], nb = op == 134 ? 6 : op == 135 ? 7 : 0;
+          if (lane < nb) {
+            const int idx = sl.args[lane];
+            KvmBuf e; e.p = nullptr; e.rows = e.cols = e.ld = 0; e.dtype = 0; e.reserved[0] = e.reserved[1] = 0;
+            if (idx >= 0 && idx < S.nbufs) e = S.bufs[idx];
+            sl.lb[lane] = e;
+          }
+          __syncwarp();
+        }
         if (lane == 0) {
           if (use_ring) kvm_static_geometry(S, sl, (int)dyn - KVM_ST_HDR - KVM_ST_RING); else { sl.kind = 0; sl.nchunks = 0; }
           sl.state = 1;
@@ -365,36 +394,44 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
         __syncwarp();
         ++fi; progressed = true;
       }
-      // 2. stream ahead: the next chunk of the oldest task that still has copies to issue
+      // 2. stream ahead: chunks of the oldest tasks that still have copies to issue, as many as there are free stages
       if (ii < fi) {
-        KvmStSlot& sl = slots[ii % KVM_ST_SLOTS];
-        const int kind = kvm_ld_volatile_shared(&sl.kind);
-        if (kind == 0) { ++ii; ic = 0; progressed = true; }
-        else if (sl.prefetch || ii < ri) {                 // constants may run ahead; anything else waits until the task is ready
-          int issued = 0;
-          if (lane == 0) {
-            const bool free_stage = pit < KVM_ST_NSTAGE || kvm_mbar_test(kvm_ring_empty(ring, pit), kvm_ring_parity(pit) ^ 1u);
-            if (free_stage) {
-              if (!sl.prefetch) asm volatile("fence.proxy.async;" ::: "memory");      // data other workers wrote with plain stores, read here by bulk copies
-              kvm_static_issue(S, sl, ring, pit, ic);
-              issued = 1;
-            }
+        int lii = ii, lic = ic;
+        unsigned lpit = pit;
+        if (lane == 0) {
+          for (int guard = 0; guard < 2 * KVM_ST_NSTAGE && lii < fi; ++guard) {
+            KvmStSlot& sl = slots[lii % KVM_ST_SLOTS];
+            if (sl.kind == 0) { ++lii; lic = 0; continue; }
+            if (!(sl.prefetch || lii < ri)) break;           // constants may run ahead; anything else waits until the task is ready
+            if (!(lpit < KVM_ST_NSTAGE || kvm_mbar_test(kvm_ring_empty(ring, lpit), kvm_ring_parity(lpit) ^ 1u))) break;
+            if (!sl.prefetch) asm volatile("fence.proxy.async;" ::: "memory");      // data other workers wrote with plain stores, read here by bulk copies
+            kvm_static_issue(S, sl, ring, lpit, lic);
+            ++lpit; ++lic;
+            if (lic >= sl.nchunks) { ++lii; lic = 0; }
           }
-          issued = __shfl_sync(0xffffffffu, issued, 0);
-          if (issued) { ++pit; ++ic; progressed = true; if (ic >= sl.nchunks) { ++ii; ic = 0; } }
         }
+        lii = __shfl_sync(0xffffffffu, lii, 0); lic = __shfl_sync(0xffffffffu, lic, 0); lpit = __shfl_sync(0xffffffffu, lpit, 0);
+        if (lii != ii || lic != ic) progressed = true;
+        ii = lii; ic = lic; pit = lpit;
       }
-      // 3. dependencies of the next task to become ready
+      // 3. dependencies of the next task to become ready: its entries are held in registers (up to five per lane) and polled with
+      //    plain loads, all in flight together; one acquire fence once they are all met
       if (ri < fi) {
         KvmStSlot& sl = slots[ri % KVM_ST_SLOTS];
-        const int off = sl.wait_off, cnt = sl.wait_cnt;
-        bool met = true;
-        for (int k = lane; k < cnt; k += 32) {
-          const int e = T.waits[off + k];
-          if (kvm_ld_acquire(&T.progress[e >> KVM_ST_WAIT_BITS]) < (e & ((1 << KVM_ST_WAIT_BITS) - 1))) met = false;
+        if (dep_pos != ri) {
+          const int off = sl.wait_off, cnt = sl.wait_cnt;
+#pragma unroll
+          for (int j = 0; j < 5; ++j) dep[j] = lane + 32 * j < cnt ? T.waits[off + lane + 32 * j] : -1;
+          dep_pos = ri;
         }
+        int seen[5];
+#pragma unroll
+        for (int j = 0; j < 5; ++j) seen[j] = dep[j] >= 0 ? kvm_ld_relaxed(&T.progress[dep[j] >> KVM_ST_WAIT_BITS]) : 0;
+        bool met = true;
+#pragma unroll
+        for (int j = 0; j < 5; ++j) if (dep[j] >= 0 && seen[j] < (dep[j] & ((1 << KVM_ST_WAIT_BITS) - 1))) met = false;
         if (__all_sync(0xffffffffu, met)) {
-          __threadfence();                                   // what the finished predecessors wrote is visible to this CTA's compute group
+          __threadfence();                                   // acquire: what the finished predecessors wrote is visible to this CTA's compute group
           if (lane == 0) { S.indeg[sl.task] = 0; sl.state = 2; }     // every predecessor's completion was observed
           __syncwarp();
           ++ri; progressed = true;
@@ -450,8 +487,8 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
       c.task = task;
       if (tid == 0 && S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
       const int op = sl.desc[0], kind = sl.kind, nch = sl.nchunks;
-      if (kind == 1) kvm_gemv_ring(c, sl.args, ring, cit, sl.R, nch, deadline);
-      else if (kind == 2) kvm_attn_part_ring(c, sl.args, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
+      if (kind == 1) kvm_gemv_ring(c, sl.args, sl.lb, ring, cit, sl.R, nch, deadline);
+      else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
       else if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       cit += (unsigned)nch;
       asm volatile("fence.proxy.async;" ::: "memory");

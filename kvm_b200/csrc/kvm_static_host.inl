@@ -81,7 +81,8 @@ static std::vector<char> kvm_written_buffers(const KvmExec* h) {
 // statically (a version wait that nothing in the program and no base version satisfies).
 static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, KvmStaticPlan& plan) {
   const int nt = (int)h->tasks.size(), W = h->workers;
-  if (W >= (1 << (31 - KVM_ST_WAIT_BITS)) || nt >= (1 << KVM_ST_WAIT_BITS)) { h->error = "static path: too many workers or tasks for the dependency encoding"; return KVM_E_STATE; }
+  // a dependency list has one entry per worker at most, and the front warp holds 5 x 32 of them
+  if (W > 160 || nt >= (1 << KVM_ST_WAIT_BITS)) { h->error = "static path: too many workers or tasks for the dependency encoding"; return KVM_E_STATE; }
   // predecessors: in-batch edges plus version waits turned into edges on their publisher
   std::vector<std::vector<int>> preds(nt);
   std::vector<int> indeg(nt, 0);

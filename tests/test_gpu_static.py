@@ -98,7 +98,10 @@ def test_training_step_on_the_static_path(kvm_lib, precision):
     assert res.done == len(b.tasks) and ex.plan_info()[0] and not ex.plan_info()[1]
     execs, observed = ex.task_counts()
     assert (execs == 1).all() and np.array_equal(observed, b.tasks['indegree'])
-    compare(ex, vm, 2e-5 if precision == 'f32' else 1e-2)
+    # bf16: the biases start at zero, so after one AdamW step they are lr * sign(gradient); where a gradient element is at the
+    # noise level of the bf16 activations its sign, and with it the whole value, may differ: the weights are compared through
+    # their gradients and moments instead (the reference judges post-AdamW weights by a float64 replay for the same reason)
+    compare(ex, vm, 2e-5 if precision == 'f32' else 1e-2, skip=() if precision == 'f32' else ('w.',))
     assert ex.get_version(0) == 2
     ex.close()
 
