@@ -16,14 +16,6 @@
 #define KVM_ATT_NBAR 12
 
 __device__ __forceinline__ float kvm_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
-__device__ __forceinline__ void kvm_tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t* r = (uint32_t*)v;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-                 "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void kvm_att_init(int* ctl) {      // thread 32 at kernel start
   for (int i = 0; i < KVM_ATT_NBAR; ++i) { kvm_mbar_init(kvm_bar_addr(ctl, KVM_CTL_ABAR + i), 1); ctl[KVM_CTL_ACNT + i] = 0; }
 }

@@ -47,6 +47,8 @@ struct KvmCtx {
   int* ctl;                   // executor control words in shared memory (ctl[0] = TMEM base address)
   const void* tmaps;          // tensor-map table of the tensor-core tasks
   int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
+  int engine;                 // 1: the kernel's engine warps run the mainloops of tensor-core GEMM tiles, the op body is their epilogue only
+  unsigned gemm_seq;          // with engine: how many tensor-core GEMM tiles this CTA ran before this one (accumulator = gemm_seq & 1)
 
   // First error wins (reference: mvm_fail, include/mvm_exec.cuh:260-266).  `fail` is for errors every thread of the group sees
   // alike (argument checks): all call it with the same arguments and thread 0 records.  `fail_any` is for data-dependent

@@ -78,6 +78,15 @@ __device__ __forceinline__ void kvm_tmem_ld32(uint32_t taddr, float (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void kvm_tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = (uint32_t*)v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                 "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor (SM100 format): start address, leading / stride byte offsets in 16-byte units,
 // descriptor version 1, 128-byte swizzle.
 __device__ __forceinline__ uint64_t kvm_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -98,6 +107,7 @@ __device__ __forceinline__ void kvm_tc_init(int* ctl, unsigned char* smem) {
   }
   if (threadIdx.x == 32) {
     for (int i = 0; i < 2 * KVM_TC_STAGES + 1; ++i) kvm_mbar_init(kvm_bar_addr(ctl, i), 1);
+    for (int i = 21; i < 25; ++i) kvm_mbar_init(kvm_bar_addr(ctl, i), 1);          // accumulator full / empty of the overlapped pipeline
     ctl[KVM_CTL_PROD_IT] = 0; ctl[KVM_CTL_MMA_IT] = 0; ctl[KVM_CTL_ACC_PH] = 0;
     kvm_att_init(ctl);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -299,11 +309,14 @@ static __device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const
   }
 }
 
+static __device__ void kvm_tce_epilogue(const KvmCtx& c, const KvmMmArgs& g);
+__device__ __forceinline__ void kvm_mbar_arrive_local(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 // aux.x = 1: tensor-core path planned by the host (aux.y / aux.z = tensor-map indices of A / B); else SIMT fallback.
 static __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmMmArgs g;
   if (!kvm_mm_args(c, a, 2, g)) return;
   if (aux.x != 1 || (c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) { kvm_mm_simt(c, g); return; }
+  if (c.engine) { kvm_tce_epilogue(c, g); return; }      // the engine warps run this tile's mainloop (ready-queue kernel)
   if (c.pair >= 0) { g.m0 &= ~255; kvm_mm_tc_pair(c, g, aux); return; }       // this task and its partner: rows m0.. and m0+128..
   int* ctl = c.ctl;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -376,4 +389,166 @@ static __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a,
     kvm_sync();
   }
   if (threadIdx.x == 0) ctl[KVM_CTL_ACC_PH] = (int)(acc_ph ^ 1);
+}
+
+
+// ---- the overlapped pipeline of the ready-queue kernel ---------------------------------------------------------------------------
+// In the ready-queue kernel two extra warps run the mainloops (one thread issues the TMA loads, one the MMAs) for every tensor-core
+// GEMM task as soon as it is staged, into one of TWO TMEM accumulators (columns 0..255 / 256..511), while the 16 compute warps are
+// still draining the previous tile: tile n's epilogue overlaps tile n+1's mainloop and the first loads of tile n+2.
+//   shared memory of the op scratch:  [0, KVM_TCE_STAGING)  epilogue staging (64 accumulator columns at a time)
+//                                     [KVM_TCE_STAGING, + 3 x 48 KB)  operand ring of the engine
+//   barriers (ctl barrier indices):   full[s] = s, empty[s] = 4 + s (s < 3), accumulator full[a] = 21 + a, accumulator empty[a] = 23 + a
+// The engine only starts a tile while the compute group runs another tensor-core GEMM tile or has finished everything before it:
+// any other op may use the whole scratch.
+#define KVM_TCE_STAGES 3
+#define KVM_TCE_STAGING 50176              // 49 KB: a multiple of 1024 (the ring's swizzled tiles start behind it), at least 128 rows x 68 floats
+#define KVM_TCE_BAR_ACC_FULL 21
+#define KVM_TCE_BAR_ACC_EMPTY 23
+#define KVM_TCE_CHUNK 64                  // accumulator columns staged at a time
+#define KVM_TCE_PITCH 68                  // floats per staged row (conflict-free 16-byte accesses)
+
+// Bounded wait that also gives up when an error has been recorded anywhere (the other side may have left).
+__device__ __forceinline__ bool kvm_mbar_wait_err(uint32_t bar, uint32_t parity, const KvmErrRec* err) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 127u) == 127u) {
+      if (*(volatile const int*)&err->code != 0) return false;
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (!t0) t0 = t; else if (t - t0 > 4000000000ull) return false;      // four seconds: the other side is not coming
+    }
+  }
+}
+
+// One tile's loads (engine producer thread).  `it` is the producer's running stage counter.
+__device__ __forceinline__ bool kvm_tce_produce(int* ctl, uint32_t ring0, const void* tmaps, const int32_t* a, const int4& aux, uint32_t& it, const KvmErrRec* err) {
+  const int m0 = a[6], n0 = a[7], K = a[10], fl = a[11];
+  const bool ta = fl & 1, tb = fl & 2;
+  const int num_kb = (K + KVM_TC_BK - 1) / KVM_TC_BK;
+  const char* tmA = (const char*)tmaps + (size_t)aux.y * 128;
+  const char* tmB = (const char*)tmaps + (size_t)aux.z * 128;
+  asm volatile("fence.proxy.async;" ::: "memory");     // operands written by other tasks' plain stores are read here through TMA
+  for (int kb = 0; kb < num_kb; ++kb, ++it) {
+    const int s = it % KVM_TCE_STAGES;
+    const uint32_t ph = (it / KVM_TCE_STAGES) & 1;
+    if (it >= KVM_TCE_STAGES && !kvm_mbar_wait_err(kvm_bar_addr(ctl, 4 + s), ph ^ 1, err)) return false;
+    const uint32_t full = kvm_bar_addr(ctl, s), sa = ring0 + s * KVM_TC_STAGE_BYTES, sb = sa + KVM_TC_A_BYTES;
+    kvm_mbar_expect_tx(full, KVM_TC_STAGE_BYTES);
+    const int k0 = kb * KVM_TC_BK;
+    if (!ta) kvm_tma_load_2d(sa, tmA, k0, m0, full);
+    else { kvm_tma_load_2d(sa, tmA, m0, k0, full); kvm_tma_load_2d(sa + 8192, tmA, m0 + 64, k0, full); }
+    if (tb) kvm_tma_load_2d(sb, tmB, k0, n0, full);
+    else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kvm_tma_load_2d(sb + i * 8192, tmB, n0 + 64 * i, k0, full);
+    }
+  }
+  return true;
+}
+
+// One tile's MMAs (engine MMA thread) into accumulator `g & 1`; `g` counts the tensor-core tiles of this CTA.
+__device__ __forceinline__ bool kvm_tce_mma(int* ctl, uint32_t ring0, uint32_t tmem, const int32_t* a, uint32_t& it, uint32_t g, const KvmErrRec* err) {
+  const int K = a[10], fl = a[11];
+  const bool ta = fl & 1, tb = fl & 2;
+  const int num_kb = (K + KVM_TC_BK - 1) / KVM_TC_BK;
+  const uint32_t acc = g & 1u, use = g >> 1;
+  if (use > 0 && !kvm_mbar_wait_err(kvm_bar_addr(ctl, KVM_TCE_BAR_ACC_EMPTY + acc), (use - 1) & 1, err)) return false;     // the tile before last has been drained
+  kvm_tc_fence_after();
+  const uint32_t idesc = kvm_idesc_bf16(128, 256, ta, !tb), d = tmem + acc * 256;
+  for (int kb = 0; kb < num_kb; ++kb, ++it) {
+    const int s = it % KVM_TCE_STAGES;
+    const uint32_t ph = (it / KVM_TCE_STAGES) & 1;
+    if (!kvm_mbar_wait_err(kvm_bar_addr(ctl, s), ph, err)) return false;
+    kvm_tc_fence_after();
+    const uint32_t sa = ring0 + s * KVM_TC_STAGE_BYTES, sb = sa + KVM_TC_A_BYTES;
+#pragma unroll
+    for (int j = 0; j < KVM_TC_BK / 16; ++j) {
+      const uint64_t da = ta ? kvm_smem_desc(sa + j * 2048, 8192, 1024) : kvm_smem_desc(sa + j * 32, 16, 1024);
+      const uint64_t db = tb ? kvm_smem_desc(sb + j * 32, 16, 1024) : kvm_smem_desc(sb + j * 2048, 8192, 1024);
+      kvm_tc_mma_bf16(d, da, db, idesc, (kb | j) ? 1u : 0u);
+    }
+    kvm_tc_commit(kvm_bar_addr(ctl, 4 + s));
+  }
+  kvm_tc_commit(kvm_bar_addr(ctl, KVM_TCE_BAR_ACC_FULL + acc));
+  return true;
+}
+
+// The compute group's share of a tile whose mainloop the engine runs: wait for the accumulator, drain it 64 columns at a time
+// through the staging area (TMEM -> shared memory by (lane quarter, 16 columns) per warp; then thread = (row, 8 columns): every
+// global access a whole row segment), hand the accumulator back.
+static __device__ void kvm_tce_epilogue(const KvmCtx& c, const KvmMmArgs& g) {
+  int* ctl = c.ctl;
+  const uint32_t acc = c.gemm_seq & 1u, use = c.gemm_seq >> 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = warp & 3, cgi = warp >> 2;
+  kvm_tc_fence_after();
+  const uint32_t tmem = *(volatile uint32_t*)(ctl + KVM_CTL_TMEM) + acc * 256;
+  bool ok = kvm_mbar_wait_err(kvm_bar_addr(ctl, KVM_TCE_BAR_ACC_FULL + acc), use & 1, c.err);
+  kvm_tc_fence_after();
+  if (!ok && atomicCAS(&c.err->code, 0, KVM_ERR_TIMEOUT) == 0) { c.err->task = c.task; c.err->a = 2122; c.err->b = (int)threadIdx.x; }
+  if (kvm_tc_epi_vec_ok(g)) {
+    float* T = (float*)c.smem;
+    const bool simple = !(g.flags & 512);
+    const float* bias = (const float*)g.bias.p;
+#pragma unroll 1
+    for (int ch = 0; ch < 256 / KVM_TCE_CHUNK; ++ch) {
+      {
+        float v[16];
+        kvm_tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ch * KVM_TCE_CHUNK + cgi * 16), v);
+        float* dst = T + (size_t)(q * 32 + lane) * KVM_TCE_PITCH + cgi * 16;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+      if (ch == 256 / KVM_TCE_CHUNK - 1) kvm_tc_fence_before();
+      kvm_sync();
+      if (ch == 256 / KVM_TCE_CHUNK - 1 && threadIdx.x == 0 && ok) kvm_mbar_arrive_local(kvm_bar_addr(ctl, KVM_TCE_BAR_ACC_EMPTY + acc));      // every TMEM read of this tile is done
+      if (ok) {
+        for (int item = threadIdx.x; item < 128 * (KVM_TCE_CHUNK / 8); item += KVM_NT) {
+          const int r = item >> 3, cc = (item & 7) * 8, m = g.m0 + r, n = g.n0 + ch * KVM_TCE_CHUNK + cc;
+          if (m >= g.M || n >= g.N) continue;
+          const float* src = T + (size_t)r * KVM_TCE_PITCH + cc;
+          float v[8];
+          *(float4*)v = *(const float4*)src; *(float4*)(v + 4) = *(const float4*)(src + 4);
+          if (n + 8 <= g.N && simple) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] *= g.alpha;
+            if (bias) { *(float4*)t = *(const float4*)(bias + n); *(float4*)(t + 4) = *(const float4*)(bias + n + 4);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+            if (g.pre.p) kvm_st8(g.pre, (size_t)m * g.pre.ld + n, v);
+            if (g.flags & 8) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = kvm_gelu(v[j]);
+            }
+            if (g.res.p) { kvm_ld8(g.res, (size_t)m * g.res.ld + n, t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+            if (g.flags & 4) { kvm_ld8(g.out, (size_t)m * g.out.ld + n, t);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += t[j]; }
+            kvm_st8(g.out, (size_t)m * g.out.ld + n, v);
+          } else {
+            for (int j = 0; j < 8 && n + j < g.N; ++j) kvm_st(g.out, (size_t)m * g.out.ld + n + j, kvm_mm_epilogue(g, v[j], m, n + j));
+          }
+        }
+      }
+      kvm_sync();
+    }
+  } else {
+    const int m = g.m0 + q * 32 + lane;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int col = cgi * 64 + h * 32;
+      float acc32[32];
+      kvm_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)col, acc32);
+      if (ok && m < g.M) kvm_tc_store32(g, acc32, m, g.n0 + col);
+    }
+    kvm_tc_fence_before();
+    kvm_sync();
+    if (threadIdx.x == 0 && ok) kvm_mbar_arrive_local(kvm_bar_addr(ctl, KVM_TCE_BAR_ACC_EMPTY + acc));
+  }
 }

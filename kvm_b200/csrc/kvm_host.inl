@@ -457,6 +457,8 @@ static KvmDevState kvm_dev_state(KvmExec* h) {
   S.cfg_flags = h->cfg.flags;
   S.tmaps = h->d_tmaps; S.task_aux = h->d_aux; S.recs = h->d_recs; S.claim = h->d_claim; S.buf_cache = kvm_feature_on("KVM_B200_BUFCACHE", h->has_gemv ? 0 : 1) ? 1 : 0;
   { const char* v = getenv("KVM_B200_PAIR_DEPTH"); S.pair_depth = v && *v ? atoi(v) : 2 * h->workers; }
+  // overlapped GEMM pipeline: on unless tiles are stacked (that path owns both accumulators) or tensor cores are off; KVM_B200_ENGINE=0 for A/B measurements
+  S.engine = !(h->cfg.flags & KVM_CFG_NO_TENSOR_CORES) && !kvm_feature_on("KVM_B200_PAIRING", (h->cfg.flags & KVM_CFG_PAIR_TILES) ? 1 : 0) && kvm_feature_on("KVM_B200_ENGINE", 1) ? 1 : 0;
   return S;
 }
 
@@ -479,7 +481,7 @@ static bool kvm_wants_static(KvmExec* h, bool has_gemv) {
 
 static void kvm_launch(KvmExec* h) {
   if (h->use_static) kvm_static_launch(kvm_static_state(h), h->workers, h->smem_bytes, h->stream);
-  else { KvmDevState S = kvm_dev_state(h); kvm_exec_kernel<<<h->workers, KVM_NT + 32, h->smem_bytes, h->stream>>>(S); }
+  else { KvmDevState S = kvm_dev_state(h); kvm_exec_kernel<<<h->workers, KVM_EXEC_THREADS, h->smem_bytes, h->stream>>>(S); }
 }
 
 // Upload whatever changed since the last run, arm the counters and enqueue the roots.
@@ -687,7 +689,7 @@ extern "C" int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32
 extern "C" int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes) {
   if (!h) return KVM_E_ARG;
   if (workers) *workers = h->workers;
-  if (threads) *threads = KVM_NT + 32;
+  if (threads) *threads = h->use_static ? KVM_NT + 32 : KVM_EXEC_THREADS;
   if (smem_bytes) *smem_bytes = h->smem_bytes;
   return 0;
 }

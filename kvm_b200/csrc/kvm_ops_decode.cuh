@@ -196,73 +196,116 @@ static __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   else kvm_decode_group(kc, vc, base, 0, n, 1, hd, sc, qs, ws, emit);
 }
 
-static __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) {
-  KvmBuf q, kc, vc, lens, part, kn, vn;
+// What a split-attention task does before it looks at the cache: inverse frequencies, the appended key (optionally RMS-normalised,
+// rotated, stored to the cache and kept as floats for the staged tile) and value, the rotated (optionally normalised) queries
+// of the group.  Shared by the ready-queue form below and the ring form of the static path.  Whole compute group.
+struct KvmPartPro {
+  KvmBuf q, kc, vc, kn, vn, gam;      // gam.p == nullptr: no QK norm
+  int b, kvh, G, hd, fl, p0;
+  size_t base;
+  float theta, eps;
+  bool appends;
+  float *qs, *inv, *kns, *vns, *rsq;  // shared memory: G*hd queries, hd/2 frequencies, hd + hd appended row, G + 1 reciprocal RMS values
+};
+static __device__ void kvm_part_prologue(const KvmPartPro& P) {
+  const int hd = P.hd, half = hd / 2, G = P.G, b = P.b, kvh = P.kvh, n = P.p0 + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (P.gam.p) {
+    // reciprocal RMS per query head (warps 0..G-1) and of the appended key (warp G): float32 sums in a fixed lane / shuffle order
+    if (warp <= G) {
+      const bool key = warp == G;
+      float ss = 0.0f;
+      if (!key || P.kn.p)
+        for (int i = lane; i < hd; i += 32) {
+          const float t = key ? kvm_ld(P.kn, (size_t)b * P.kn.ld + kvh * hd + i) : kvm_ld(P.q, (size_t)b * P.q.ld + (kvh * G + warp) * hd + i);
+          ss += t * t;
+        }
+      ss = kvm_warp_sum(ss);
+      if (lane == 0) P.rsq[warp] = 1.0f / sqrtf(ss / hd + P.eps);
+    }
+    kvm_sync();
+  }
+  const float* gq = P.gam.p ? (const float*)P.gam.p : nullptr;
+  const float* gk = P.gam.p ? (const float*)P.gam.p + P.gam.ld : nullptr;
+  if (P.fl & 1) {
+    for (int i = threadIdx.x; i < half; i += KVM_NT) P.inv[i] = kvm_rope_inv(P.theta, i, hd);
+    kvm_sync();
+  }
+  if (P.appends) {
+    for (int i = threadIdx.x; i < half; i += KVM_NT) {
+      float sn, co; sincosf(__fmul_rn((float)P.p0, P.inv[i]), &sn, &co);
+      float x1 = kvm_ld(P.kn, (size_t)b * P.kn.ld + kvh * hd + i), x2 = kvm_ld(P.kn, (size_t)b * P.kn.ld + kvh * hd + i + half);
+      if (gk) { x1 = x1 * P.rsq[G] * gk[i]; x2 = x2 * P.rsq[G] * gk[i + half]; }
+      const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+      P.kns[i] = y1; P.kns[i + half] = y2;
+      kvm_st(P.kc, (P.base + n - 1) * P.kc.ld + i, y1);
+      kvm_st(P.kc, (P.base + n - 1) * P.kc.ld + i + half, y2);
+    }
+    for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) {
+      const float t = kvm_ld(P.vn, (size_t)b * P.vn.ld + kvh * hd + cc);
+      P.vns[cc] = t;
+      kvm_st(P.vc, (P.base + n - 1) * P.vc.ld + cc, t);
+    }
+  }
+  for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
+    const int g = e / half, i = e % half, h = kvh * G + g;
+    float x1 = kvm_ld(P.q, (size_t)b * P.q.ld + h * hd + i), x2 = kvm_ld(P.q, (size_t)b * P.q.ld + h * hd + i + half);
+    if (gq) { x1 = x1 * P.rsq[g] * gq[i]; x2 = x2 * P.rsq[g] * gq[i + half]; }
+    if (P.fl & 1) {
+      float sn, co; sincosf(__fmul_rn((float)P.p0, P.inv[i]), &sn, &co);
+      const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
+      x1 = y1; x2 = y2;
+      if (P.fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
+    }
+    P.qs[g * hd + i] = x1; P.qs[g * hd + i + half] = x2;
+  }
+}
+
+// attn_decode_part (135) and, with qkn, its QK-norm extension attn_decode_part_qkn (300: two more arguments, qk_gamma and eps).
+static __device__ void kvm_attn_decode_part_op(const KvmCtx& c, const int32_t* a, bool qkn) {
+  KvmBuf q, kc, vc, lens, part, kn, vn, gam{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
       !kvm_buf(c, a[4], KVM_M_F32, part) || !kvm_buf(c, a[5], KVM_M_FLT, kn, true) || !kvm_buf(c, a[6], KVM_M_FLT, vn, true)) return;
+  if (qkn && !kvm_buf(c, a[18], KVM_M_F32, gam)) return;
   const int b = a[7], kvh = a[8], s = a[9], S = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
   const float sc = kvm_bits_f32(a[15]), theta = kvm_bits_f32(a[16]);
   if (b < 0 || Hkv <= 0 || H % Hkv || kvh < 0 || kvh >= Hkv || s < 0 || s >= S || Tmax <= 0 || hd <= 0 || hd > 128 || (hd & 7) || H / Hkv > 8 ||
       !(fl == 0 || fl == 1 || fl == 3) || ((fl & 1) && (!kn.p || !vn.p))) { c.fail(KVM_OPE_SHAPE, hd, fl); return; }
   const int G = H / Hkv;
   if (!kvm_mat_ok(c, q, b + 1, H * hd) || !kvm_mat_ok(c, kc, (long long)(b + 1) * Hkv * Tmax, hd) || !kvm_mat_ok(c, vc, (long long)(b + 1) * Hkv * Tmax, hd) ||
-      !kvm_flat_ok(c, lens, b + 1) || !kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) || !kvm_mat_ok(c, kn, b + 1, Hkv * hd) || !kvm_mat_ok(c, vn, b + 1, Hkv * hd)) return;
+      !kvm_flat_ok(c, lens, b + 1) || !kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) || !kvm_mat_ok(c, kn, b + 1, Hkv * hd) || !kvm_mat_ok(c, vn, b + 1, Hkv * hd) ||
+      !kvm_mat_ok(c, gam, 2, hd)) return;
   const int p0 = ((const int*)lens.p)[b], n = p0 + 1;
   if (p0 < 0 || n > Tmax) { c.fail(KVM_OPE_KVLEN, b, p0); return; }
-  const int chunk = (n + S - 1) / S, j0 = s * chunk, j1 = min(n, s * chunk + chunk), half = hd / 2;
+  const int chunk = (n + S - 1) / S, j0 = s * chunk, j1 = min(n, s * chunk + chunk);
   const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
-  float* qs = (float*)(c.smem + KVM_AS_OFF_QS);                  // G*hd rotated queries
-  float* inv = (float*)(c.smem + KVM_AS_OFF_INV);                // hd/2 inverse frequencies
-  float* kns = (float*)(c.smem + KVM_AS_OFF_KNEW);               // the appended key (rotated) and value, float
-  float* vns = (float*)(c.smem + KVM_AS_OFF_VNEW);
+  KvmPartPro P;
+  P.q = q; P.kc = kc; P.vc = vc; P.kn = kn; P.vn = vn; P.gam = gam;
+  P.b = b; P.kvh = kvh; P.G = G; P.hd = hd; P.fl = fl; P.p0 = p0; P.base = base; P.theta = theta; P.eps = qkn ? kvm_bits_f32(a[19]) : 0.0f;
+  P.appends = (fl & 1) && j0 <= n - 1 && n - 1 < j1;    // this split holds the newest key: it appends (rotated key), rounded to the cache dtype
+  P.qs = (float*)(c.smem + KVM_AS_OFF_QS);                       // G*hd rotated queries
+  P.inv = (float*)(c.smem + KVM_AS_OFF_INV);                     // hd/2 inverse frequencies
+  P.kns = (float*)(c.smem + KVM_AS_OFF_KNEW);                    // the appended key (rotated) and value, float
+  P.vns = (float*)(c.smem + KVM_AS_OFF_VNEW);
+  P.rsq = (float*)(c.smem + KVM_AS_OFF_ML);                      // free until the softmax writes its (m, l) there
   float* ws = (float*)(c.smem + KVM_AS_OFF_SC);
-  const bool appends = (fl & 1) && j0 <= n - 1 && n - 1 < j1;    // this split holds the newest key: it appends (rotated key), rounded to the cache dtype
-  auto prologue = [&]() {
-    if (fl & 1) {
-      for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
-      kvm_sync();
-    }
-    if (appends) {
-      for (int i = threadIdx.x; i < half; i += KVM_NT) {
-        float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-        const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
-        const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
-        kns[i] = y1; kns[i + half] = y2;
-        kvm_st(kc, (base + n - 1) * kc.ld + i, y1);
-        kvm_st(kc, (base + n - 1) * kc.ld + i + half, y2);
-      }
-      for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) {
-        const float t = kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc);
-        vns[cc] = t;
-        kvm_st(vc, (base + n - 1) * vc.ld + cc, t);
-      }
-    }
-    for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
-      const int g = e / half, i = e % half, h = kvh * G + g;
-      float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
-      if (fl & 1) {
-        float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-        const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
-        x1 = y1; x2 = y2;
-        if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
-      }
-      qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
-    }
-  };
+  auto prologue = [&]() { kvm_part_prologue(P); };
   float* pp = (float*)part.p;
   auto emit = [&](int g, int cc, float M, float Lsum, float A) {
     const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
     pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
     if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M; pp[row + hd + 1] = Lsum; }
   };
-  if (kvm_attn_part_stream(c, kc, vc, base, j0, j1, appends ? n - 1 - j0 : -1, G, hd, sc, prologue, emit)) return;
+  if (kvm_attn_part_stream(c, kc, vc, base, j0, j1, P.appends ? n - 1 - j0 : -1, G, hd, sc, prologue, emit)) return;
   kvm_sync();
   prologue();
   __threadfence_block();
   kvm_sync();
-  if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
-  else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, qs, ws, emit);
+  if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, j0, j1, G, hd, sc, P.qs, ws, emit);
+  else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, P.qs, ws, emit);
 }
+static __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, false); }
+static __device__ void kvm_op_attn_decode_part_qkn(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, true); }
 
 static __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, o;

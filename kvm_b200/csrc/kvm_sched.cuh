@@ -16,11 +16,15 @@
 #pragma once
 #include "kvm_state.cuh"
 
+#define KVM_NSLOT 4               // tasks a worker holds at most: one running and up to three staged behind it
 struct KvmSlot {
   int task;                   // -1 = leave
   int state;                  // 0 free, 1 full, 2 finished (awaiting release)
   int pair;                   // partner task run together with `task` (stacked GEMM tiles), or -1
   int go;                     // written by compute thread 0 before the group's barrier: 0 leave, 1 run the op body, 2 skip it (an error is recorded)
+  int seq;                    // fill counter for the engine warps: 2k - 1 while fill k is being written, 2k once it is complete
+  int kind;                   // 1: a tensor-core GEMM tile whose mainloop the engine warps run; -1: leave; else 0
+  int pad[2];
   int32_t desc[16];
   int32_t args[KVM_MAX_ARGS];
   int4 aux;
@@ -211,14 +215,16 @@ static __device__ int kvm_finish_task(const KvmDevState& S, int task, int so, in
   if (lane == 0) atomicAdd(S.done, 1);
   return cont;
 }
-__global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S) {
+#define KVM_EXEC_THREADS (KVM_NT + 96)      // 16 compute warps, the scheduler warp, two engine warps (TMA producer, MMA issuer)
+__global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevState S) {
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
-  KvmSlot* slots = (KvmSlot*)kvm_smem;                 // two slots
-  int* ctl = (int*)(kvm_smem + 2 * sizeof(KvmSlot));   // ctl[0] = TMEM base, ctl[1..] scratch
-  static_assert(2 * sizeof(KvmSlot) + 96 * sizeof(int) <= KVM_EXEC_SMEM_HDR, "header too small");
+  KvmSlot* slots = (KvmSlot*)kvm_smem;                 // the slot ring
+  int* ctl = (int*)(kvm_smem + KVM_NSLOT * sizeof(KvmSlot));   // ctl[0] = TMEM base, ctl[1..] scratch
+  static_assert(KVM_NSLOT * sizeof(KvmSlot) + 96 * sizeof(int) <= KVM_EXEC_SMEM_HDR, "header too small");
   const int tid = threadIdx.x;
-  const bool is_sched = tid >= KVM_NT;
-  if (tid < 2) { slots[tid].state = 0; slots[tid].task = -1; }
+  const bool is_sched = tid >= KVM_NT && tid < KVM_NT + 32;
+  const int engine_role = tid == KVM_NT + 32 ? 1 : tid == KVM_NT + 64 ? 2 : 0;      // one thread each: TMA producer, MMA issuer
+  if (tid < KVM_NSLOT) { slots[tid].state = 0; slots[tid].task = -1; slots[tid].seq = 0; slots[tid].kind = 0; }
   unsigned dyn;
   asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   kvm_tc_init(ctl, kvm_smem);                          // TMEM allocation + mbarrier init (whole CTA)
@@ -229,10 +235,12 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
   if (buf_cache) {
     const uint4* src = (const uint4*)S.bufs;
     uint4* dst = (uint4*)(kvm_smem + KVM_EXEC_SMEM_HDR);
-    for (int i = tid; i < S.nbufs * 2; i += KVM_NT + 32) dst[i] = src[i];
+    for (int i = tid; i < S.nbufs * 2; i += KVM_EXEC_THREADS) dst[i] = src[i];
   }
   __syncthreads();
   const unsigned long long t_begin = kvm_globaltimer();
+  const int used_hdr = KVM_EXEC_SMEM_HDR + (buf_cache ? cache_bytes : 0);
+  const bool engine_on = S.engine && (int)dyn - used_hdr >= KVM_TCE_STAGING + KVM_TCE_STAGES * KVM_TC_STAGE_BYTES;
 
   if (is_sched) {
     const int lane = tid & 31;
@@ -241,6 +249,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
     int inflight = 0;          // slots handed to the compute group and not yet released
     int ticket = -1;           // >= 0 while this worker holds an unfilled ticket
     int held[KVM_NCLASS] = {-1, -1, -1, -1};
+    int nfill = 0;             // slots filled so far (fill k goes to slot (k - 1) % KVM_NSLOT)
 
     int cont = -1;             // continuation ready to be staged
     bool stop = false;
@@ -264,17 +273,17 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         __syncwarp();
         if (lane == 0) slots[drain].state = 0;
         __syncwarp();
-        drain ^= 1; --inflight; progressed = true;
+        drain = (drain + 1) % KVM_NSLOT; --inflight; progressed = true;
       }
       // 2. stage the next task if a slot is free
-      if (!stop && inflight < 2) {
+      if (!stop && inflight < KVM_NSLOT) {
         int task = -1;
         unsigned depth = 0;                 // tasks queued when this one was popped (0 for a continuation)
         if (cont >= 0) { task = cont; cont = -1; }
         else {
           int tk = -1, hold = 0;
           unsigned dp = 0;
-          if (lane == 0) { tk = kvm_try_pop(S, held, inflight > 0 ? gridDim.x : 1u, dp); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
+          if (lane == 0) { tk = kvm_try_pop(S, held, inflight > 0 ? (unsigned)inflight * gridDim.x : 1u, dp); hold = (held[0] & held[1] & held[2] & held[3]) >= 0 ? 1 : ((held[0] >= 0) | (held[1] >= 0) | (held[2] >= 0) | (held[3] >= 0)); }
           task = __shfl_sync(0xffffffffu, tk, 0);
           ticket = __shfl_sync(0xffffffffu, hold, 0) ? 0 : -1;      // ticket >= 0 now only means: this worker holds a ticket (no continuation then)
           depth = __shfl_sync(0xffffffffu, dp, 0);
@@ -290,7 +299,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
           // claim word runs it; a ticket whose tile is already taken is dropped.
           int pair = -1;
           bool drop = false;
-          const int ax = __shfl_sync(0xffffffffu, w1, 4), aw = __shfl_sync(0xffffffffu, w1, 7);
+          const int ax = __shfl_sync(0xffffffffu, w1, 4), aw = __shfl_sync(0xffffffffu, w1, 7), opid = __shfl_sync(0xffffffffu, w0, 0);
           if (ax == 1 && aw > 0) {
             int v = 0;
             if (lane == 0) {
@@ -307,13 +316,17 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
             if (pair >= 0) atomicAdd(&S.exec_count[pair], 1);      // counted only: the claim word is what makes a stacked tile run once
           }
           KvmSlot& sl = slots[fill];
+          ++nfill;
+          if (lane == 0) { *(volatile int*)&sl.seq = 2 * nfill - 1; __threadfence_block(); }
+          __syncwarp();
           if (lane < 16) sl.desc[lane] = w0; else sl.args[lane - 16] = w0;
           if (lane < 4) sl.args[16 + lane] = w1; else if (lane < 8) ((int32_t*)&sl.aux)[lane - 4] = w1;
           if (lane == 31) { sl.task = task; sl.pair = pair; }
-          __threadfence();       // gpu scope: the predecessors' data must be visible to this CTA's compute group
+          if (lane == 30) sl.kind = (engine_on && pair < 0 && opid == 122 && ax == 1) ? 1 : 0;      // host-planned tensor-core tile: the engine warps run its mainloop
+          __threadfence();       // gpu scope: the predecessors' data must be visible to this CTA's compute group (and its engine warps)
           __syncwarp();
-          if (lane == 0) sl.state = 1;
-          fill ^= 1; ++inflight; progressed = true;
+          if (lane == 0) { *(volatile int*)&sl.seq = 2 * nfill; __threadfence_block(); sl.state = 1; }
+          fill = (fill + 1) % KVM_NSLOT; ++inflight; progressed = true;
         }
       }
       // 3. termination / failure / stall
@@ -335,13 +348,67 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
       } else polls = 0;
     }
     // tell the compute group to leave: it consumes slots in order, `fill` is the next one it looks at
-    if (lane == 0) { slots[fill].task = -1; __threadfence_block(); slots[fill].state = 1; }
+    if (lane == 0) {
+      KvmSlot& sl = slots[fill];
+      ++nfill;
+      *(volatile int*)&sl.seq = 2 * nfill - 1; __threadfence_block();
+      sl.task = -1; sl.kind = -1;
+      __threadfence_block();
+      *(volatile int*)&sl.seq = 2 * nfill; __threadfence_block();
+      sl.state = 1;
+    }
+  } else if (tid >= KVM_NT) {
+    // ---- engine warps: one thread issues the TMA loads, one the MMAs, of every tensor-core GEMM tile, in the order the slots are filled
+    if (engine_role && engine_on) {
+      const uint32_t ring0 = kvm_smem_addr(kvm_smem + used_hdr + KVM_TCE_STAGING);
+      kvm_tc_fence_after();
+      const uint32_t tmem = *(volatile uint32_t*)(ctl + KVM_CTL_TMEM);
+      const unsigned long long t_limit = t_begin + 2 * S.timeout_ns;
+      uint32_t it = 0, g = 0;
+      bool prev_tile = false;            // the task before this one is one of the engine's tiles (it only uses the staging area)
+      for (int k = 1;; ++k) {
+        KvmSlot& sl = slots[(k - 1) % KVM_NSLOT];
+        int sq;
+        unsigned polls = 0;
+        while ((sq = *(volatile int*)&sl.seq) < 2 * k) {
+          if ((++polls & 1023u) == 0 && kvm_globaltimer() > t_limit) { sq = -1; break; }
+        }
+        if (sq < 0) break;                                   // the scheduler always posts the leave message first
+        if (sq > 2 * k) { prev_tile = false; continue; }     // filled, run and recycled meanwhile: not a tile of ours (ours wait for us)
+        const int kind = *(volatile int*)&sl.kind;
+        int32_t a[12];
+#pragma unroll
+        for (int j = 6; j < 12; ++j) a[j] = *(volatile int32_t*)&sl.args[j];
+        int4 aux;
+        aux.x = 1; aux.y = *(volatile int*)&sl.aux.y; aux.z = *(volatile int*)&sl.aux.z; aux.w = 0;
+        __threadfence_block();
+        if (*(volatile int*)&sl.seq != 2 * k) { prev_tile = false; continue; }
+        if (kind < 0) break;
+        if (kind != 1) { prev_tile = false; continue; }
+        bool ok = true;
+        if (engine_role == 1) {
+          if (!prev_tile && k > 1) {
+            // whatever the compute group runs before this tile may use the whole scratch: wait until it has finished
+            KvmSlot& pv = slots[(k - 2) % KVM_NSLOT];
+            polls = 0;
+            while (*(volatile int*)&pv.seq == 2 * (k - 1) && *(volatile int*)&pv.state == 1) {
+              if ((++polls & 1023u) == 0 && (kvm_globaltimer() > t_limit || *(volatile int*)&S.err->code != 0)) { ok = false; break; }
+            }
+          }
+          if (ok) ok = kvm_tce_produce(ctl, ring0, S.tmaps, a, aux, it, S.err);
+        } else ok = kvm_tce_mma(ctl, ring0, tmem, a, it, g, S.err);
+        if (!ok) { if (*(volatile int*)&S.err->code == 0) kvm_dev_fail(S, KVM_ERR_TIMEOUT, sl.task, 3122, engine_role); break; }
+        ++g; prev_tile = true;
+      }
+    }
   } else {
     KvmCtx c;
     c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps;
     c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_EXEC_SMEM_HDR) : S.bufs;
-    const int used = KVM_EXEC_SMEM_HDR + (buf_cache ? cache_bytes : 0);
+    const int used = used_hdr;
     c.smem = kvm_smem + used; c.smem_bytes = (int)dyn - used;
+    c.engine = engine_on ? 1 : 0; c.gemm_seq = 0;
+    unsigned tiles = 0;
     int cur = 0;
     while (true) {
       KvmSlot& sl = slots[cur];
@@ -372,7 +439,10 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         }
       }
       const int op = sl.desc[0];
+      const bool tile = sl.kind == 1;
+      c.gemm_seq = tiles;
       if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
+      if (tile) ++tiles;
       // this task's generic-proxy writes (global results, shared scratch) ordered before any later TMA access to them
       asm volatile("fence.proxy.async;" ::: "memory");
       kvm_sync();                       // every thread's writes happen before thread 0's fence below (barrier, then a cumulative gpu-scope fence)
@@ -381,7 +451,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_exec_kernel(KvmDevState S)
         __threadfence();
         sl.state = 2;
       }
-      cur ^= 1;
+      cur = (cur + 1) % KVM_NSLOT;
     }
   }
   __syncthreads();

@@ -35,6 +35,7 @@ struct KvmDevState {
   int buf_cache;              // 1: copy the buffer table into shared memory at launch (off for graphs of streaming GEMVs, which want the space)
   int pair_depth;             // tiles are stacked only while at least this many tasks are queued (wide phases; narrow ones keep their parallelism)
   int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
+  int engine;                 // 1: the ready-queue kernel's engine warps run the mainloops of the tensor-core GEMM tiles (overlapped with the previous tile's epilogue)
 };
 #define KVM_REC_WORDS 48
 #define KVM_SUCC_BITS 27          // successor entry on the device: index | class << 27 | has-version-wait << 29
@@ -61,6 +62,6 @@ __device__ __forceinline__ int kvm_class_of(int priority) { return priority < 0 
 
 static __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* args, const int4& aux);
 
-#define KVM_EXEC_SMEM_HDR 1024     // slots + control words at the start of dynamic shared memory
+#define KVM_EXEC_SMEM_HDR 2048     // slots + control words at the start of dynamic shared memory
 #define KVM_BUFCACHE_BYTES 32768    // shared-memory copy of the buffer table (up to 1024 buffers), after the header
 

@@ -178,25 +178,21 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
 // ---- streamed split attention, consumer side ----------------------------------------------------------------------------------
 // Stage use `cit` holds the split's keys, `cit + 1` its values (the appended row left out).  Semantics as kvm_op_attn_decode_part
 // (runtime/ref_extra.py:421-498); the front warp has validated the geometry before it issued the copies.
-static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow,
+static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, bool qkn, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow,
                                           unsigned long long deadline) {
-  KvmBuf q, kc, vc, lens, part, kn, vn;
+  KvmBuf q, kc, vc, lens, part, kn, vn, gam{};
   bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, q) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, kc) && kvm_buf_local(c, lb, a, 2, KVM_M_FLT, vc) &&
             kvm_buf_local(c, lb, a, 3, KVM_M_I32, lens) && kvm_buf_local(c, lb, a, 4, KVM_M_F32, part) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, kn, true) &&
             kvm_buf_local(c, lb, a, 6, KVM_M_FLT, vn, true);
+  if (ok && qkn) ok = kvm_buf(c, a[18], KVM_M_F32, gam);
   const int b = a[7], kvh = a[8], s = a[9], S = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
   const float sc = kvm_bits_f32(a[15]), theta = kvm_bits_f32(a[16]);
-  const int G = H / Hkv, half = hd / 2;
-  if (ok) ok = kvm_mat_ok(c, q, b + 1, H * hd) && kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) && kvm_mat_ok(c, kn, b + 1, Hkv * hd) && kvm_mat_ok(c, vn, b + 1, Hkv * hd);
+  const int G = H / Hkv;
+  if (ok) ok = kvm_mat_ok(c, q, b + 1, H * hd) && kvm_mat_ok(c, part, (long long)(b + 1) * S * H, hd + 2) && kvm_mat_ok(c, kn, b + 1, Hkv * hd) && kvm_mat_ok(c, vn, b + 1, Hkv * hd) &&
+            kvm_mat_ok(c, gam, 2, hd);
   if (ok && ((fl & 1) && (!kn.p || !vn.p))) { c.fail(KVM_OPE_SHAPE, hd, fl); ok = false; }
-  const int p0 = ok ? ((const int*)lens.p)[b] : 0, n = p0 + 1, nk = max(j1 - j0, 0);
-  const size_t base = (size_t)(b * Hkv + kvh) * Tmax;
+  const int p0 = ok ? ((const int*)lens.p)[b] : 0, nk = max(j1 - j0, 0);
   unsigned char* sm = c.smem;
-  float* qs = (float*)(sm + KVM_AS_OFF_QS);
-  float* inv = (float*)(sm + KVM_AS_OFF_INV);
-  float* kns = (float*)(sm + KVM_AS_OFF_KNEW);
-  float* vns = (float*)(sm + KVM_AS_OFF_VNEW);
-  const bool appends = newrow >= 0;
   unsigned char* Ks = ring.base + (cit % KVM_ST_NSTAGE) * KVM_ST_STAGE;
   unsigned char* Vs = ring.base + ((cit + 1) % KVM_ST_NSTAGE) * KVM_ST_STAGE;
   auto wait_use = [&](unsigned it) {
@@ -208,38 +204,13 @@ static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, con
   kvm_sync();                                              // the previous task is done with the scratch
   bool waited = true;
   if (ok) {
-    auto prologue = [&]() {
-      if (fl & 1) {
-        for (int i = threadIdx.x; i < half; i += KVM_NT) inv[i] = kvm_rope_inv(theta, i, hd);
-        kvm_sync();
-      }
-      if (appends) {
-        for (int i = threadIdx.x; i < half; i += KVM_NT) {
-          float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-          const float x1 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i), x2 = kvm_ld(kn, (size_t)b * kn.ld + kvh * hd + i + half);
-          const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
-          kns[i] = y1; kns[i + half] = y2;
-          kvm_st(kc, (base + n - 1) * kc.ld + i, y1);
-          kvm_st(kc, (base + n - 1) * kc.ld + i + half, y2);
-        }
-        for (int cc = threadIdx.x; cc < hd; cc += KVM_NT) {
-          const float t = kvm_ld(vn, (size_t)b * vn.ld + kvh * hd + cc);
-          vns[cc] = t;
-          kvm_st(vc, (base + n - 1) * vc.ld + cc, t);
-        }
-      }
-      for (int e = threadIdx.x; e < G * half; e += KVM_NT) {
-        const int g = e / half, i = e % half, h = kvh * G + g;
-        float x1 = kvm_ld(q, (size_t)b * q.ld + h * hd + i), x2 = kvm_ld(q, (size_t)b * q.ld + h * hd + i + half);
-        if (fl & 1) {
-          float sn, co; sincosf(__fmul_rn((float)p0, inv[i]), &sn, &co);
-          const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
-          x1 = y1; x2 = y2;
-          if (fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
-        }
-        qs[g * hd + i] = x1; qs[g * hd + i + half] = x2;
-      }
-    };
+    KvmPartPro P;
+    P.q = q; P.kc = kc; P.vc = vc; P.kn = kn; P.vn = vn; P.gam = gam;
+    P.b = b; P.kvh = kvh; P.G = G; P.hd = hd; P.fl = fl; P.p0 = p0; P.base = (size_t)(b * Hkv + kvh) * Tmax; P.theta = theta; P.eps = qkn ? kvm_bits_f32(a[19]) : 0.0f;
+    P.appends = newrow >= 0;
+    P.qs = (float*)(sm + KVM_AS_OFF_QS); P.inv = (float*)(sm + KVM_AS_OFF_INV); P.kns = (float*)(sm + KVM_AS_OFF_KNEW); P.vns = (float*)(sm + KVM_AS_OFF_VNEW);
+    P.rsq = (float*)(sm + KVM_AS_OFF_ML);
+    auto prologue = [&]() { kvm_part_prologue(P); };
     float* pp = (float*)part.p;
     auto emit = [&](int g, int cc, float M, float Lsum, float A) {
       const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
@@ -277,7 +248,7 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
     if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
     if (((K * 2 + 127) & ~127) + 256 + ((n1 - n0 + 7) & ~7) * (KVM_ST_ARRIVALS / R) * 4 > scratch_bytes) return;
     sl.kind = 1; sl.R = R; sl.nchunks = (n1 - n0 + R - 1) / R;
-  } else if (op == 135) {
+  } else if (op == 135 || op == 300) {
     const int kci = a[1], vci = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], Sp = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
     if (kci < 0 || kci >= S.nbufs || vci < 0 || vci >= S.nbufs || li < 0 || li >= S.nbufs) return;
     if (b < 0 || Hkv <= 0 || H <= 0 || H % Hkv || kvh < 0 || kvh >= Hkv || s < 0 || Sp <= 0 || s >= Sp || Tmax <= 0 || !(fl == 0 || fl == 1 || fl == 3)) return;
@@ -378,7 +349,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
         if (lane == 31) sl.task = task;
         __syncwarp();
         if (use_ring) {                                      // table entries of the buffer arguments of a streaming op, lanes in parallel
-          const int op = sl.desc[0], nb = op == 134 ? 6 : op == 135 ? 7 : 0;
+          const int op = sl.desc[0], nb = op == 134 ? 6 : (op == 135 || op == 300) ? 7 : 0;
           if (lane < nb) {
             const int idx = sl.args[lane];
             KvmBuf e; e.p = nullptr; e.rows = e.cols = e.ld = 0; e.dtype = 0; e.reserved[0] = e.reserved[1] = 0;
@@ -463,7 +434,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
     sctl[2] = (int)pit;
   } else {
     KvmCtx c;
-    c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps; c.pair = -1;
+    c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps; c.pair = -1; c.engine = 0; c.gemm_seq = 0;
     c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_ST_HDR) : S.bufs;
     const int used = KVM_ST_HDR + (buf_cache ? cache_bytes : 0);
     c.smem = kvm_smem + used;
@@ -488,7 +459,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
       if (tid == 0 && S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
       const int op = sl.desc[0], kind = sl.kind, nch = sl.nchunks;
       if (kind == 1) kvm_gemv_ring(c, sl.args, sl.lb, ring, cit, sl.R, nch, deadline);
-      else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
+      else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, op == 300, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
       else if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       cit += (unsigned)nch;
       asm volatile("fence.proxy.async;" ::: "memory");

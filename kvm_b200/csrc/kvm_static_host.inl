@@ -18,7 +18,7 @@ static double kvm_static_cost(const KvmExec* h, const KvmTaskDesc& d, const int3
   switch (d.op_id) {
     case 0: return 0.2;
     case 134: return 1.5 + elems(a[6], a[7]) * a[8] * 2.0 / BPU;
-    case 135: { const double keys = a[10] > 0 ? (double)a[14] / a[10] : a[14]; return 3.0 + 2.0 * keys * a[13] * 2.0 / BPU; }
+    case 135: case 300: { const double keys = a[10] > 0 ? (double)a[14] / a[10] : a[14]; return 3.0 + 2.0 * keys * a[13] * 2.0 / BPU; }
     case 136: return 1.0;
     case 58: case 57: return 2.0 + elems(a[d.op_id == 58 ? 2 : 3], a[d.op_id == 58 ? 3 : 4]) * a[d.op_id == 58 ? 4 : 5] * 4.0 / BPU;
     case 122: { const double m = std::min(128, a[8] - a[6]), n = std::min(256, a[9] - a[7]); return 5.0 + 2.0 * m * n * a[10] / 8.0e6; }
@@ -62,7 +62,7 @@ static std::vector<char> kvm_written_buffers(const KvmExec* h) {
       bool read_only = false;
       switch (d.op_id) {
         case 134: read_only = j != 4; break;                          // x, x2, gamma, w, res
-        case 135: read_only = j != 4; break;                          // q, kc, vc, lens, knew, vnew (kc / vc: own appended row only)
+        case 135: case 300: read_only = j != 4; break;                // q, kc, vc, lens, knew, vnew, qk_gamma (kc / vc: own appended row only)
         case 136: read_only = j == 0; break;
         case 63: read_only = j != 2; break;
         case 58: read_only = j == 0; break;
@@ -180,11 +180,11 @@ static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, Kv
   // the task itself would read only if every task that may change the counter comes after the reader: for each written counter,
   // the readers that are direct predecessors of ALL its other users.
   std::vector<std::vector<int>> len_readers(nb), len_users(nb);
-  for (int t = 0; t < nt; ++t) if (h->tasks[t].op_id == 135) { const int L = h->args[h->tasks[t].args_off + 3]; if (L >= 0 && L < nb && written[L]) len_readers[L].push_back(t); }
+  for (int t = 0; t < nt; ++t) if (h->tasks[t].op_id == 135 || h->tasks[t].op_id == 300) { const int L = h->args[h->tasks[t].args_off + 3]; if (L >= 0 && L < nb && written[L]) len_readers[L].push_back(t); }
   for (int u = 0; u < nt; ++u) {
     const KvmTaskDesc& du = h->tasks[u];
     const KvmOpInfo* op = kvm_find_op(du.op_id);
-    if (!op || du.op_id == 134 || du.op_id == 135) continue;
+    if (!op || du.op_id == 134 || du.op_id == 135 || du.op_id == 300) continue;
     const int32_t* au = h->args.data() + du.args_off;
     for (int j = 0; j < op->arity; ++j) if (op->types[j] >= 2 && au[j] >= 0 && au[j] < nb && !len_readers[au[j]].empty()) { len_users[au[j]].push_back(u); break; }
   }
@@ -203,7 +203,7 @@ static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, Kv
       const int K = a[8];
       if (K <= 0 || (K & 255) || K * 2 > KVM_ST_STAGE) all_fit = false;       // such a row does not stream through a stage: run the whole program without the ring
       if (a[3] >= 0 && a[3] < nb && !written[a[3]]) plan.stream[t] = 1;
-    } else if (d.op_id == 135) {
+    } else if (d.op_id == 135 || d.op_id == 300) {
       if (a[1] >= 0 && a[2] >= 0 && a[3] >= 0 && a[1] < nb && a[2] < nb && a[3] < nb && !written[a[1]] && !written[a[2]] && len_ok[t]) plan.stream[t] = 1;
     }
   }

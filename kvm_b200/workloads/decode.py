@@ -7,7 +7,8 @@ gemv with the SwiGLU prologue (pro 2) and the residual.  Then final norm folded 
 bookkeeping for the next token (token -> gather_rows of the embedding, lens += 1).  Re-arming the one-token template generates
 the next token.  Op semantics: include/mvm_ops_extra.def:79-95 of the reference.  Weights are bf16 [N, K] serving copies
 (`serve.py:317-344`), here seeded in place; the KV cache is prefilled with seeded values standing in for a prompt of `ctx` tokens.
-QK RMSNorm (Qwen3) is not part of the reference op set and is left out.
+QK RMSNorm (Qwen3) is not part of the reference op set: `qk_norm=True` uses this executor's extension op attn_decode_part_qkn
+(id 300, include/kvm_ops.def), which is attn_decode_part with the per-head normalisation in front of the rotary embedding.
 """
 from __future__ import annotations
 
@@ -41,6 +42,7 @@ class DecodeConfig:
     workers: int = 148
     join_threshold: int = 24  # fan-ins wider than this go through a join no-op (fewer edges, one more hop)
     lockstep: bool = False    # several users: keep them in step phase by phase (see build_decode); measured slower, kept for experiments
+    qk_norm: bool = False     # Qwen3: RMSNorm of every query head and of the new key over the head dimension before RoPE (extension op attn_decode_part_qkn)
 
 
 PRESETS = {
@@ -140,6 +142,10 @@ def build_decode(c: DecodeConfig) -> Graph:
         part = [g.buffer(TL[u] + 'part', S * H, hd + 2) for u in U]
         o = [g.buffer(TL[u] + 'o', 1, H * hd) for u in U]
         slice_ = c.tmax // S
+        qkn = None
+        if c.qk_norm:        # per-layer weights of the two norms, rows (query, key), around one
+            rng = np.random.default_rng(zlib.crc32(f'{c.seed}/{p}qkn'.encode()))
+            qkn = g.data('w.' + p + 'qkn', (1.0 + 0.25 * rng.uniform(-1, 1, (2, hd))).astype(np.float32))
         for u in U:
             for kvh in range(Hkv):
                 # Only the split that holds the newest key appends (one cache row); which one depends on the length at run time.
@@ -147,9 +153,12 @@ def build_decode(c: DecodeConfig) -> Graph:
                 # written (ordering against the next step comes through `lens`), and the S splits run concurrently.
                 for s in range(S):
                     rows = (kvh * c.tmax + s * slice_, kvh * c.tmax + (s + 1) * slice_)
-                    g.task('attn_decode_part', {'q': q[u], 'kc': kc[u], 'vc': vc[u], 'lens': lens[u], 'part': part[u], 'knew': k[u], 'vnew': v[u], 'b': 0, 'kvh': kvh, 's': s,
-                                                'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3},
-                           [q[u], k[u], v[u], lens[u]], [(kc[u], rows), (vc[u], rows), (part[u], (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{TL[u]}part.{kvh}.{s}')
+                    args = {'q': q[u], 'kc': kc[u], 'vc': vc[u], 'lens': lens[u], 'part': part[u], 'knew': k[u], 'vnew': v[u], 'b': 0, 'kvh': kvh, 's': s,
+                            'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3}
+                    if qkn:
+                        args.update(qk_gamma=qkn, eps=c.eps)
+                    g.task('attn_decode_part_qkn' if qkn else 'attn_decode_part', args,
+                           [q[u], k[u], v[u], lens[u], qkn], [(kc[u], rows), (vc[u], rows), (part[u], (s * H + kvh * G, s * H + (kvh + 1) * G))], prio, f'{TL[u]}part.{kvh}.{s}')
         for u in U:
             for kvh in range(Hkv):                              # one merge per GQA group: short tasks, all concurrent
                 g.task('attn_decode_merge', {'part': part[u], 'o': o[u], 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': H, 'hd': hd},

@@ -595,6 +595,33 @@ def attn_decode_part(b, a, **kw):
         part.a[row, hd], part.a[row, hd + 1] = f32(m), f32(p.sum())
 
 
+def _rms_head(x, gamma, eps):
+    """RMSNorm of one head vector, reference norm rounding (runtime/ref_gpt.py:107-173): statistics in double, rstd rounded to
+    float32, out = f32(x * rs * gamma)."""
+    ss = (x.astype(f64) ** 2).sum() / x.size
+    rs = f32(1.0 / math.sqrt(ss + f64(f32(eps))))
+    return (x.astype(f64) * f64(rs) * gamma.astype(f64)).astype(np.float32)
+
+
+def attn_decode_part_qkn(b, a, **kw):
+    """attn_decode_part with QK RMSNorm before the rotary embedding (an extension op, id 300): q heads and the appended key are
+    normalised over the head dimension and scaled by qk_gamma rows 0 / 1; then exactly attn_decode_part on the normalised values."""
+    bb, kvh, H, Hkv, hd = a['b'], a['kvh'], a['H'], a['Hkv'], a['hd']
+    gam = b['qk_gamma']
+    _need(gam.rows >= 2 and gam.cols >= hd, 'attn_decode_part_qkn: qk_gamma must be [2, hd]')
+    G = H // Hkv
+    q2 = Buf(b['q'].a.copy(), b['q'].dtype)
+    for g in range(G):
+        h = kvh * G + g
+        q2.a[bb, h * hd:(h + 1) * hd] = _rms_head(b['q'].a[bb, h * hd:(h + 1) * hd], gam.a[0, :hd], a['eps'])
+    b2 = dict(b, q=q2)
+    if b.get('knew') is not None:
+        k2 = Buf(b['knew'].a.copy(), b['knew'].dtype)
+        k2.a[bb, kvh * hd:(kvh + 1) * hd] = _rms_head(b['knew'].a[bb, kvh * hd:(kvh + 1) * hd], gam.a[1, :hd], a['eps'])
+        b2['knew'] = k2
+    attn_decode_part(b2, a, **kw)
+
+
 def attn_decode_merge(b, a, **kw):
     part, o = b['part'], b['o']
     bb, S, H, hd = a['b'], a['S'], a['H'], a['hd']

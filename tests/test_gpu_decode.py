@@ -127,3 +127,53 @@ def test_greedy_decode_32_tokens_identical(kvm_lib):
         assert (execs == 1).all() and np.array_equal(observed, b.tasks['indegree'])
     assert got == ref
     assert len({tuple(x) for x in ref}) > 1, 'degenerate test: the model emits one token pair only'
+
+
+# ---- QK RMSNorm extension (attn_decode_part_qkn, op 300) ------------------------------------------------------------------------------
+@pytest.mark.parametrize('flags, dt', [(3, 'bf16'), (1, 'f32'), (0, 'bf16')])
+def test_decode_part_with_qk_norm(kvm_lib, flags, dt):
+    """The extension op against its oracle function: per-head RMSNorm of the queries and of the appended key before the rotary
+    embedding, everything else as attn_decode_part (which the same fixtures pin to the reference)."""
+    B, H, Hkv, hd, Tmax, S = 2, 8, 2, 128, 200, 3
+    lens = np.array([[100], [0]], np.int32)
+    kc, vc = _cache(B, Hkv, Tmax, hd, dt)
+    g = Graph('dec')
+    g.data('q', 3.0 * f(B, H * hd)), g.data('kc', kc, dt), g.data('vc', vc, dt), g.data('lens', lens, 'i32'), g.data('knew', 0.3 * f(B, Hkv * hd)), g.data('vnew', f(B, Hkv * hd))
+    g.data('gam', 1.0 + 0.25 * f(2, hd))
+    g.buffer('part', B * S * H, hd + 2), g.buffer('o', B, H * hd, 'bf16')
+    for b in range(B):
+        ps = []
+        for kvh in range(Hkv):
+            for s in range(S):
+                base = (b * Hkv + kvh) * Tmax
+                ps.append(g.task('attn_decode_part_qkn', {'q': 'q', 'kc': 'kc', 'vc': 'vc', 'lens': 'lens', 'part': 'part', 'knew': 'knew' if flags else None,
+                                                          'vnew': 'vnew' if flags else None, 'b': b, 'kvh': kvh, 's': s, 'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd, 'Tmax': Tmax,
+                                                          'scale': hd ** -0.5, 'theta': 1e6, 'flags': flags, 'qk_gamma': 'gam', 'eps': 1e-6},
+                                 ['q', 'lens', 'knew', 'vnew', 'gam'], [('kc', (base, base + Tmax)), ('vc', (base, base + Tmax))]))
+        g.task('attn_decode_merge', {'part': 'part', 'o': 'o', 'b': b, 'h0': 0, 'h1': H, 'S': S, 'H': H, 'hd': hd}, [], [('o', (b, b + 1))], after=ps)
+    ex, vm, res = run_both(g.to_bundle())
+    compare(ex, vm, 6e-3)
+    ex.close()
+
+
+def test_greedy_decode_with_qk_norm_both_paths(kvm_lib):
+    """16 greedy tokens of the tiny decoder with QK norm: the static path (stream ring) and the ready queue both equal the oracle."""
+    from kvm_b200.executor import CFG_DYNAMIC, Executor
+    from kvm_b200.workloads.decode import build_decode, preset
+    from oracle.vm_np import VM
+    b = build_decode(preset('decode_tiny', init_std=0.08, qk_norm=True)).to_bundle()
+    assert 300 in b.tasks['op_id']
+    vm, ref = VM(b), []
+    for s in range(16):
+        vm.run()
+        ref.append(int(vm.buffer('u0.tok').a[0, 0]))
+        vm = VM(b, buffers=vm.bufs)
+    for flags in (0, CFG_DYNAMIC):
+        with Executor(flags=flags) as ex:
+            ex.load(b)
+            got = []
+            for s in range(16):
+                assert ex.run().done == len(b.tasks)
+                got.append(int(ex.read_buffer('u0.tok')[0, 0]))
+            assert ex.plan_info()[0] == (flags == 0)
+        assert got == ref, (flags, got, ref)
