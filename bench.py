@@ -331,6 +331,10 @@ def run_ours(args, rank, world, local_rank):
                 line['small_models'] = run_small(local_rank)
             except Exception as e:
                 line['small_models'] = {'error': str(e)[:300]}
+            try:
+                line['gpt_355m'] = run_355m(local_rank)
+            except Exception as e:
+                line['gpt_355m'] = {'error': str(e)[:300]}
         if cpu:
             line['cpu_baseline'] = {'value': cpu['steps_per_s'], 'unit': 'steps/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
                                     'sample': f"{cpu['tasks']} of {cpu['of_tasks']} tasks of one step, a few of each of its {cpu['kinds']} op kinds, {cpu['seconds']:.1f} s on the numpy oracle; step time = sum over kinds of count x mean task time"}
@@ -724,26 +728,48 @@ def run_alone_more(device, pk):
 
 
 def run_small(device):
-    """The two small configurations of the reference's benchmark list through the generic per-op path: the tiny GPT (2 layers,
-    d 128, batch 8 x 64, f32, AdamW, 20 steps unrolled in one launch) and eight MLPs of different widths trained side by side
-    (batch 256, f32, SGD with momentum, 10 steps in one launch).  Both are latency-bound here (no fused small-model step)."""
-    from kvm_b200.executor import Executor
+    """The two small configurations of the reference's benchmark list: the tiny GPT (2 layers, d 128, batch 8 x 64, f32, AdamW,
+    20 steps unrolled in one launch) and eight MLPs of different widths trained side by side (batch 256, f32, SGD with momentum,
+    10 steps in one launch), each on the ready-queue path and on the static-schedule path (per-worker task lists planned on the
+    host: a dependent hop is one progress-word poll instead of a trip through the queue)."""
+    from kvm_b200.executor import CFG_DYNAMIC, CFG_STATIC, Executor
     from kvm_b200.workloads.gpt import build_training, preset as gpt_preset
     from kvm_b200.workloads.mlp import build_mlps, params, preset as mlp_preset
     out = {}
     b = build_training(gpt_preset('gpt_tiny'), 20, stream_steps=80).to_bundle(check=False)
-    with Executor(device=device) as ex:
-        ex.load(b); ex.run()
-        ms = min(ex.run().ms for _ in range(2))
-        out['gpt_tiny'] = {'steps_per_s': 20 / (ms * 1e-3), 'us_per_step': ms * 1e3 / 20, 'tasks_per_step': len(b.tasks) // 20, 'loss_step0': float(ex.read_buffer('loss.0')[0, 0]),
-                           'loss_step19': float(ex.read_buffer('loss.19')[0, 0])}
     c = mlp_preset('mlp8')
-    b = build_mlps(c, 10).to_bundle(check=False)
-    with Executor(device=device) as ex:
-        ex.load(b); ex.run()
-        ms = min(ex.run().ms for _ in range(2))
-        out['mlp8'] = {'us_per_joint_step': ms * 1e3 / 10, 'tasks_per_step': len(b.tasks) // 10, 'params': params(c), 'gflop_per_step': 6.0 * params(c) * c.batch / 1e9}
+    bm = build_mlps(c, 10).to_bundle(check=False)
+    for tag, flags in (('queue', CFG_DYNAMIC), ('static', CFG_STATIC)):
+        with Executor(device=device, flags=flags) as ex:
+            ex.load(b); ex.run()
+            ms = min(ex.run().ms for _ in range(2))
+            out.setdefault('gpt_tiny', {'tasks_per_step': len(b.tasks) // 20})[tag] = {
+                'steps_per_s': 20 / (ms * 1e-3), 'us_per_step': ms * 1e3 / 20, 'loss_step0': float(ex.read_buffer('loss.0')[0, 0]), 'loss_step19': float(ex.read_buffer('loss.19')[0, 0])}
+        with Executor(device=device, flags=flags) as ex:
+            ex.load(bm); ex.run()
+            ms = min(ex.run().ms for _ in range(2))
+            out.setdefault('mlp8', {'tasks_per_step': len(bm.tasks) // 10, 'params': params(c), 'gflop_per_step': 6.0 * params(c) * c.batch / 1e9})[tag] = {'us_per_joint_step': ms * 1e3 / 10}
     return out
+
+
+def run_355m(device, steps=3):
+    """BASELINE configs[3], bf16 run: GPT-355M (24 layers, d 1024, 16 heads, FFN 4096, vocabulary 50304, T 1024), micro-batch 8, one
+    persistent-kernel launch per step; a few steps, reported beside the headline with its own roofline fraction."""
+    from kvm_b200.executor import Executor
+    cfg, bundle = get_bundle('gpt_355m', 0, 1, 2 * steps + 6, {})
+    with Executor(device=device) as ex:
+        ex.load(bundle)
+        ex.run_steps(2)
+        res = ex.run_steps(steps)
+        loss = float(ex.read_buffer('loss.0')[0, 0])
+        tc = ex.tc_task_count()
+    g, a = algorithmic_flops(cfg)
+    pk, kind = peaks()
+    peak = pk.get('bf16_tflops_sustained', PEAK_FALLBACK['bf16_tflops_sustained'])
+    ms = res.ms / steps
+    return {'workload': workload_name('gpt_355m', cfg), 'ms_per_step': ms, 'steps_per_s': 1e3 / ms, 'tasks': len(bundle.tasks), 'tc_tasks': tc, 'loss': loss,
+            'roofline': {'bound': 'tensor', 'achieved': (g + a) / (ms * 1e-3) / 1e12, 'unit': 'TFLOP/s', 'peak': peak, 'frac': (g + a) / (ms * 1e-3) / 1e12 / peak,
+                         'flops_per_launch': g + a, 'peak_source': f'{kind} bf16_tflops_sustained'}}
 
 
 def main():

@@ -72,6 +72,7 @@ static __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* a, c
     case 135: kvm_op_attn_decode_part(c, a); break;
     case 136: kvm_op_attn_decode_merge(c, a); break;
     case 300: kvm_op_attn_decode_part_qkn(c, a); break;
+    case 301: kvm_op_gemv_bf16_rows(c, a); break;
     default: c.fail(KVM_ERR_BAD_OP, op); break;
   }
 }

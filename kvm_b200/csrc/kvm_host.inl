@@ -12,7 +12,7 @@ struct KvmOwned { void* p; size_t bytes; };
 struct KvmStaticPlan {
   std::vector<int> prog, prog_off, waits;
   std::vector<int> wait_off, wait_cnt, stream;      // per task
-  bool ring = false;                                // the program streams (decode GEMVs / split attention): launch with the stage ring
+  int ring = 0;                                     // 0 no stream ring; 1 three stages (decode programs); 2 two stages and a large scratch (programs with gemv_bf16_rows)
   double makespan_us = 0.0;                         // the planner's estimate of one run
 };
 
@@ -466,7 +466,7 @@ static KvmStaticState kvm_static_state(KvmExec* h) {
   KvmStaticState T{};
   T.D = kvm_dev_state(h);
   T.prog = h->d_prog; T.prog_off = h->d_prog_off; T.waits = h->d_waits; T.progress = h->d_progress;
-  T.ring = h->splan.ring ? 1 : 0;
+  T.ring = h->splan.ring;
   return T;
 }
 
@@ -524,7 +524,7 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     if (!h->args.empty()) KVM_CUDA(cudaMemcpyAsync(h->d_args, h->args.data(), h->args.size() * 4, cudaMemcpyHostToDevice, h->stream));
     KVM_CUDA(cudaMemcpyAsync(h->d_aux, h->aux.data(), nt * sizeof(int4), cudaMemcpyHostToDevice, h->stream));
     h->has_gemv = false;
-    for (const KvmTaskDesc& d : h->tasks) if (d.op_id == 134) h->has_gemv = true;
+    for (const KvmTaskDesc& d : h->tasks) if (d.op_id == 134 || d.op_id == 301) h->has_gemv = true;
     h->use_static = false;
     if (kvm_wants_static(h, h->has_gemv)) {
       std::vector<int> base(h->nvars, 0);
@@ -683,7 +683,17 @@ extern "C" int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32
   cudaSetDevice(h->device);
   if (start_ns) KVM_CUDA(cudaMemcpy(start_ns, h->d_tstart, (size_t)n * 8, cudaMemcpyDeviceToHost));
   if (end_ns) KVM_CUDA(cudaMemcpy(end_ns, h->d_tend, (size_t)n * 8, cudaMemcpyDeviceToHost));
-  if (smid) KVM_CUDA(cudaMemcpy(smid, h->d_tsmid, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  if (smid) {
+    KVM_CUDA(cudaMemcpy(smid, h->d_tsmid, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; ++i) smid[i] &= 0xff;
+  }
+  return 0;
+}
+extern "C" int kvm_trace_detail(KvmExec* h, int32_t* detail, int32_t n) {
+  if (!h || !h->cfg.trace || !detail || n < 0 || n > (int)h->tasks.size() || !h->d_tstart) { if (h) h->error = "kvm_trace_detail: tracing is off or no run yet"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaMemcpy(detail, h->d_tsmid, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  for (int i = 0; i < n; ++i) detail[i] = (int32_t)((uint32_t)detail[i] >> 8);
   return 0;
 }
 extern "C" int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes) {

@@ -338,15 +338,9 @@ static __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* 
 // out[0,n] = sum_k v[k] w[n,k] (+ res[0,n]), v = bf16(prologue(x)); w bf16 [>=n1, K], rows contiguous in K.
 // The activation row is staged once per task in shared memory (as float); each warp then streams four weight rows at a
 // time with 16-byte loads, two k-steps in flight, float32 accumulation in a fixed order, warp-shuffle reduction.
-static __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
-  KvmBuf x, x2, gm, w, out, res;
-  if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, x2, true) || !kvm_buf(c, a[2], KVM_M_F32, gm, true) || !kvm_buf(c, a[3], KVM_M_BF16, w) ||
-      !kvm_buf(c, a[4], KVM_M_FLT, out) || !kvm_buf(c, a[5], KVM_M_FLT, res, true)) return;
-  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
-  const float eps = kvm_bits_f32(a[10]);
-  if (n0 < 0 || n1 <= n0 || K <= 0 || (K & 7) || pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || (w.ld & 7) || !kvm_vec_ok(w) ||
-      K * 4 + 256 > c.smem_bytes) { c.fail(KVM_OPE_SHAPE, K, pro); return; }
-  if (!kvm_mat_ok(c, w, n1, K) || !kvm_mat_ok(c, x, 1, K) || !kvm_mat_ok(c, x2, 1, K) || !kvm_flat_ok(c, gm, K) || !kvm_mat_ok(c, out, 1, n1) || !kvm_mat_ok(c, res, 1, n1)) return;
+// One activation row: x / x2 / out / res are one-row views (row 0 of what they point to).
+static __device__ void kvm_gemv_row(const KvmCtx& c, const KvmBuf& x, const KvmBuf& x2, const KvmBuf& gm, const KvmBuf& w, const KvmBuf& out, const KvmBuf& res, int n0, int n1, int K,
+                                    int pro, float eps) {
   if (kvm_gemv_stream(c, x, x2, gm, w, out, res, n0, n1, K, pro, eps)) return;      // bulk-copy ring; the form below serves what does not fit
   float* vs = (float*)c.smem;
   float* red = vs + K;
@@ -413,6 +407,30 @@ static __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) {
     kvm_st(out, n, res.p ? __fadd_rn(sum, kvm_ld(res, n)) : sum);
   }
 }
+
+__device__ __forceinline__ KvmBuf kvm_row_view(const KvmBuf& b, int r) {
+  KvmBuf v = b;
+  if (b.p) { v.p = (char*)b.p + (size_t)r * b.ld * (b.dtype == KVM_BF16 ? 2 : 4); v.rows = 1; }
+  return v;
+}
+// gemv_bf16 (134): row 0.  gemv_bf16_rows (301, an extension): rows r0..r1 of x / x2 / out / res, one after the other here (the
+// static path's ring form reads the weights once for all rows; this form serves the ready queue and shapes the ring cannot take).
+static __device__ void kvm_gemv_op(const KvmCtx& c, const int32_t* a, int r0, int r1) {
+  KvmBuf x, x2, gm, w, out, res;
+  if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, x2, true) || !kvm_buf(c, a[2], KVM_M_F32, gm, true) || !kvm_buf(c, a[3], KVM_M_BF16, w) ||
+      !kvm_buf(c, a[4], KVM_M_FLT, out) || !kvm_buf(c, a[5], KVM_M_FLT, res, true)) return;
+  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
+  const float eps = kvm_bits_f32(a[10]);
+  if (n0 < 0 || n1 <= n0 || K <= 0 || (K & 7) || pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || (w.ld & 7) || !kvm_vec_ok(w) ||
+      K * 4 + 256 > c.smem_bytes || r0 < 0 || r1 <= r0) { c.fail(KVM_OPE_SHAPE, K, pro); return; }
+  if (!kvm_mat_ok(c, w, n1, K) || !kvm_mat_ok(c, x, r1, K) || !kvm_mat_ok(c, x2, r1, K) || !kvm_flat_ok(c, gm, K) || !kvm_mat_ok(c, out, r1, n1) || !kvm_mat_ok(c, res, r1, n1)) return;
+  for (int r = r0; r < r1; ++r) {
+    if (r > r0) kvm_sync();
+    kvm_gemv_row(c, kvm_row_view(x, r), kvm_row_view(x2, r), gm, w, kvm_row_view(out, r), kvm_row_view(res, r), n0, n1, K, pro, eps);
+  }
+}
+static __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, 0, 1); }
+static __device__ void kvm_op_gemv_bf16_rows(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, a[11], a[12]); }
 
 // ---- sampling: Philox-4x32-10 counter (row, ctr, 0, 0), key (seed, 0x9E3779B9) (runtime/ref_gpt.py:488-506) --------------------------
 __device__ __forceinline__ float kvm_philox_uniform(unsigned seed, unsigned ctr, unsigned row) {

@@ -16,7 +16,7 @@
 #pragma once
 #include "kvm_state.cuh"
 
-#define KVM_NSLOT 4               // tasks a worker holds at most: one running and up to three staged behind it
+#define KVM_NSLOT 2               // tasks a worker holds at most: one running and one staged behind it (more slots let a worker hoard ready tasks while others idle)
 struct KvmSlot {
   int task;                   // -1 = leave
   int state;                  // 0 free, 1 full, 2 finished (awaiting release)

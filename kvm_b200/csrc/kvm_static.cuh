@@ -21,8 +21,8 @@
 
 #define KVM_ST_SLOTS 4                 // record ring depth (tasks fetched ahead)
 #define KVM_ST_HDR 3072                // header bytes: slots, control words, barriers
-#define KVM_ST_RING (KVM_ST_NSTAGE * KVM_ST_STAGE)
-#define KVM_ST_ARRIVALS 8              // consumer arrivals that free a stage
+#define KVM_ST_MMA_WARPS 8             // warps of the rows consumer that multiply (each a slice of the chunk's k)
+#define KVM_ST_ARRIVALS 16             // arrivals that free a stage: every compute warp, once it is done with the stage (or has nothing to do with it)
 
 struct KvmStSlot {
   int task;
@@ -51,10 +51,13 @@ struct KvmRing {
   uint32_t bar0;              // full[s] at bar0 + 8 s, empty[s] at bar0 + 64 + 8 s
   unsigned char* base;        // stage s at base + s * KVM_ST_STAGE
   uint32_t base_addr;
+  unsigned ns;                // stages: 3 (32 KB of op scratch beside them) or, for programs with gemv_bf16_rows, 2 (96 KB of scratch: the activations of eight rows)
 };
-__device__ __forceinline__ uint32_t kvm_ring_full(const KvmRing& r, unsigned it) { return r.bar0 + 8 * (it % KVM_ST_NSTAGE); }
-__device__ __forceinline__ uint32_t kvm_ring_empty(const KvmRing& r, unsigned it) { return r.bar0 + 64 + 8 * (it % KVM_ST_NSTAGE); }
-__device__ __forceinline__ uint32_t kvm_ring_parity(unsigned it) { return (it / KVM_ST_NSTAGE) & 1u; }
+__device__ __forceinline__ unsigned kvm_ring_slot(const KvmRing& r, unsigned it) { return r.ns == 2 ? (it & 1u) : it % 3u; }
+__device__ __forceinline__ uint32_t kvm_ring_full(const KvmRing& r, unsigned it) { return r.bar0 + 8 * kvm_ring_slot(r, it); }
+__device__ __forceinline__ uint32_t kvm_ring_empty(const KvmRing& r, unsigned it) { return r.bar0 + 64 + 8 * kvm_ring_slot(r, it); }
+__device__ __forceinline__ uint32_t kvm_ring_parity(const KvmRing& r, unsigned it) { return (r.ns == 2 ? (it >> 1) : it / 3u) & 1u; }
+__device__ __forceinline__ unsigned char* kvm_ring_stage(const KvmRing& r, unsigned it) { return r.base + kvm_ring_slot(r, it) * KVM_ST_STAGE; }
 
 // Buffer argument j of a streamed task from the slot's own copy of the table entries (same checks as kvm_buf).
 __device__ __forceinline__ bool kvm_buf_local(const KvmCtx& c, const KvmBuf* lb, const int32_t* a, int j, int mask, KvmBuf& out, bool optional = false) {
@@ -71,11 +74,26 @@ __device__ __forceinline__ int kvm_ld_relaxed(const int* p) {
   return v;
 }
 
+// Wait for stage use `it` to land: lane 0 polls (bounded by the launch deadline and by an error recorded elsewhere), the verdict
+// is the same for the whole warp.  All 32 lanes must call it.
+__device__ __forceinline__ bool kvm_ring_wait_warp(const KvmRing& ring, unsigned it, unsigned long long deadline, const KvmErrRec* err) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(ring, it);
+    unsigned spins = 0;
+    while (!kvm_mbar_test(bar, par)) {
+      if ((++spins & 1023u) == 0 && (kvm_globaltimer() > deadline || *(volatile const int*)&err->code != 0)) { ok = 0; break; }      // an error elsewhere: the copies may never come
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---- streamed GEMV, consumer side --------------------------------------------------------------------------------------------
-// Stage use `cit + ci` holds rows n0 + ci*R .. of the weight matrix in full (R*K*2 bytes).  Warps 0..7 consume: warp = (row r of the
+// Stage use `cit + ci` holds rows n0 + ci*R .. of the weight matrix in full (R*K*2 bytes).  All sixteen warps consume: warp = (row r of the
 // stage, part of K); the activation row v = bf16(prologue(x)) is staged once as bf16.  Partial sums are added in part order.
 // Semantics as kvm_op_gemv_bf16 (runtime/ref_extra.py:398-415).  Always consumes its nchunks stage uses, also after an error.
-static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline) {
+static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline,
+                                     unsigned long long t_task, int* stamp) {
   KvmBuf x, x2, gm, w, out, res;
   const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
   const float eps = kvm_bits_f32(a[10]);
@@ -132,24 +150,35 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
   }
   kvm_sync();
   bool waited = true;
-  if (warp < KVM_ST_ARRIVALS) {
+  unsigned long long t_pro = 0, t_wait = 0, t_first = 0;
+  if (stamp && tid == 0) t_pro = kvm_globaltimer();
+  {
     const int r = warp / KP, part = warp % KP;
     const int plen = (((K + KP - 1) / KP) + 255) & ~255, kb = part * plen, ke = min(K, kb + plen);
     for (int ci = 0; ci < NC; ++ci) {
       const unsigned it = cit + ci;
-      // bounded wait for the stage
-      {
-        const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
-        unsigned spins = 0;
-        while (!kvm_mbar_test(bar, par)) {
-          if ((++spins & 1023u) == 0 && (kvm_globaltimer() > deadline || *(volatile int*)&c.err->code != 0)) { waited = false; break; }      // an error elsewhere: the copies may never come
-        }
-      }
-      if (!waited) break;
+      unsigned long long tw = 0;
+      if (stamp && tid == 0) tw = kvm_globaltimer();
+      if (waited && !kvm_ring_wait_warp(ring, it, deadline, c.err)) waited = false;
+      if (stamp && tid == 0) { const unsigned long long d = kvm_globaltimer() - tw; t_wait += d; if (ci == 0) t_first = d; }
+      if (!waited) break;                                  // warp-uniform
       if (ok && r < R && ci * R + r < rows) {
-        const unsigned char* st = ring.base + (it % KVM_ST_NSTAGE) * KVM_ST_STAGE + (size_t)r * K * 2;
-        float acc0 = 0.0f, acc1 = 0.0f;
-        for (int k = kb + lane * 8; k < ke; k += 256) {
+        const unsigned char* st = kvm_ring_stage(ring, it) + (size_t)r * K * 2;
+        float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+        int k = kb + lane * 8;
+        for (; k + 256 < ke; k += 512) {                   // two 16-byte pieces of the row and of the activations in flight per trip
+          const uint4 wa = *(const uint4*)(st + k * 2), wb = *(const uint4*)(st + (k + 256) * 2);
+          const uint4 xa = *(const uint4*)(vs + k), xb = *(const uint4*)(vs + k + 256);
+          acc0 = fmaf(kvm_bf16lo(xa.x), kvm_bf16lo(wa.x), acc0); acc1 = fmaf(kvm_bf16hi(xa.x), kvm_bf16hi(wa.x), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.x), kvm_bf16lo(wb.x), acc2); acc3 = fmaf(kvm_bf16hi(xb.x), kvm_bf16hi(wb.x), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.y), kvm_bf16lo(wa.y), acc0); acc1 = fmaf(kvm_bf16hi(xa.y), kvm_bf16hi(wa.y), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.y), kvm_bf16lo(wb.y), acc2); acc3 = fmaf(kvm_bf16hi(xb.y), kvm_bf16hi(wb.y), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.z), kvm_bf16lo(wa.z), acc0); acc1 = fmaf(kvm_bf16hi(xa.z), kvm_bf16hi(wa.z), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.z), kvm_bf16lo(wb.z), acc2); acc3 = fmaf(kvm_bf16hi(xb.z), kvm_bf16hi(wb.z), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.w), kvm_bf16lo(wa.w), acc0); acc1 = fmaf(kvm_bf16hi(xa.w), kvm_bf16hi(wa.w), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.w), kvm_bf16lo(wb.w), acc2); acc3 = fmaf(kvm_bf16hi(xb.w), kvm_bf16hi(wb.w), acc3);
+        }
+        for (; k < ke; k += 256) {
           const uint4 wv = *(const uint4*)(st + k * 2);
           const uint4 xv = *(const uint4*)(vs + k);
           acc0 = fmaf(kvm_bf16lo(xv.x), kvm_bf16lo(wv.x), acc0); acc1 = fmaf(kvm_bf16hi(xv.x), kvm_bf16hi(wv.x), acc1);
@@ -157,7 +186,7 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
           acc0 = fmaf(kvm_bf16lo(xv.z), kvm_bf16lo(wv.z), acc0); acc1 = fmaf(kvm_bf16hi(xv.z), kvm_bf16hi(wv.z), acc1);
           acc0 = fmaf(kvm_bf16lo(xv.w), kvm_bf16lo(wv.w), acc0); acc1 = fmaf(kvm_bf16hi(xv.w), kvm_bf16hi(wv.w), acc1);
         }
-        const float sum = kvm_warp_sum(acc0 + acc1);
+        const float sum = kvm_warp_sum((acc0 + acc1) + (acc2 + acc3));
         if (lane == 0) parts[(ci * R + r) * KP + part] = sum;
       }
       __syncwarp();
@@ -165,13 +194,128 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
     }
   }
   __syncwarp();
+  if (stamp && tid == 0)        // trace detail: prologue | wait for the first stage (both in 0.1 us) | all waits for stages (0.2 us), one byte each
+    stamp[0] = (int)min(255ull, (t_pro - t_task) / 100) | ((int)min(255ull, t_first / 100) << 8) | ((int)min(255ull, t_wait / 200) << 16);
   if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1134);
   kvm_sync();
-  if (ok && waited)
+  if (ok && *(volatile int*)&c.err->code == 0)
     for (int i = tid; i < rows; i += KVM_NT) {
       float sum = 0.0f;
       for (int p = 0; p < KP; ++p) sum += parts[i * KP + p];
       kvm_st(out, n0 + i, res.p ? __fadd_rn(sum, kvm_ld(res, n0 + i)) : sum);
+    }
+}
+
+// ---- streamed GEMV for up to eight activation rows (gemv_bf16_rows), consumer side ------------------------------------------------------
+// Tensor cores: D[16 x 8] += A[16 x 16] B[16 x 8] (mma.sync m16n8k16, bf16 operands, float32 accumulate) with A = activations (rows =
+// activation rows, eight of the sixteen used), B = eight weight rows of a stage (columns).  A dot product does not care in which order
+// k is visited, so both operands are read 16 bytes per thread from row-major [row][k] arrays at the SAME k offsets (thread t of a
+// quad takes k = 8t .. 8t+7 of a 32-wide slice for two MMAs) instead of in the instruction's interleaved k layout.
+// Chunks arrive k-chunk outer, row group inner: per k-chunk the prologue'd activations of that k range are staged once (bf16,
+// padded rows), then every row group's stage is multiplied against them by the eight consumer warps (each a slice of the chunk's k);
+// accumulators of up to eight row groups stay in registers over the whole task; at the end the warps' partial sums are added in
+// warp order.  Semantics per row as gemv_bf16 (runtime/ref_extra.py:398-415).
+__device__ __forceinline__ void kvm_mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+static __device__ void kvm_gemv_rows_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int KC, unsigned long long deadline) {
+  KvmBuf x, x2, gm, w, out, res;
+  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9], r0 = a[11], r1 = a[12];
+  const float eps = kvm_bits_f32(a[10]);
+  bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, x) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, x2, true) && kvm_buf_local(c, lb, a, 2, KVM_M_F32, gm, true) &&
+            kvm_buf_local(c, lb, a, 3, KVM_M_BF16, w) && kvm_buf_local(c, lb, a, 4, KVM_M_FLT, out) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, res, true);
+  const int rows = n1 - n0, ng = (rows + 7) / 8, nkc = K / KC, M = r1 - r0;
+  if (ok && (pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p))) { c.fail(KVM_OPE_SHAPE, K, pro); ok = false; }
+  if (ok) ok = kvm_mat_ok(c, x, r1, K) && kvm_mat_ok(c, x2, r1, K) && kvm_flat_ok(c, gm, K) && kvm_mat_ok(c, out, r1, n1) && kvm_mat_ok(c, res, r1, n1);
+  const int pitch = KC * 2 + 16;                          // bytes per staged activation row: 16-byte accesses of the eight rows fall into different banks
+  unsigned char* xs = c.smem;                              // [8][pitch]
+  float* rsq = (float*)(c.smem + 8 * pitch);              // [8] reciprocal RMS per activation row, then [64] reduction scratch
+  float* parts = rsq + 128;                                // [8 warps][ng][8 activation rows][8 weight rows]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const bool vec_x = ok && (x.ld & 7) == 0 && kvm_vec_ok(x), vec_x2 = ok && x2.p && (x2.ld & 7) == 0 && kvm_vec_ok(x2), vec_g = ok && gm.p && kvm_vec_ok(gm);
+  kvm_sync();                                              // the previous task is done with the scratch
+  if (ok && pro == 1) {                                    // RMS statistics: two warps per activation row
+    const int u = warp >> 1, hf = warp & 1;
+    float q = 0.0f;
+    if (u < M) for (int k = hf * (K / 2) + lane; k < (hf + 1) * (K / 2); k += 32) { const float v = kvm_ld(x, (size_t)(r0 + u) * x.ld + k); q += v * v; }
+    q = kvm_warp_sum(q);
+    if (lane == 0) rsq[64 + warp] = q;
+    kvm_sync();
+    if (tid < 8) rsq[tid] = tid < M ? 1.0f / sqrtf((rsq[64 + 2 * tid] + rsq[64 + 2 * tid + 1]) / K + eps) : 0.0f;
+  }
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  bool waited = true;
+  const int kw = KC / KVM_ST_MMA_WARPS;                                   // k extent of one consumer warp inside a chunk (a multiple of 32)
+  for (int kc = 0; kc < nkc; ++kc) {
+    kvm_sync();                                            // statistics written; the consumers are done with the previous chunk's activations
+    if (ok) {
+      // stage v = bf16(pro(x)) of this k range for the M rows, zeros for the unused rows (all 16 warps)
+      for (int e = tid; e < 8 * (KC / 8); e += KVM_NT) {
+        const int u = e / (KC / 8), k0 = (e % (KC / 8)) * 8, k = kc * KC + k0;
+        uint4 pk = make_uint4(0, 0, 0, 0);
+        if (u < M) {
+          float v[8], v2[8];
+          if (vec_x) kvm_ld8(x, (size_t)(r0 + u) * x.ld + k, v);
+          else for (int j = 0; j < 8; ++j) v[j] = kvm_ld(x, (size_t)(r0 + u) * x.ld + k + j);
+          if (pro == 2) {
+            if (vec_x2) kvm_ld8(x2, (size_t)(r0 + u) * x2.ld + k, v2);
+            else for (int j = 0; j < 8; ++j) v2[j] = kvm_ld(x2, (size_t)(r0 + u) * x2.ld + k + j);
+          } else if (pro == 1) {
+            if (vec_g) { *(float4*)v2 = *(const float4*)((const float*)gm.p + k); *(float4*)(v2 + 4) = *(const float4*)((const float*)gm.p + k + 4); }
+            else for (int j = 0; j < 8; ++j) v2[j] = ((const float*)gm.p)[k + j];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = pro == 1 ? v[j] * rsq[u] * v2[j] : pro == 2 ? kvm_silu(v[j]) * v2[j] : v[j];
+          __nv_bfloat162* hh = (__nv_bfloat162*)&pk;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) hh[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        }
+        *(uint4*)(xs + (size_t)u * pitch + k0 * 2) = pk;
+      }
+    }
+    kvm_sync();
+    {
+#pragma unroll
+      for (int rg = 0; rg < 8; ++rg) {
+        if (rg >= ng) break;
+        const unsigned it = cit + (unsigned)(kc * ng + rg);
+        if (waited && !kvm_ring_wait_warp(ring, it, deadline, c.err)) waited = false;
+        if (!waited) break;                                // warp-uniform; the warp still takes part in every barrier below
+        if (ok && warp < KVM_ST_MMA_WARPS) {               // the other warps only release the stage once it has landed
+          const unsigned char* wrow = kvm_ring_stage(ring, it) + (size_t)g * KC * 2 + (size_t)(warp * kw + t * 8) * 2;
+          const unsigned char* xrow = xs + (size_t)g * pitch + (size_t)(warp * kw + t * 8) * 2;
+#pragma unroll 4
+          for (int kk = 0; kk < kw; kk += 32) {
+            const uint4 bv = *(const uint4*)(wrow + kk * 2);
+            const uint4 av = *(const uint4*)(xrow + kk * 2);
+            kvm_mma_bf16_16816(acc[rg], av.x, av.y, bv.x, bv.y);
+            kvm_mma_bf16_16816(acc[rg], av.z, av.w, bv.z, bv.w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) kvm_mbar_arrive(kvm_ring_empty(ring, it));
+      }
+    }
+  }
+  __syncwarp();
+  if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1301);
+  // partial sums of the eight consumer warps -> shared memory -> added in warp order; thread = (row group, activation row, weight row)
+  if (warp < KVM_ST_MMA_WARPS)
+#pragma unroll
+    for (int rg = 0; rg < 8; ++rg) if (rg < ng) *(float2*)(parts + (((size_t)warp * ng + rg) * 8 + g) * 8 + 2 * t) = make_float2(acc[rg][0], acc[rg][1]);
+  kvm_sync();
+  if (ok && *(volatile int*)&c.err->code == 0)            // a warp that gave up has recorded the timeout before the barrier
+    for (int e = tid; e < ng * 64; e += KVM_NT) {
+      const int rg = e >> 6, u = (e >> 3) & 7, nn = e & 7, n = n0 + rg * 8 + nn;
+      if (u >= M || n >= n1) continue;
+      float sum = 0.0f;
+#pragma unroll
+      for (int wv = 0; wv < KVM_ST_MMA_WARPS; ++wv) sum += parts[(((size_t)wv * ng + rg) * 8 + u) * 8 + nn];
+      const size_t o = (size_t)(r0 + u) * out.ld + n;
+      kvm_st(out, o, res.p ? __fadd_rn(sum, kvm_ld(res, (size_t)(r0 + u) * res.ld + n)) : sum);
     }
 }
 
@@ -193,10 +337,10 @@ static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, con
   if (ok && ((fl & 1) && (!kn.p || !vn.p))) { c.fail(KVM_OPE_SHAPE, hd, fl); ok = false; }
   const int p0 = ok ? ((const int*)lens.p)[b] : 0, nk = max(j1 - j0, 0);
   unsigned char* sm = c.smem;
-  unsigned char* Ks = ring.base + (cit % KVM_ST_NSTAGE) * KVM_ST_STAGE;
-  unsigned char* Vs = ring.base + ((cit + 1) % KVM_ST_NSTAGE) * KVM_ST_STAGE;
+  unsigned char* Ks = kvm_ring_stage(ring, cit);
+  unsigned char* Vs = kvm_ring_stage(ring, cit + 1);
   auto wait_use = [&](unsigned it) {
-    const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
+    const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(ring, it);
     unsigned spins = 0;
     while (!kvm_mbar_test(bar, par)) if ((++spins & 1023u) == 0 && (kvm_globaltimer() > deadline || *(volatile int*)&c.err->code != 0)) return false;
     return true;
@@ -229,7 +373,7 @@ static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, con
   if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1135);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the appended row was written by threads; the next copies into these stages come after it
   kvm_sync();
-  if (waited && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) < KVM_ST_ARRIVALS) { kvm_mbar_arrive(kvm_ring_empty(ring, cit)); kvm_mbar_arrive(kvm_ring_empty(ring, cit + 1)); }
+  if (waited && (threadIdx.x & 31) == 0) { kvm_mbar_arrive(kvm_ring_empty(ring, cit)); kvm_mbar_arrive(kvm_ring_empty(ring, cit + 1)); }
 }
 
 // ---- front warp: stream geometry of a fetched task (lane 0) ---------------------------------------------------------------------
@@ -248,6 +392,17 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
     if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
     if (((K * 2 + 127) & ~127) + 256 + ((n1 - n0 + 7) & ~7) * (KVM_ST_ARRIVALS / R) * 4 > scratch_bytes) return;
     sl.kind = 1; sl.R = R; sl.nchunks = (n1 - n0 + R - 1) / R;
+  } else if (op == 301) {
+    // gemv_bf16_rows: stages hold eight weight rows x KC columns; chunks run k-chunk outer, row group inner (the activations of the
+    // current k-chunk stay in the scratch while every row group passes over them)
+    const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8], r0 = a[11], r1 = a[12];
+    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || n1 - n0 > 64 || K <= 0 || (K & 255) || r0 < 0 || r1 <= r0 || r1 - r0 > 8) return;
+    const KvmBuf w = sl.lb[3];
+    if (!w.p || w.dtype != KVM_BF16 || (w.ld & 7) || ((uintptr_t)w.p & 15) || n1 > w.rows || K > w.cols) return;
+    int KC = K;
+    if (KC > 4096) { KC = 4096; while (K % KC) KC -= 256; }
+    if (8 * (KC * 2 + 16) + 8 * 8 * 8 * 8 * 4 + 1024 > scratch_bytes) return;      // activations of one k-chunk + the partial sums of up to eight row groups
+    sl.kind = 3; sl.R = KC; sl.nchunks = (K / KC) * ((n1 - n0 + 7) / 8);
   } else if (op == 135 || op == 300) {
     const int kci = a[1], vci = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], Sp = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
     if (kci < 0 || kci >= S.nbufs || vci < 0 || vci >= S.nbufs || li < 0 || li >= S.nbufs) return;
@@ -268,9 +423,17 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
 
 // Issue the copies of chunk `ci` of the task in `sl` as stage use `it` (front warp, lane 0; the stage is known to be free).
 static __device__ void kvm_static_issue(const KvmDevState& S, const KvmStSlot& sl, const KvmRing& ring, unsigned it, int ci) {
-  const uint32_t full = kvm_ring_full(ring, it), dst = ring.base_addr + (it % KVM_ST_NSTAGE) * KVM_ST_STAGE;
+  const uint32_t full = kvm_ring_full(ring, it), dst = ring.base_addr + kvm_ring_slot(ring, it) * KVM_ST_STAGE;
   const int32_t* a = sl.args;
-  if (sl.kind == 1) {
+  if (sl.kind == 3) {
+    const KvmBuf w = sl.lb[3];
+    const int n0 = a[6], n1 = a[7], K = a[8], KC = sl.R, ng = (n1 - n0 + 7) / 8;
+    const int kc = ci / ng, rg = ci % ng, r0 = n0 + rg * 8, nr = min(8, n1 - r0);
+    const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p + (size_t)kc * KC;
+    kvm_mbar_expect_tx(full, (uint32_t)(nr * KC * 2));
+    if (KC == K && w.ld == K) kvm_bulk_g2s(dst, wp + (size_t)r0 * w.ld, (uint32_t)(nr * K * 2), full);
+    else for (int r = 0; r < nr; ++r) kvm_bulk_g2s(dst + r * KC * 2, wp + (size_t)(r0 + r) * w.ld, (uint32_t)(KC * 2), full);
+  } else if (sl.kind == 1) {
     const KvmBuf w = sl.lb[3];
     const int n0 = a[6], n1 = a[7], K = a[8], R = sl.R;
     const int r0 = n0 + ci * R, nr = min(R, n1 - r0);
@@ -304,9 +467,11 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
   if (tid < KVM_ST_SLOTS) { slots[tid].state = 0; slots[tid].task = -1; }
   if (tid == 0) { sctl[0] = 0; sctl[1] = 0; }
   kvm_tc_init(ctl, kvm_smem);
-  const bool use_ring = T.ring && dyn >= KVM_ST_HDR + KVM_ST_RING + 32768;
+  const unsigned ring_ns = T.ring == 2 ? 2u : 3u;
+  const int ring_bytes = (int)ring_ns * KVM_ST_STAGE;
+  const bool use_ring = T.ring && dyn >= KVM_ST_HDR + ring_bytes + 32768;
   if (tid == 64 && use_ring) {
-    for (int s = 0; s < KVM_ST_NSTAGE; ++s) { kvm_mbar_init(sbar + 8 * s, 1); kvm_mbar_init(sbar + 64 + 8 * s, KVM_ST_ARRIVALS); }
+    for (int s = 0; s < 3; ++s) { kvm_mbar_init(sbar + 8 * s, 1); kvm_mbar_init(sbar + 64 + 8 * s, KVM_ST_ARRIVALS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -322,7 +487,8 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
   const unsigned long long deadline = t_begin + S.timeout_ns;
   KvmRing ring;
   ring.bar0 = sbar;
-  ring.base = kvm_smem + (use_ring ? dyn - KVM_ST_RING : 0);
+  ring.ns = ring_ns;
+  ring.base = kvm_smem + (use_ring ? dyn - ring_bytes : 0);
   ring.base_addr = kvm_smem_addr(ring.base);
   const int p_lo = T.prog_off[w], n = T.prog_off[w + 1] - p_lo;
 
@@ -333,6 +499,28 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
     int dep[5] = {-1, -1, -1, -1, -1}, dep_pos = -1;     // dependency entries of the task at `ri`
     bool stop = false;
     unsigned idle = 0;
+    // one pass of the copy issuer: lane 0 issues chunks of the oldest tasks that still have copies to issue while stages are free
+    auto stream_pass = [&]() -> bool {
+      if (ii >= fi) return false;
+      int lii = ii, lic = ic;
+      unsigned lpit = pit;
+      if (lane == 0) {
+        for (int guard = 0; guard < 6 && lii < fi; ++guard) {
+          KvmStSlot& sl = slots[lii % KVM_ST_SLOTS];
+          if (sl.kind == 0) { ++lii; lic = 0; continue; }
+          if (!(sl.prefetch || lii < ri)) break;             // constants may run ahead; anything else waits until the task is ready
+          if (!(lpit < ring.ns || kvm_mbar_test(kvm_ring_empty(ring, lpit), kvm_ring_parity(ring, lpit) ^ 1u))) break;
+          if (!sl.prefetch) asm volatile("fence.proxy.async;" ::: "memory");      // data other workers wrote with plain stores, read here by bulk copies
+          kvm_static_issue(S, sl, ring, lpit, lic);
+          ++lpit; ++lic;
+          if (lic >= sl.nchunks) { ++lii; lic = 0; }
+        }
+      }
+      lii = __shfl_sync(0xffffffffu, lii, 0); lic = __shfl_sync(0xffffffffu, lic, 0); lpit = __shfl_sync(0xffffffffu, lpit, 0);
+      const bool moved = lii != ii || lic != ic;
+      ii = lii; ic = lic; pit = lpit;
+      return moved;
+    };
     while (!stop && (ri < n || ii < n)) {
       bool progressed = false;
       // 1. fetch the next record into a free slot
@@ -349,7 +537,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
         if (lane == 31) sl.task = task;
         __syncwarp();
         if (use_ring) {                                      // table entries of the buffer arguments of a streaming op, lanes in parallel
-          const int op = sl.desc[0], nb = op == 134 ? 6 : (op == 135 || op == 300) ? 7 : 0;
+          const int op = sl.desc[0], nb = (op == 134 || op == 301) ? 6 : (op == 135 || op == 300) ? 7 : 0;
           if (lane < nb) {
             const int idx = sl.args[lane];
             KvmBuf e; e.p = nullptr; e.rows = e.cols = e.ld = 0; e.dtype = 0; e.reserved[0] = e.reserved[1] = 0;
@@ -359,32 +547,14 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
           __syncwarp();
         }
         if (lane == 0) {
-          if (use_ring) kvm_static_geometry(S, sl, (int)dyn - KVM_ST_HDR - KVM_ST_RING); else { sl.kind = 0; sl.nchunks = 0; }
+          if (use_ring) kvm_static_geometry(S, sl, (int)dyn - KVM_ST_HDR - ring_bytes); else { sl.kind = 0; sl.nchunks = 0; }
           sl.state = 1;
         }
         __syncwarp();
         ++fi; progressed = true;
       }
       // 2. stream ahead: chunks of the oldest tasks that still have copies to issue, as many as there are free stages
-      if (ii < fi) {
-        int lii = ii, lic = ic;
-        unsigned lpit = pit;
-        if (lane == 0) {
-          for (int guard = 0; guard < 2 * KVM_ST_NSTAGE && lii < fi; ++guard) {
-            KvmStSlot& sl = slots[lii % KVM_ST_SLOTS];
-            if (sl.kind == 0) { ++lii; lic = 0; continue; }
-            if (!(sl.prefetch || lii < ri)) break;           // constants may run ahead; anything else waits until the task is ready
-            if (!(lpit < KVM_ST_NSTAGE || kvm_mbar_test(kvm_ring_empty(ring, lpit), kvm_ring_parity(lpit) ^ 1u))) break;
-            if (!sl.prefetch) asm volatile("fence.proxy.async;" ::: "memory");      // data other workers wrote with plain stores, read here by bulk copies
-            kvm_static_issue(S, sl, ring, lpit, lic);
-            ++lpit; ++lic;
-            if (lic >= sl.nchunks) { ++lii; lic = 0; }
-          }
-        }
-        lii = __shfl_sync(0xffffffffu, lii, 0); lic = __shfl_sync(0xffffffffu, lic, 0); lpit = __shfl_sync(0xffffffffu, lpit, 0);
-        if (lii != ii || lic != ic) progressed = true;
-        ii = lii; ic = lic; pit = lpit;
-      }
+      if (stream_pass()) progressed = true;
       // 3. dependencies of the next task to become ready: its entries are held in registers (up to five per lane) and polled with
       //    plain loads, all in flight together; one acquire fence once they are all met
       if (ri < fi) {
@@ -398,6 +568,10 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
         int seen[5];
 #pragma unroll
         for (int j = 0; j < 5; ++j) seen[j] = dep[j] >= 0 ? kvm_ld_relaxed(&T.progress[dep[j] >> KVM_ST_WAIT_BITS]) : 0;
+        // while those loads are in flight (an L2 round trip, longer when the memory system is saturated by the copies) keep
+        // refilling stages: a freed stage must not wait for the poll
+        if (ii < fi)
+          for (int sp = 0; sp < 6; ++sp) if (stream_pass()) progressed = true;
         bool met = true;
 #pragma unroll
         for (int j = 0; j < 5; ++j) if (dep[j] >= 0 && seen[j] < (dep[j] & ((1 << KVM_ST_WAIT_BITS) - 1))) met = false;
@@ -438,7 +612,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
     c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_ST_HDR) : S.bufs;
     const int used = KVM_ST_HDR + (buf_cache ? cache_bytes : 0);
     c.smem = kvm_smem + used;
-    c.smem_bytes = (int)dyn - used - (use_ring ? KVM_ST_RING : 0);
+    c.smem_bytes = (int)dyn - used - (use_ring ? ring_bytes : 0);
     unsigned cit = 0;
     int finished = 0;
     for (int i = 0; i < n; ++i) {
@@ -456,28 +630,29 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
       if (go == 0) break;
       const int task = sl.task;
       c.task = task;
-      if (tid == 0 && S.trace) { S.t_start[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid(); }
+      unsigned long long t_task = 0;
+      if (tid == 0 && S.trace) { t_task = kvm_globaltimer(); S.t_start[task] = t_task; sctl[3] = 0; }
       const int op = sl.desc[0], kind = sl.kind, nch = sl.nchunks;
-      if (kind == 1) kvm_gemv_ring(c, sl.args, sl.lb, ring, cit, sl.R, nch, deadline);
+      if (kind == 1) kvm_gemv_ring(c, sl.args, sl.lb, ring, cit, sl.R, nch, deadline, t_task, S.trace ? sctl + 3 : nullptr);
+      else if (kind == 3) kvm_gemv_rows_ring(c, sl.args, sl.lb, ring, cit, sl.R, deadline);
       else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, op == 300, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
       else if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       cit += (unsigned)nch;
       asm volatile("fence.proxy.async;" ::: "memory");
       kvm_sync();
       if (tid == 0) {
-        if (S.trace) S.t_end[task] = kvm_globaltimer();
-        S.exec_count[task] += 1;
-        __threadfence();
+        if (S.trace) { S.t_end[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid() | (sctl[3] << 8); }     // bits 8.. : detail of a streamed task
+        atomicAdd(&S.exec_count[task], 1);                   // no result needed: nothing waits for the old value
         const int pv = sl.desc[10];
         if (pv >= 0) {                                       // publish (include/mvm_task_abi.h:20-23): old + 1, else VERSION_GAP
           if (pv >= S.nvars) kvm_dev_fail(S, KVM_ERR_BAD_VAR, task, pv);
           else {
+            __threadfence();                                 // the task's writes before its version
             const int ver = sl.desc[11] + S.ver_off[pv];
             if (atomicCAS(&S.versions[pv], ver - 1, ver) != ver - 1) kvm_dev_fail(S, KVM_ERR_VERSION_GAP, task, pv, ver);
-            __threadfence();
           }
         }
-        kvm_st_release(&T.progress[w], i + 1);
+        kvm_st_release(&T.progress[w], i + 1);               // release at gpu scope: the CTA's writes (ordered before this thread by the barrier) come first
         sctl[0] = (int)cit;
         sl.state = 0;
       }
@@ -490,7 +665,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
   if (use_ring && tid == KVM_NT) {
     const unsigned pit = (unsigned)sctl[2], cit = (unsigned)sctl[0];
     for (unsigned it = cit; it < pit; ++it) {
-      const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(it);
+      const uint32_t bar = kvm_ring_full(ring, it), par = kvm_ring_parity(ring, it);
       const unsigned long long t0 = kvm_globaltimer();
       unsigned spins = 0;
       while (!kvm_mbar_test(bar, par)) if ((++spins & 63u) == 0 && kvm_globaltimer() - t0 > 50000000ull) break;      // 50 ms: a bulk copy lands in microseconds

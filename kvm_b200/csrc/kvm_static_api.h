@@ -6,7 +6,6 @@
 #include "kvm_state.cuh"
 
 #define KVM_ST_STAGE 65536             // bytes of one stream stage
-#define KVM_ST_NSTAGE 3
 #define KVM_ST_WAIT_BITS 20            // dependency entry: worker << 20 | tasks that worker must have finished
 
 struct KvmStaticState {
@@ -15,7 +14,7 @@ struct KvmStaticState {
   const int* prog_off;        // [workers + 1]
   const int* waits;           // dependency entries of all tasks (deduplicated lists)
   int* progress;              // [workers]: tasks finished by that worker (release stores)
-  int ring;                   // 1: the launch carries the stream ring (decode programs), 0: all shared memory is op scratch
+  int ring;                   // 0: all shared memory is op scratch; 1: three 64 KB stream stages + 32 KB scratch (decode programs); 2: two stages + 96 KB scratch (programs with gemv_bf16_rows)
 };
 
 // record words beyond the ready-queue path's (descriptor 0..15, arguments 16..35, path selector 36..39)

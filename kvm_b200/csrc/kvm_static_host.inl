@@ -17,7 +17,7 @@ static double kvm_static_cost(const KvmExec* h, const KvmTaskDesc& d, const int3
   auto elems = [&](int e0, int e1) { return (double)(e1 > e0 ? e1 - e0 : 0); };
   switch (d.op_id) {
     case 0: return 0.2;
-    case 134: return 1.5 + elems(a[6], a[7]) * a[8] * 2.0 / BPU;
+    case 134: case 301: return 1.5 + elems(a[6], a[7]) * a[8] * 2.0 / BPU;
     case 135: case 300: { const double keys = a[10] > 0 ? (double)a[14] / a[10] : a[14]; return 3.0 + 2.0 * keys * a[13] * 2.0 / BPU; }
     case 136: return 1.0;
     case 58: case 57: return 2.0 + elems(a[d.op_id == 58 ? 2 : 3], a[d.op_id == 58 ? 3 : 4]) * a[d.op_id == 58 ? 4 : 5] * 4.0 / BPU;
@@ -61,7 +61,7 @@ static std::vector<char> kvm_written_buffers(const KvmExec* h) {
       if (op->types[j] < 2 || a[j] < 0 || a[j] >= (int)wr.size()) continue;
       bool read_only = false;
       switch (d.op_id) {
-        case 134: read_only = j != 4; break;                          // x, x2, gamma, w, res
+        case 134: case 301: read_only = j != 4; break;                // x, x2, gamma, w, res
         case 135: case 300: read_only = j != 4; break;                // q, kc, vc, lens, knew, vnew, qk_gamma (kc / vc: own appended row only)
         case 136: read_only = j == 0; break;
         case 63: read_only = j != 2; break;
@@ -184,7 +184,7 @@ static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, Kv
   for (int u = 0; u < nt; ++u) {
     const KvmTaskDesc& du = h->tasks[u];
     const KvmOpInfo* op = kvm_find_op(du.op_id);
-    if (!op || du.op_id == 134 || du.op_id == 135 || du.op_id == 300) continue;
+    if (!op || du.op_id == 134 || du.op_id == 301 || du.op_id == 135 || du.op_id == 300) continue;
     const int32_t* au = h->args.data() + du.args_off;
     for (int j = 0; j < op->arity; ++j) if (op->types[j] >= 2 && au[j] >= 0 && au[j] < nb && !len_readers[au[j]].empty()) { len_users[au[j]].push_back(u); break; }
   }
@@ -194,12 +194,13 @@ static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, Kv
     for (int t : len_readers[L]) if (!mark[t]) len_ok[t] = 0;
     for (int p : preds[u]) mark[p] = 0;
   }
-  bool any_stream = false, all_fit = true;
+  bool any_stream = false, all_fit = true, any_rows = false;
   for (int t = 0; t < nt; ++t) {
     const KvmTaskDesc& d = h->tasks[t];
     const int32_t* a = h->args.data() + d.args_off;
-    if (d.op_id == 134) {
+    if (d.op_id == 134 || d.op_id == 301) {
       any_stream = true;
+      if (d.op_id == 301) any_rows = true;
       const int K = a[8];
       if (K <= 0 || (K & 255) || K * 2 > KVM_ST_STAGE) all_fit = false;       // such a row does not stream through a stage: run the whole program without the ring
       if (a[3] >= 0 && a[3] < nb && !written[a[3]]) plan.stream[t] = 1;
@@ -207,6 +208,6 @@ static int kvm_plan_static(KvmExec* h, const std::vector<int>& base_versions, Kv
       if (a[1] >= 0 && a[2] >= 0 && a[3] >= 0 && a[1] < nb && a[2] < nb && a[3] < nb && !written[a[1]] && !written[a[2]] && len_ok[t]) plan.stream[t] = 1;
     }
   }
-  plan.ring = any_stream && all_fit;
+  plan.ring = !(any_stream && all_fit) ? 0 : any_rows ? 2 : 1;
   return 0;
 }

@@ -77,6 +77,7 @@ SYMBOLS = {
     'kvm_clear_tasks': (C.c_int, [C.c_void_p]),
     'kvm_task_counts': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_trace': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
+    'kvm_trace_detail': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_launch_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     'kvm_plan_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     'kvm_tc_task_count': (C.c_int, [C.c_void_p]),
@@ -323,6 +324,13 @@ class Executor:
         s, e, sm = np.empty(n, np.uint64), np.empty(n, np.uint64), np.empty(n, np.int32)
         self._check(self.L.kvm_trace(self._h, s.ctypes.data, e.ctypes.data, sm.ctypes.data, n))
         return s, e, sm
+
+    def trace_detail(self, n=None):
+        """Per task the packed prologue / stage-wait times of a streamed GEMV on the static path (see kvm_trace_detail)."""
+        n = n if n is not None else len(self.bundle.tasks)
+        d = np.empty(n, np.int32)
+        self._check(self.L.kvm_trace_detail(self._h, d.ctypes.data, n))
+        return d
 
     def plan_info(self):
         """(runs on the static path?, with the stream ring?, planner's estimate of one run in us) of the prepared program."""

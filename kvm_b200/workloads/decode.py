@@ -184,6 +184,104 @@ def build_decode(c: DecodeConfig) -> Graph:
     return g
 
 
+def build_decode_rows(c: DecodeConfig, exact_caches: bool = False) -> Graph:
+    """The same decode step with the batch as ROWS of shared activation matrices (x [B, hidden], q [B, H*hd], ...), so that every
+    projection is one pass over its weights for all users: gemv_bf16_rows (extension op 301) instead of one gemv_bf16 per user.
+    Attention stays per user (each has its own cache rows and length; the ops take the user as their `b` argument), as do the
+    split merges; embedding, argmax and the length counters run over the B rows at once.  Same weights (same seeds) as
+    build_decode, so the tokens of user u equal those of build_decode's user u: exact_caches=True also gives every user the
+    cache contents build_decode seeds for it (small configurations, parity tests); otherwise the combined caches are seeded."""
+    from .. import initgen
+    g = Graph('decode_rows')
+    g.join_threshold = c.join_threshold
+    d, H, Hkv, hd, F, V, B, S = c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.batch, c.splits
+    seed_of = lambda name: zlib.crc32(f'{c.seed}/{name}'.encode())
+    seeded = lambda name, scale=None: {'kind': 'seeded', 'seed': seed_of(name), 'scale': scale or c.init_std, 'dist': 'normal'}
+    W = lambda name, n, k: g.buffer('wb.' + name, n, k, 'bf16', seeded(name))
+
+    def phase_rows(ns, k):
+        if c.rows_per_task > 0:
+            return c.rows_per_task
+        total = sum(ns)
+        slots = c.workers * max(1, round(total * k * 2 / (c.workers * (2 << 20))))
+        rows = max(8, -(-total // slots))
+        while sum(-(-n // rows) for n in ns) > slots:
+            rows += 1
+        return -(-rows // 8) * 8                 # whole groups of eight weight rows: what one stage of the stream ring holds
+
+    def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20, rows=None):
+        rows = rows or phase_rows([n], k)
+        for i, n0 in enumerate(range(0, n, rows)):
+            n1 = min(n0 + rows, n)
+            g.task('gemv_bf16_rows', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps, 'r0': 0, 'r1': B},
+                   [x, x2, gamma, (w, (n0, n1)), (res, (0, B), (n0, n1)) if res else None], [(out, (0, B), (n0, n1))], prio, f'{tag}.{i}')
+
+    g.buffer('wb.embed', V, d, 'bf16', seeded('embed'))
+    g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
+    W('head', V, d)
+    for l in range(c.layers):
+        p = f'l{l}.'
+        g.buffer('w.' + p + 'ln1', 1, d, init={'kind': 'fill', 'value': 1.0}), g.buffer('w.' + p + 'ln2', 1, d, init={'kind': 'fill', 'value': 1.0})
+        W(p + 'q', H * hd, d), W(p + 'k', Hkv * hd, d), W(p + 'v', Hkv * hd, d), W(p + 'o', d, H * hd), W(p + 'gate', F, d), W(p + 'up', F, d), W(p + 'down', d, F)
+    lens = g.buffer('lens', B, 1, 'i32', {'kind': 'fill', 'value': c.ctx})
+    tok = g.data('tok', np.array([[(7 * u + 3) % V] for u in range(B)], np.int32), 'i32')
+    x = g.buffer('x', B, d)
+    g.task('gather_rows', {'src': 'wb.embed', 'idx': tok, 'dst': x, 'r0': 0, 'r1': B, 'd': d}, ['wb.embed', tok], [x], 31, 'embed')
+    G = H // Hkv
+    slice_ = c.tmax // S
+    for l in range(c.layers):
+        p = f'l{l}.'
+        prio = max(30 - l, 2)
+
+        def cache(n):
+            if exact_caches:
+                draws, bias, coef = initgen.seeded_params('normal', 1.0)
+                parts = [initgen.seeded_values(seed_of(f'u{u}.l{l}.{n}'), Hkv * c.tmax * hd, draws, bias, coef).reshape(Hkv * c.tmax, hd) for u in range(B)]
+                return g.data(p + n, np.concatenate(parts), 'bf16')
+            return g.buffer(p + n, B * Hkv * c.tmax, hd, 'bf16', seeded(p + n, 1.0))
+        kc, vc = cache('kc'), cache('vc')
+        q, k, v = (g.buffer(p + n, B, cols) for n, cols in (('q', H * hd), ('k', Hkv * hd), ('v', Hkv * hd)))
+        r_qkv = phase_rows([H * hd, Hkv * hd, Hkv * hd], d)
+        gemv(p + 'q', x, 'wb.' + p + 'q', q, H * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
+        gemv(p + 'k', x, 'wb.' + p + 'k', k, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
+        gemv(p + 'v', x, 'wb.' + p + 'v', v, Hkv * hd, d, 1, gamma='w.' + p + 'ln1', prio=prio, rows=r_qkv)
+        part, o = g.buffer(p + 'part', B * S * H, hd + 2), g.buffer(p + 'o', B, H * hd)
+        qkn = None
+        if c.qk_norm:
+            rng = np.random.default_rng(zlib.crc32(f'{c.seed}/{p}qkn'.encode()))
+            qkn = g.data('w.' + p + 'qkn', (1.0 + 0.25 * rng.uniform(-1, 1, (2, hd))).astype(np.float32))
+        for u in range(B):
+            for kvh in range(Hkv):
+                base = (u * Hkv + kvh) * c.tmax
+                for s in range(S):
+                    rows = (base + s * slice_, base + (s + 1) * slice_)
+                    args = {'q': q, 'kc': kc, 'vc': vc, 'lens': lens, 'part': part, 'knew': k, 'vnew': v, 'b': u, 'kvh': kvh, 's': s, 'S': S, 'H': H, 'Hkv': Hkv, 'hd': hd,
+                            'Tmax': c.tmax, 'scale': hd ** -0.5, 'theta': c.theta, 'flags': 3}
+                    if qkn:
+                        args.update(qk_gamma=qkn, eps=c.eps)
+                    prow = (u * S + s) * H + kvh * G
+                    g.task('attn_decode_part_qkn' if qkn else 'attn_decode_part', args, [(q, (u, u + 1)), (k, (u, u + 1)), (v, (u, u + 1)), lens, qkn],
+                           [(kc, rows), (vc, rows), (part, (prow, prow + G))], prio, f'{p}part.{u}.{kvh}.{s}')
+        for u in range(B):
+            for kvh in range(Hkv):
+                g.task('attn_decode_merge', {'part': part, 'o': o, 'b': u, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': H, 'hd': hd},
+                       [(part, (u * S * H, (u + 1) * S * H))], [(o, (u, u + 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{p}merge.{u}.{kvh}')
+        x1 = g.buffer(p + 'x1', B, d)
+        gemv(p + 'o', o, 'wb.' + p + 'o', x1, d, H * hd, 0, res=x, prio=prio)
+        gate, up = g.buffer(p + 'gate', B, F), g.buffer(p + 'up', B, F)
+        r_gu = phase_rows([F, F], d)
+        gemv(p + 'gate', x1, 'wb.' + p + 'gate', gate, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
+        gemv(p + 'up', x1, 'wb.' + p + 'up', up, F, d, 1, gamma='w.' + p + 'ln2', prio=prio, rows=r_gu)
+        xn = g.buffer(p + 'x2', B, d)
+        gemv(p + 'down', gate, 'wb.' + p + 'down', xn, d, F, 2, x2=up, res=x1, prio=prio)
+        x = xn
+    logits = g.buffer('logits', B, V)
+    gemv('head', x, 'wb.head', logits, V, d, 1, gamma='w.lnf', prio=1)
+    g.task('argmax', {'logits': logits, 'out': tok, 'r0': 0, 'r1': B, 'V': V}, [logits], [tok], 1, 'argmax')
+    g.task('counter_inc', {'x': lens, 'i0': 0, 'i1': B, 'delta': 1}, [lens], [lens], 0, 'advance')
+    return g
+
+
 def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False):
     """Rank `rank`'s share of the one-token graph under tensor parallelism over `world` ranks, batch 1.
 

@@ -652,6 +652,17 @@ def gemv_bf16(b, a, **kw):
     out.flat[n0:n1] = _st(out, y)
 
 
+def gemv_bf16_rows(b, a, **kw):
+    """gemv_bf16 for rows r0..r1 of x / x2 / out / res against the same weight rows (an extension op, id 301): the batch of a
+    decode step as rows of one activation matrix, so that the weights are read once for all of them.  Row by row it is exactly
+    gemv_bf16 (same rounding points), which is how it is restated here."""
+    r0, r1 = a['r0'], a['r1']
+    _need(0 <= r0 < r1 and r1 <= b['x'].rows and r1 <= b['out'].rows, 'gemv_bf16_rows: bad row range')
+    for r in range(r0, r1):
+        row = {k: (None if v is None else (v if k in ('w', 'gamma') else Buf(v.a[r:r + 1], v.dtype))) for k, v in b.items()}
+        gemv_bf16(row, a, **kw)
+
+
 # ---- loss -------------------------------------------------------------------------------------------------------------------
 def softmax_ce_fwd(b, a, **kw):
     lg, tg, rl, ls = b['logits'], b['tgt'], b['rowloss'], b['lse']

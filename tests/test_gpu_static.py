@@ -166,3 +166,62 @@ def test_streamed_gemv_shapes(kvm_lib, case):
         assert ex.run().done == len(b.tasks)
         assert ex.plan_info()[:2] == (True, True)
         assert rel_err(ex.read_buffer('out'), vm.buffer('out').a) <= 2e-5
+
+
+# ---- the batch of a decode step as rows: gemv_bf16_rows (extension op 301) ----------------------------------------------------------------
+@pytest.mark.parametrize('case', [dict(K=4096, N=70, M=8, pro=1), dict(K=12288, N=40, M=8, pro=2), dict(K=1024, N=64, M=3, pro=0), dict(K=2048, N=33, M=8, pro=1, ld=2304),
+                                  dict(K=4096, N=16, M=1, pro=1)])
+def test_streamed_gemv_rows_shapes(kvm_lib, case):
+    """The tensor-core ring form of gemv_bf16_rows against the oracle (row by row gemv_bf16): one k-chunk and three (K 12288),
+    ragged row groups, fewer than eight activation rows, a strided weight matrix, every prologue; on the static path with the
+    two-stage ring, and the same program on the ready queue (row-by-row fallback)."""
+    from kvm_b200.executor import CFG_DYNAMIC, Executor
+    from kvm_b200.workloads.graph import Graph
+    from oracle.vm_np import VM
+    K, N, M, pro, ld = case['K'], case['N'], case['M'], case['pro'], case.get('ld')
+    rng = np.random.default_rng(11)
+    g = Graph('gemv_rows')
+    g.data('x', rng.standard_normal((M, K)).astype(np.float32))
+    g.data('x2', rng.standard_normal((M, K)).astype(np.float32))
+    g.data('gamma', 1.0 + 0.1 * rng.standard_normal((1, K)).astype(np.float32))
+    g.data('w', (rng.standard_normal((N, ld or K)) * 0.05).astype(np.float32), 'bf16')
+    g.data('res', rng.standard_normal((M, N)).astype(np.float32))
+    g.buffer('out', M, N)
+    for n0 in range(0, N, 24):
+        g.task('gemv_bf16_rows', {'x': 'x', 'x2': 'x2' if pro == 2 else None, 'gamma': 'gamma' if pro == 1 else None, 'w': 'w', 'out': 'out', 'res': 'res',
+                                  'n0': n0, 'n1': min(n0 + 24, N), 'K': K, 'pro': pro, 'eps': 1e-6, 'r0': 0, 'r1': M})
+    b = g.to_bundle()
+    vm = VM(b).run()
+    for flags in (0, CFG_DYNAMIC):
+        with Executor(flags=flags) as ex:
+            ex.load(b)
+            assert ex.run().done == len(b.tasks)
+            assert ex.plan_info()[:2] == ((True, True) if flags == 0 else (False, False))
+            assert rel_err(ex.read_buffer('out'), vm.buffer('out').a) <= 2e-5, flags
+
+
+def test_decode_batch_as_rows_equals_per_user_decode(kvm_lib):
+    """Three users as rows of shared activations (weights read once per step) give, token for token, what three independent
+    one-row users give (the oracle on the per-user graph), with and without QK norm."""
+    from kvm_b200.executor import Executor
+    from kvm_b200.workloads.decode import build_decode, build_decode_rows, preset
+    from oracle.vm_np import VM
+    for qkn in (False, True):
+        cfg = preset('decode_tiny', batch=3, init_std=0.08, qk_norm=qkn)
+        bu = build_decode(cfg).to_bundle()
+        vm, ref = VM(bu), []
+        for s in range(16):
+            vm.run()
+            ref.append([int(vm.buffer(f'u{u}.tok').a[0, 0]) for u in range(3)])
+            vm = VM(bu, buffers=vm.bufs)
+        br = build_decode_rows(cfg, exact_caches=True).to_bundle()
+        with Executor() as ex:
+            ex.load(br)
+            got = []
+            for s in range(16):
+                assert ex.run().done == len(br.tasks)
+                got.append(ex.read_buffer('tok')[:, 0].tolist())
+            assert ex.plan_info()[:2] == (True, True)
+            execs, observed = ex.task_counts()
+            assert (execs == 1).all() and np.array_equal(observed, br.tasks['indegree'])
+        assert got == ref, (qkn, got, ref)
