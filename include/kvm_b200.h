@@ -139,8 +139,9 @@ int kvm_clear_tasks(KvmExec* h);
 int kvm_task_counts(KvmExec* h, int32_t* exec_count, int32_t* observed, int32_t n);
 /* With trace on: per task start / end (ns, %globaltimer) and SM id (MvmTrace, include/mvm_exec.cuh:167-176). */
 int kvm_trace(KvmExec* h, uint64_t* start_ns, uint64_t* end_ns, int32_t* smid, int32_t n);
-/* With trace on, static path: per streamed GEMV task three bytes of where its time went: bits 0-7 prologue (units of 0.1 us,
- * saturating), bits 8-15 wait for the first stage of weights (0.1 us), bits 16-23 all waits for stages (0.2 us); 0 for other tasks. */
+/* With trace on, static path: per streamed GEMV task three bytes of where its time went, each in units of 0.2 us (saturating):
+ * bits 0-7 prologue, bits 8-15 the loop over the stages of weights (waits included), bits 16-23 the waits for stages alone;
+ * for a streamed attention split: bits 0-7 prologue (0.1 us), bits 8-15 waits for keys and values (0.1 us); 0 for other tasks. */
 int kvm_trace_detail(KvmExec* h, int32_t* detail, int32_t n);
 /* Launch geometry of the persistent kernel: worker CTAs, threads per CTA, dynamic shared memory bytes. */
 int kvm_launch_info(KvmExec* h, int32_t* workers, int32_t* threads, int32_t* smem_bytes);

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import os
+import time
 import subprocess
 import sys
 from pathlib import Path
@@ -43,6 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not stale():
         return LIB
     objs, procs = [], []
+    started = time.time()          # an object counts as built when its compile STARTED: a source edited while nvcc runs stays newer
     for unit in UNITS:
         obj = PKG / f'_{unit}.o'
         objs.append(obj)
@@ -56,6 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out + err)
         if p.returncode:
             raise RuntimeError(f'nvcc failed ({p.returncode}): {" ".join(cmd)}')
+        os.utime(cmd[-1], (started, started))
     cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', *map(str, objs), '-o', str(LIB), '-lcudart']
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode:

@@ -67,7 +67,7 @@ __device__ __forceinline__ void kvm_att_mma_pv(uint32_t tmem_d, uint32_t sa, uin
 #define KVM_LN2 0.6931471805599453f
 
 // aux: x = 2 (tensor-core attention), y / z / w = tensor-map indices of q / k / v (box 64 x 128 over [rows, H*hd]).
-static __device__ void kvm_attn_fwd_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
+KVM_OP_FN void kvm_attn_fwd_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmBuf o, lse;
   if (!kvm_buf(c, a[3], KVM_M_FLT, o) || !kvm_buf(c, a[4], KVM_M_F32, lse)) return;
   const int b = a[5], h = a[6], q0 = a[7], T = a[8], H = a[9], Hkv = a[10];
@@ -185,7 +185,7 @@ static __device__ void kvm_attn_fwd_tc(const KvmCtx& c, const int32_t* a, const 
 
 // dq for 128 query rows.  aux.y/z/w = maps of q / k / v; the dO map index travels in the high half of aux.x (aux.x = 2 | idx << 8).
 // Shared memory: Q 16K, dO 16K, two stages of (K 16K, V 16K), dS tile 32K.  TMEM: S cols 0..127, dP 128..255, dQ 256..319.
-static __device__ void kvm_attn_dq_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
+KVM_OP_FN void kvm_attn_dq_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmBuf lse, delta, dq;
   if (!kvm_buf(c, a[4], KVM_M_F32, lse) || !kvm_buf(c, a[5], KVM_M_F32, delta) || !kvm_buf(c, a[6], KVM_M_FLT, dq)) return;
   const int b = a[7], h = a[8], q0 = a[9], T = a[10], H = a[11], Hkv = a[12];
@@ -293,7 +293,7 @@ static __device__ void kvm_attn_dq_tc(const KvmCtx& c, const int32_t* a, const i
 // dk, dv for 128 key rows of kv head kvh: loops over the heads of the GQA group and the query blocks at or after the key block.
 // Shared memory: K 16K, V 16K, two stages of (Q 16K, dO 16K), P^T tile 32K, dS^T tile 32K, lse / delta of the block 1K.
 // TMEM: S^T cols 0..127, dP^T 128..255, dV 256..319, dK 320..383.
-static __device__ void kvm_attn_dkv_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
+KVM_OP_FN void kvm_attn_dkv_tc(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmBuf lse, delta, dk, dv, kb;
   if (!kvm_buf(c, a[1], KVM_M_FLT, kb) || !kvm_buf(c, a[4], KVM_M_F32, lse) || !kvm_buf(c, a[5], KVM_M_F32, delta) || !kvm_buf(c, a[6], KVM_M_FLT, dk) ||
       !kvm_buf(c, a[7], KVM_M_FLT, dv)) return;

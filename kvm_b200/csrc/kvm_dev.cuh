@@ -47,6 +47,7 @@ struct KvmCtx {
   int* ctl;                   // executor control words in shared memory (ctl[0] = TMEM base address)
   const void* tmaps;          // tensor-map table of the tensor-core tasks
   int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
+  float* rope_cache;          // shared memory, 66 floats kept over the tasks of a launch: [0] theta bits, [1] head dimension bits, [2..] the inverse frequencies of that pair (or nullptr)
   int engine;                 // 1: the kernel's engine warps run the mainloops of tensor-core GEMM tiles, the op body is their epilogue only
   unsigned gemm_seq;          // with engine: how many tensor-core GEMM tiles this CTA ran before this one (accumulator = gemm_seq & 1)
 
@@ -75,6 +76,11 @@ __device__ __forceinline__ void kvm_st(const KvmBuf& b, size_t i, float v) {
   else ((float*)b.p)[i] = v;
 }
 __device__ __forceinline__ float kvm_bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// The same with the storage type as a template argument, for loops whose memory parallelism must not depend on whether the compiler
+// hoists the type test out of the loop (with the test inside, every load sits in a basic block of its own and waits for the one
+// before it: measured 2.3x on the column reductions).
+template <bool BF>
+__device__ __forceinline__ float kvm_ldt(const void* p, size_t i) { return BF ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i]; }
 
 // 8 consecutive elements starting at i (i % 8 == 0 and the base 16-byte aligned).
 __device__ __forceinline__ void kvm_ld8(const KvmBuf& b, size_t i, float (&v)[8]) {
@@ -100,6 +106,31 @@ __device__ __forceinline__ void kvm_st8(const KvmBuf& b, size_t i, const float (
     *(float4*)((float*)b.p + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
   }
 }
+template <bool BF>
+__device__ __forceinline__ void kvm_ld8t(const void* p, size_t i, float (&v)[8]) {
+  if (BF) {
+    uint4 u = *(const uint4*)((const __nv_bfloat16*)p + i);
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&u;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+  } else {
+    float4 a = *(const float4*)((const float*)p + i), c = *(const float4*)((const float*)p + i + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+  }
+}
+template <bool BF>
+__device__ __forceinline__ void kvm_st8t(void* p, size_t i, const float (&v)[8]) {
+  if (BF) {
+    uint4 u;
+    __nv_bfloat162* h = (__nv_bfloat162*)&u;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *(uint4*)((__nv_bfloat16*)p + i) = u;
+  } else {
+    *(float4*)((float*)p + i) = make_float4(v[0], v[1], v[2], v[3]);
+    *(float4*)((float*)p + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
 __device__ __forceinline__ bool kvm_vec_ok(const KvmBuf& b) { return ((uintptr_t)b.p & 15) == 0; }
 
 // ---- argument checking ------------------------------------------------------------------------------------------------------
@@ -108,6 +139,14 @@ __device__ __forceinline__ bool kvm_vec_ok(const KvmBuf& b) { return ((uintptr_t
 #define KVM_M_I32 2
 #define KVM_M_BF16 4
 #define KVM_M_FLT (KVM_M_F32 | KVM_M_BF16)
+
+// Op bodies are inlined into the dispatcher.  For a per-op report of registers and spills from the compiler (-Xptxas -v), build once
+// with -DKVM_OPS_NOINLINE: every op then is a function of its own (measured 3% slower on a training step, so not the default).
+#ifdef KVM_OPS_NOINLINE
+#define KVM_OP_FN static __device__ __noinline__
+#else
+#define KVM_OP_FN static __device__
+#endif
 
 // Fetch table entry `idx` (an argument word). Optional buffers: idx == -1 gives p == nullptr and returns true.
 __device__ __forceinline__ bool kvm_buf(const KvmCtx& c, int idx, int mask, KvmBuf& out, bool optional = false) {

@@ -312,7 +312,7 @@ static __device__ void kvm_mm_tc_pair(const KvmCtx& c, const KvmMmArgs& g, const
 static __device__ void kvm_tce_epilogue(const KvmCtx& c, const KvmMmArgs& g);
 __device__ __forceinline__ void kvm_mbar_arrive_local(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 // aux.x = 1: tensor-core path planned by the host (aux.y / aux.z = tensor-map indices of A / B); else SIMT fallback.
-static __device__ void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
+KVM_OP_FN void kvm_op_matmul_mma_bf16(const KvmCtx& c, const int32_t* a, const int4& aux) {
   KvmMmArgs g;
   if (!kvm_mm_args(c, a, 2, g)) return;
   if (aux.x != 1 || (c.cfg_flags & KVM_CFG_NO_TENSOR_CORES)) { kvm_mm_simt(c, g); return; }

@@ -25,7 +25,7 @@ static __device__ bool kvm_attn_geom(const KvmCtx& c, int b, int h, int r0, int 
   return true;
 }
 
-static __device__ void kvm_op_attn_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, k, v, o, lse;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, k) || !kvm_buf(c, a[2], KVM_M_FLT, v) || !kvm_buf(c, a[3], KVM_M_FLT, o) ||
       !kvm_buf(c, a[4], KVM_M_F32, lse)) return;
@@ -68,7 +68,7 @@ static __device__ void kvm_op_attn_fwd(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-static __device__ void kvm_op_attn_bwd_delta(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_bwd_delta(const KvmCtx& c, const int32_t* a) {
   KvmBuf o, dO, delta;
   if (!kvm_buf(c, a[0], KVM_M_FLT, o) || !kvm_buf(c, a[1], KVM_M_FLT, dO) || !kvm_buf(c, a[2], KVM_M_F32, delta)) return;
   const int r0 = a[3], r1 = a[4], T = a[5], H = a[6], hd = a[7];
@@ -116,7 +116,7 @@ static __device__ void kvm_op_attn_bwd_delta(const KvmCtx& c, const int32_t* a) 
   }
 }
 
-static __device__ void kvm_op_attn_bwd_dq(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_bwd_dq(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, k, v, dO, lse, delta, dq;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, k) || !kvm_buf(c, a[2], KVM_M_FLT, v) || !kvm_buf(c, a[3], KVM_M_FLT, dO) ||
       !kvm_buf(c, a[4], KVM_M_F32, lse) || !kvm_buf(c, a[5], KVM_M_F32, delta) || !kvm_buf(c, a[6], KVM_M_FLT, dq)) return;
@@ -161,7 +161,7 @@ static __device__ void kvm_op_attn_bwd_dq(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-static __device__ void kvm_op_attn_bwd_dkv(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_bwd_dkv(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, k, v, dO, lse, delta, dk, dv;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, k) || !kvm_buf(c, a[2], KVM_M_FLT, v) || !kvm_buf(c, a[3], KVM_M_FLT, dO) ||
       !kvm_buf(c, a[4], KVM_M_F32, lse) || !kvm_buf(c, a[5], KVM_M_F32, delta) || !kvm_buf(c, a[6], KVM_M_FLT, dk) || !kvm_buf(c, a[7], KVM_M_FLT, dv)) return;

@@ -10,7 +10,7 @@
 
 #define KVM_ATTN_EMPTY_M (-3.4028234663852886e38f)
 
-static __device__ void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_kv_append(const KvmCtx& c, const int32_t* a) {
   KvmBuf kn, vn, kc, vc, lens;
   if (!kvm_buf(c, a[0], KVM_M_FLT, kn) || !kvm_buf(c, a[1], KVM_M_FLT, vn) || !kvm_buf(c, a[2], KVM_M_FLT, kc) || !kvm_buf(c, a[3], KVM_M_FLT, vc) ||
       !kvm_buf(c, a[4], KVM_M_I32, lens)) return;
@@ -174,7 +174,7 @@ __device__ __forceinline__ bool kvm_decode_vec_ok(const KvmBuf& kc, const KvmBuf
   return hd >= 8 && hd <= 128 && (hd & (hd - 1)) == 0 && (kc.ld & 7) == 0 && (vc.ld & 7) == 0 && kvm_vec_ok(kc) && kvm_vec_ok(vc);
 }
 
-static __device__ void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_decode(const KvmCtx& c, const int32_t* a) {
   KvmBuf q, kc, vc, lens, o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, q) || !kvm_buf(c, a[1], KVM_M_FLT, kc) || !kvm_buf(c, a[2], KVM_M_FLT, vc) || !kvm_buf(c, a[3], KVM_M_I32, lens) ||
       !kvm_buf(c, a[4], KVM_M_FLT, o)) return;
@@ -206,6 +206,7 @@ struct KvmPartPro {
   float theta, eps;
   bool appends;
   float *qs, *inv, *kns, *vns, *rsq;  // shared memory: G*hd queries, hd/2 frequencies, hd + hd appended row, G + 1 reciprocal RMS values
+  float* rope_cache;                  // KvmCtx::rope_cache
 };
 static __device__ void kvm_part_prologue(const KvmPartPro& P) {
   const int hd = P.hd, half = hd / 2, G = P.G, b = P.b, kvh = P.kvh, n = P.p0 + 1;
@@ -227,13 +228,23 @@ static __device__ void kvm_part_prologue(const KvmPartPro& P) {
   }
   const float* gq = P.gam.p ? (const float*)P.gam.p : nullptr;
   const float* gk = P.gam.p ? (const float*)P.gam.p + P.gam.ld : nullptr;
+  const float* inv = P.inv;
   if (P.fl & 1) {
-    for (int i = threadIdx.x; i < half; i += KVM_NT) P.inv[i] = kvm_rope_inv(P.theta, i, hd);
-    kvm_sync();
+    // theta^(-2i/hd) is a double-precision pow per frequency: computed once per (theta, head dimension) and launch, not per task
+    float* rc = P.rope_cache;
+    const bool hit = rc && __float_as_int(rc[0]) == __float_as_int(P.theta) && __float_as_int(rc[1]) == hd;
+    if (rc) kvm_sync();                                      // every thread has looked at the key before anyone replaces it
+    if (!hit) {
+      float* dst = rc ? rc + 2 : P.inv;
+      for (int i = threadIdx.x; i < half; i += KVM_NT) dst[i] = kvm_rope_inv(P.theta, i, hd);
+      if (rc && threadIdx.x == 0) { rc[0] = P.theta; rc[1] = __int_as_float(hd); }
+      kvm_sync();
+    }
+    if (rc) inv = rc + 2;
   }
   if (P.appends) {
     for (int i = threadIdx.x; i < half; i += KVM_NT) {
-      float sn, co; sincosf(__fmul_rn((float)P.p0, P.inv[i]), &sn, &co);
+      float sn, co; sincosf(__fmul_rn((float)P.p0, inv[i]), &sn, &co);
       float x1 = kvm_ld(P.kn, (size_t)b * P.kn.ld + kvh * hd + i), x2 = kvm_ld(P.kn, (size_t)b * P.kn.ld + kvh * hd + i + half);
       if (gk) { x1 = x1 * P.rsq[G] * gk[i]; x2 = x2 * P.rsq[G] * gk[i + half]; }
       const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
@@ -252,7 +263,7 @@ static __device__ void kvm_part_prologue(const KvmPartPro& P) {
     float x1 = kvm_ld(P.q, (size_t)b * P.q.ld + h * hd + i), x2 = kvm_ld(P.q, (size_t)b * P.q.ld + h * hd + i + half);
     if (gq) { x1 = x1 * P.rsq[g] * gq[i]; x2 = x2 * P.rsq[g] * gq[i + half]; }
     if (P.fl & 1) {
-      float sn, co; sincosf(__fmul_rn((float)P.p0, P.inv[i]), &sn, &co);
+      float sn, co; sincosf(__fmul_rn((float)P.p0, inv[i]), &sn, &co);
       const float y1 = x1 * co - x2 * sn, y2 = x1 * sn + x2 * co;
       x1 = y1; x2 = y2;
       if (P.fl & 2) { x1 = kvm_bf16_round(x1); x2 = kvm_bf16_round(x2); }
@@ -282,6 +293,7 @@ static __device__ void kvm_attn_decode_part_op(const KvmCtx& c, const int32_t* a
   KvmPartPro P;
   P.q = q; P.kc = kc; P.vc = vc; P.kn = kn; P.vn = vn; P.gam = gam;
   P.b = b; P.kvh = kvh; P.G = G; P.hd = hd; P.fl = fl; P.p0 = p0; P.base = base; P.theta = theta; P.eps = qkn ? kvm_bits_f32(a[19]) : 0.0f;
+  P.rope_cache = c.rope_cache;
   P.appends = (fl & 1) && j0 <= n - 1 && n - 1 < j1;    // this split holds the newest key: it appends (rotated key), rounded to the cache dtype
   P.qs = (float*)(c.smem + KVM_AS_OFF_QS);                       // G*hd rotated queries
   P.inv = (float*)(c.smem + KVM_AS_OFF_INV);                     // hd/2 inverse frequencies
@@ -304,10 +316,10 @@ static __device__ void kvm_attn_decode_part_op(const KvmCtx& c, const int32_t* a
   if (kvm_decode_vec_ok(kc, vc, hd)) kvm_decode_group_vec(kc, vc, base, j0, j1, G, hd, sc, P.qs, ws, emit);
   else kvm_decode_group(kc, vc, base, j0, j1, G, hd, sc, P.qs, ws, emit);
 }
-static __device__ void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, false); }
-static __device__ void kvm_op_attn_decode_part_qkn(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, true); }
+KVM_OP_FN void kvm_op_attn_decode_part(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, false); }
+KVM_OP_FN void kvm_op_attn_decode_part_qkn(const KvmCtx& c, const int32_t* a) { kvm_attn_decode_part_op(c, a, true); }
 
-static __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, o;
   if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   const int b = a[2], h0 = a[3], h1 = a[4], S = a[5], H = a[6], hd = a[7];
@@ -317,16 +329,16 @@ static __device__ void kvm_op_attn_decode_merge(const KvmCtx& c, const int32_t* 
   for (int e = threadIdx.x; e < (h1 - h0) * hd; e += KVM_NT) {
     const int h = h0 + e / hd, cc = e % hd;
     float M = KVM_ATTN_EMPTY_M, L = 0.0f, A = 0.0f;
-    for (int s0 = 0; s0 < S; s0 += 8) {        // eight splits at a time: their loads are independent and issued together
-      float ms[8], ls[8], as[8];
+    for (int s0 = 0; s0 < S; s0 += 12) {       // twelve splits at a time: their loads are independent and issued together
+      float ms[12], ls[12], as[12];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 12; ++u) {
         const int s = s0 + u;
         const float* r = pp + ((size_t)(b * S + (s < S ? s : 0)) * H + h) * part.ld;
         ms[u] = r[hd]; ls[u] = s < S ? r[hd + 1] : 0.0f; as[u] = r[cc];
       }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) if (ls[u] > 0.0f) {      // split order, as the reference merges
+      for (int u = 0; u < 12; ++u) if (ls[u] > 0.0f) {      // split order, as the reference merges
         const float mn = fmaxf(M, ms[u]), ca = __expf(M - mn), cb = __expf(ms[u] - mn);
         L = L * ca + ls[u] * cb; A = A * ca + as[u] * cb; M = mn;
       }
@@ -429,8 +441,8 @@ static __device__ void kvm_gemv_op(const KvmCtx& c, const int32_t* a, int r0, in
     kvm_gemv_row(c, kvm_row_view(x, r), kvm_row_view(x2, r), gm, w, kvm_row_view(out, r), kvm_row_view(res, r), n0, n1, K, pro, eps);
   }
 }
-static __device__ void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, 0, 1); }
-static __device__ void kvm_op_gemv_bf16_rows(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, a[11], a[12]); }
+KVM_OP_FN void kvm_op_gemv_bf16(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, 0, 1); }
+KVM_OP_FN void kvm_op_gemv_bf16_rows(const KvmCtx& c, const int32_t* a) { kvm_gemv_op(c, a, a[11], a[12]); }
 
 // ---- sampling: Philox-4x32-10 counter (row, ctr, 0, 0), key (seed, 0x9E3779B9) (runtime/ref_gpt.py:488-506) --------------------------
 __device__ __forceinline__ float kvm_philox_uniform(unsigned seed, unsigned ctr, unsigned row) {
@@ -447,7 +459,7 @@ __device__ __forceinline__ unsigned kvm_order_key(float x) { const unsigned b = 
 
 // temp <= 0: argmax. Otherwise inverse-CDF over softmax(logits/temp) restricted to the topk largest (ties kept), weights and
 // running sum in double in index order by one thread (the reference's order; rows are short-lived serving rows).
-static __device__ void kvm_op_sample(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_sample(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, out, ctr;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, out) || !kvm_buf(c, a[2], KVM_M_I32, ctr, true)) return;
   const int r0 = a[3], r1 = a[4], V = a[5], topk = a[7];

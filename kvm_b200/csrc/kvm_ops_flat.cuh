@@ -87,7 +87,7 @@ __device__ __forceinline__ float kvm_tf32_round(float x) {
 }
 
 // ---- core pack: n elements from 0 --------------------------------------------------------------------------------------------
-static __device__ void kvm_op_copy(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_copy(const KvmCtx& c, const int32_t* a) {
   KvmBuf s, d;
   if (!kvm_buf(c, a[0], 7, s) || !kvm_buf(c, a[1], 7, d)) return;
   long long n = a[2];
@@ -96,14 +96,14 @@ static __device__ void kvm_op_copy(const KvmCtx& c, const int32_t* a) {
   if (s.dtype == KVM_BF16) { for (long long i = threadIdx.x; i < n; i += KVM_NT) ((uint16_t*)d.p)[i] = ((const uint16_t*)s.p)[i]; }
   else { for (long long i = threadIdx.x; i < n; i += KVM_NT) ((uint32_t*)d.p)[i] = ((const uint32_t*)s.p)[i]; }
 }
-static __device__ void kvm_op_add(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_add(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[2], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, in[1]) || !kvm_buf(c, a[2], KVM_M_FLT, o)) return;
   long long n = a[3];
   if (!kvm_range_ok(c, 0, n) || !kvm_flat_ok(c, in[0], n) || !kvm_flat_ok(c, in[1], n) || !kvm_flat_ok(c, o, n)) return;
   kvm_flat_map<2>(in, o, 0, n, [](const float (&x)[2]) { return __fadd_rn(x[0], x[1]); });
 }
-static __device__ void kvm_op_scale(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_scale(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   float al = kvm_bits_f32(a[2]);
@@ -111,7 +111,7 @@ static __device__ void kvm_op_scale(const KvmCtx& c, const int32_t* a) {
   if (!kvm_range_ok(c, 0, n) || !kvm_flat_ok(c, in[0], n) || !kvm_flat_ok(c, o, n)) return;
   kvm_flat_map<1>(in, o, 0, n, [al](const float (&x)[1]) { return __fmul_rn(x[0], al); });
 }
-static __device__ void kvm_op_relu(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_relu(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   long long n = a[2];
@@ -124,9 +124,9 @@ static __device__ void kvm_sgd_common(const KvmCtx& c, int wi, int gi, float lr,
   if (!kvm_range_ok(c, e0, e1) || !kvm_flat_ok(c, in[0], e1) || !kvm_flat_ok(c, in[1], e1)) return;
   kvm_flat_map<2>(in, in[0], e0, e1, [lr](const float (&x)[2]) { return __fsub_rn(x[0], __fmul_rn(lr, x[1])); });
 }
-static __device__ void kvm_op_sgd(const KvmCtx& c, const int32_t* a) { kvm_sgd_common(c, a[0], a[1], kvm_bits_f32(a[2]), 0, a[3]); }
-static __device__ void kvm_op_sgd_range(const KvmCtx& c, const int32_t* a) { kvm_sgd_common(c, a[0], a[1], kvm_bits_f32(a[2]), a[3], a[4]); }
-static __device__ void kvm_op_predict(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_sgd(const KvmCtx& c, const int32_t* a) { kvm_sgd_common(c, a[0], a[1], kvm_bits_f32(a[2]), 0, a[3]); }
+KVM_OP_FN void kvm_op_sgd_range(const KvmCtx& c, const int32_t* a) { kvm_sgd_common(c, a[0], a[1], kvm_bits_f32(a[2]), a[3], a[4]); }
+KVM_OP_FN void kvm_op_predict(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], w, o;
   if (!kvm_buf(c, a[0], KVM_M_F32, in[0]) || !kvm_buf(c, a[1], KVM_M_F32, w) || !kvm_buf(c, a[2], KVM_M_F32, o)) return;
   long long n = a[3];
@@ -135,7 +135,7 @@ static __device__ void kvm_op_predict(const KvmCtx& c, const int32_t* a) {
   kvm_flat_map<1>(in, o, 0, n, [w0](const float (&x)[1]) { return __fmul_rn(w0, x[0]); });
 }
 // loss[0] = mean((p-t)^2), grad[0] = mean(2(p-t)x): float32 sums in index order (runtime/ref_ops.py:44-52), so one thread.
-static __device__ void kvm_op_mse_grad(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_mse_grad(const KvmCtx& c, const int32_t* a) {
   KvmBuf p, t, x, l, g;
   if (!kvm_buf(c, a[0], KVM_M_F32, p) || !kvm_buf(c, a[1], KVM_M_F32, t) || !kvm_buf(c, a[2], KVM_M_F32, x) || !kvm_buf(c, a[3], KVM_M_F32, l) ||
       !kvm_buf(c, a[4], KVM_M_F32, g)) return;
@@ -152,7 +152,7 @@ static __device__ void kvm_op_mse_grad(const KvmCtx& c, const int32_t* a) {
     ((float*)g.p)[0] = (float)((double)ga / n);
   }
 }
-static __device__ void kvm_op_fill(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_fill(const KvmCtx& c, const int32_t* a) {
   KvmBuf x;
   if (!kvm_buf(c, a[0], 7, x)) return;
   long long n = a[2];
@@ -161,7 +161,7 @@ static __device__ void kvm_op_fill(const KvmCtx& c, const int32_t* a) {
   if (x.dtype == KVM_I32) { for (long long i = threadIdx.x; i < n; i += KVM_NT) ((int*)x.p)[i] = (int)v; }
   else { for (long long i = threadIdx.x; i < n; i += KVM_NT) kvm_st(x, i, v); }
 }
-static __device__ void kvm_op_spin(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_spin(const KvmCtx& c, const int32_t* a) {
   if (threadIdx.x == 0) {
     unsigned long long t0 = kvm_globaltimer(), lim = (unsigned long long)(a[0] < 0 ? 0 : (a[0] > 1000000 ? 1000000 : a[0])) * 1000ull;
     while (kvm_globaltimer() - t0 < lim) __nanosleep(200);
@@ -169,7 +169,7 @@ static __device__ void kvm_op_spin(const KvmCtx& c, const int32_t* a) {
 }
 
 // ---- GPT / extra packs -----------------------------------------------------------------------------------------------------------
-static __device__ void kvm_op_gelu_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_gelu_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   if (!kvm_range_ok(c, a[2], a[3]) || !kvm_flat_ok(c, in[0], a[3]) || !kvm_flat_ok(c, o, a[3])) return;
@@ -187,10 +187,10 @@ __device__ __forceinline__ void kvm_bwd_map(const KvmCtx& c, int xi, int dyi, in
     kvm_flat_map<2>(in2, in[2], e0, e1, [grad](const float (&x)[2]) { return __fmul_rn(x[1], grad(x[0])); });
   }
 }
-static __device__ void kvm_op_gelu_bwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_gelu_bwd(const KvmCtx& c, const int32_t* a) {
   kvm_bwd_map(c, a[0], a[1], a[2], a[3], a[4], a[5], [](float x) { return kvm_gelu_grad(x); });
 }
-static __device__ void kvm_op_act_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_act_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   int kind = a[2];
@@ -198,44 +198,44 @@ static __device__ void kvm_op_act_fwd(const KvmCtx& c, const int32_t* a) {
   if (!kvm_range_ok(c, a[3], a[4]) || !kvm_flat_ok(c, in[0], a[4]) || !kvm_flat_ok(c, o, a[4])) return;
   kvm_flat_map<1>(in, o, a[3], a[4], [kind](const float (&x)[1]) { return kvm_act(kind, x[0]); });
 }
-static __device__ void kvm_op_act_bwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_act_bwd(const KvmCtx& c, const int32_t* a) {
   int kind = a[3];
   if (kind < 0 || kind > 3) { c.fail(KVM_OPE_RANGE, kind); return; }
   kvm_bwd_map(c, a[0], a[1], a[2], a[4], a[5], a[6], [kind](float x) { return kvm_act_grad(kind, x); });
 }
-static __device__ void kvm_op_silu_mul_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_silu_mul_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[2], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, in[1]) || !kvm_buf(c, a[2], KVM_M_FLT, o)) return;
   if (!kvm_range_ok(c, a[3], a[4]) || !kvm_flat_ok(c, in[0], a[4]) || !kvm_flat_ok(c, in[1], a[4]) || !kvm_flat_ok(c, o, a[4])) return;
   kvm_flat_map<2>(in, o, a[3], a[4], [](const float (&x)[2]) { return kvm_silu(x[0]) * x[1]; });
 }
-static __device__ void kvm_op_residual_add(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_residual_add(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[2], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, in[1]) || !kvm_buf(c, a[2], KVM_M_FLT, o)) return;
   if (!kvm_range_ok(c, a[3], a[4]) || !kvm_flat_ok(c, in[0], a[4]) || !kvm_flat_ok(c, in[1], a[4]) || !kvm_flat_ok(c, o, a[4])) return;
   kvm_flat_map<2>(in, o, a[3], a[4], [](const float (&x)[2]) { return __fadd_rn(x[0], x[1]); });
 }
-static __device__ void kvm_op_round_tf32(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_round_tf32(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_F32, in[0]) || !kvm_buf(c, a[1], KVM_M_F32, o)) return;
   if (!kvm_range_ok(c, a[2], a[3]) || !kvm_flat_ok(c, in[0], a[3]) || !kvm_flat_ok(c, o, a[3])) return;
   kvm_flat_map<1>(in, o, a[2], a[3], [](const float (&x)[1]) { return kvm_tf32_round(x[0]); });
 }
 // f32 -> bf16 narrows (RNE), bf16 -> f32 widens, f32 -> f32 emulates, bf16 -> bf16 copies (include/mvm_ops_extra.def:63-66).
-static __device__ void kvm_op_round_bf16(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_round_bf16(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   if (!kvm_range_ok(c, a[2], a[3]) || !kvm_flat_ok(c, in[0], a[3]) || !kvm_flat_ok(c, o, a[3])) return;
   kvm_flat_map<1>(in, o, a[2], a[3], [](const float (&x)[1]) { return kvm_bf16_round(x[0]); });
 }
-static __device__ void kvm_op_scale_flat(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_scale_flat(const KvmCtx& c, const int32_t* a) {
   KvmBuf in[1], o;
   if (!kvm_buf(c, a[0], KVM_M_FLT, in[0]) || !kvm_buf(c, a[1], KVM_M_FLT, o)) return;
   float al = kvm_bits_f32(a[2]);
   if (!kvm_range_ok(c, a[3], a[4]) || !kvm_flat_ok(c, in[0], a[4]) || !kvm_flat_ok(c, o, a[4])) return;
   kvm_flat_map<1>(in, o, a[3], a[4], [al](const float (&x)[1]) { return __fmul_rn(al, x[0]); });
 }
-static __device__ void kvm_op_zero_buf(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_zero_buf(const KvmCtx& c, const int32_t* a) {
   KvmBuf x;
   if (!kvm_buf(c, a[0], 7, x)) return;
   long long e0 = a[1], e1 = a[2];
@@ -243,14 +243,14 @@ static __device__ void kvm_op_zero_buf(const KvmCtx& c, const int32_t* a) {
   if (x.dtype == KVM_BF16) { for (long long i = e0 + threadIdx.x; i < e1; i += KVM_NT) ((uint16_t*)x.p)[i] = 0; }
   else { for (long long i = e0 + threadIdx.x; i < e1; i += KVM_NT) ((uint32_t*)x.p)[i] = 0; }
 }
-static __device__ void kvm_op_counter_inc(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_counter_inc(const KvmCtx& c, const int32_t* a) {
   KvmBuf x;
   if (!kvm_buf(c, a[0], KVM_M_I32, x)) return;
   if (!kvm_range_ok(c, a[1], a[2]) || !kvm_flat_ok(c, x, a[2])) return;
   for (long long i = a[1] + threadIdx.x; i < a[2]; i += KVM_NT) ((unsigned*)x.p)[i] += (unsigned)a[3];
 }
 // dst[i] = src[step[0]*stride + off + i], any 4-byte dtype (include/mvm_ops_gpt.def:86-88).
-static __device__ void kvm_op_select_window(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_select_window(const KvmCtx& c, const int32_t* a) {
   KvmBuf s, st, d;
   if (!kvm_buf(c, a[0], KVM_M_F32 | KVM_M_I32, s) || !kvm_buf(c, a[1], KVM_M_I32, st) || !kvm_buf(c, a[2], KVM_M_F32 | KVM_M_I32, d)) return;
   if (s.dtype != d.dtype) { c.fail(KVM_OPE_DTYPE, a[0], a[2]); return; }

@@ -101,16 +101,16 @@ static __device__ void kvm_mm_simt(const KvmCtx& c, const KvmMmArgs& g) {
     }
 }
 
-static __device__ void kvm_op_matmul_tile(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_matmul_tile(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g;
   if (kvm_mm_args(c, a, 0, g)) kvm_mm_simt(c, g);
 }
-static __device__ void kvm_op_matmul_tile_bf16(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_matmul_tile_bf16(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g;
   if (kvm_mm_args(c, a, 1, g)) kvm_mm_simt(c, g);
 }
 // out[m,n] = a[m,k] @ b[k,n] from element 0, contiguous (include/mvm_ops.def:14; runtime/ref_ops.py:55-64).
-static __device__ void kvm_op_matmul(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_matmul(const KvmCtx& c, const int32_t* a) {
   KvmMmArgs g{};
   if (!kvm_buf(c, a[0], KVM_M_F32, g.a) || !kvm_buf(c, a[1], KVM_M_F32, g.b) || !kvm_buf(c, a[2], KVM_M_F32, g.out)) return;
   const int m = a[3], n = a[4], k = a[5];

@@ -6,7 +6,7 @@
 #include "kvm_dev.cuh"
 
 // ---- embeddings --------------------------------------------------------------------------------------------------------------
-static __device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf ids, wte, wpe, out;
   if (!kvm_buf(c, a[0], KVM_M_I32, ids) || !kvm_buf(c, a[1], KVM_M_FLT, wte) || !kvm_buf(c, a[2], KVM_M_FLT, wpe, true) ||
       !kvm_buf(c, a[3], KVM_M_FLT, out)) return;
@@ -30,7 +30,7 @@ static __device__ void kvm_op_embedding_fwd(const KvmCtx& c, const int32_t* a) {
 // One task owns keys [v0,v1): rows with a key in range are compacted in ascending order into shared memory (block-wide
 // ordered scan), then added row by row, each thread owning columns, so every element sums its rows in ascending order
 // with one float32 add each (runtime/ref_gpt.py:55-66).
-static __device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf ids, dout, dt;
   if (!kvm_buf(c, a[0], KVM_M_I32, ids, true) || !kvm_buf(c, a[1], KVM_M_FLT, dout) || !kvm_buf(c, a[2], KVM_M_F32, dt)) return;
   int N = a[3], mod = a[4], v0 = a[5], v1 = a[6], d = a[7], acc = a[8];
@@ -87,7 +87,7 @@ static __device__ void kvm_op_embedding_bwd(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-static __device__ void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, pos, out;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, pos) || !kvm_buf(c, a[2], KVM_M_FLT, out)) return;
   int r0 = a[3], r1 = a[4], T = a[5], d = a[6];
@@ -99,7 +99,7 @@ static __device__ void kvm_op_add_rowtile(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-static __device__ void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_gather_rows(const KvmCtx& c, const int32_t* a) {
   KvmBuf src, idx, dst;
   if (!kvm_buf(c, a[0], KVM_M_FLT, src) || !kvm_buf(c, a[1], KVM_M_I32, idx) || !kvm_buf(c, a[2], KVM_M_FLT, dst)) return;
   int r0 = a[3], r1 = a[4], d = a[5];
@@ -193,10 +193,10 @@ static __device__ void kvm_norm_fwd(const KvmCtx& c, int xi, int gi, int bi, int
     if (lane == 0) { ((float*)rstd.p)[r] = rs; if (!RMS) ((float*)mean.p)[r] = mu; }
   }
 }
-static __device__ void kvm_op_layernorm_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_layernorm_fwd(const KvmCtx& c, const int32_t* a) {
   kvm_norm_fwd<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], kvm_bits_f32(a[9]));
 }
-static __device__ void kvm_op_rmsnorm_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_rmsnorm_fwd(const KvmCtx& c, const int32_t* a) {
   kvm_norm_fwd<true>(c, a[0], a[1], -1, a[2], -1, a[3], a[4], a[5], a[6], kvm_bits_f32(a[7]));
 }
 
@@ -254,28 +254,54 @@ static __device__ void kvm_norm_bwd_dx(const KvmCtx& c, int xi, int dyi, int gi,
     }
   }
 }
-static __device__ void kvm_op_layernorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9]); }
-static __device__ void kvm_op_rmsnorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<true>(c, a[0], a[1], a[2], -1, a[3], a[4], a[5], a[6], a[7], a[8]); }
+KVM_OP_FN void kvm_op_layernorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<false>(c, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9]); }
+KVM_OP_FN void kvm_op_rmsnorm_bwd_dx(const KvmCtx& c, const int32_t* a) { kvm_norm_bwd_dx<true>(c, a[0], a[1], a[2], -1, a[3], a[4], a[5], a[6], a[7], a[8]); }
 
 // Column sums over R rows for columns [c0,c1): thread = (row group, column), row groups reduced in fixed order through
 // shared memory.  MODE 0: colsum of x; MODE 1: dgamma / dbeta of a norm layer.
-template <int MODE>
-static __device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy, const KvmBuf& mean, const KvmBuf& rstd, float* o1, float* o2,
-                              int R, int c0, int c1, int acc) {
+template <int MODE, bool XB, bool YB>
+static __device__ void kvm_colreduce_t(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy, const KvmBuf& mean, const KvmBuf& rstd, float* o1, float* o2,
+                                       int R, int c0, int c1, int acc) {
   float* red = (float*)c.smem;                    // [2][KVM_NT]
+  const void* xp = x.p;
+  const void* yp = dy.p;
+  const float* mp = (const float*)mean.p;
+  const float* rp = (const float*)rstd.p;
+  const size_t xld = x.ld, yld = MODE == 1 ? dy.ld : 0;
   for (int cb = c0; cb < c1; cb += 64) {
     const int w = min(64, c1 - cb), col = threadIdx.x & 63, rg = threadIdx.x >> 6, ngroups = KVM_NT / 64;
     float s1 = 0.0f, s2 = 0.0f;
-    if (col < w)
-      for (int r = rg; r < R; r += ngroups) {
-        if (MODE == 0) s1 += kvm_ld(x, (size_t)r * x.ld + cb + col);
+    if (col < w) {
+      // latency-bound (one short load per row): eight rows' loads are issued before the first is used; the sums run in row order
+      int r = rg;
+      for (; r + 7 * ngroups < R; r += 8 * ngroups) {
+        float xv[8], gv[8], mu[8], rs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int rr = r + u * ngroups;
+          xv[u] = kvm_ldt<XB>(xp, (size_t)rr * xld + cb + col);
+          if (MODE == 1) {
+            gv[u] = kvm_ldt<YB>(yp, (size_t)rr * yld + cb + col);
+            mu[u] = mp ? mp[rr] : 0.0f;
+            rs[u] = rp[rr];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (MODE == 0) s1 += xv[u];
+          else { s1 += gv[u] * (xv[u] - mu[u]) * rs[u]; s2 += gv[u]; }
+        }
+      }
+      for (; r < R; r += ngroups) {
+        if (MODE == 0) s1 += kvm_ldt<XB>(xp, (size_t)r * xld + cb + col);
         else {
-          float g = kvm_ld(dy, (size_t)r * dy.ld + cb + col);
-          float mu = mean.p ? ((const float*)mean.p)[r] : 0.0f;
-          s1 += g * (kvm_ld(x, (size_t)r * x.ld + cb + col) - mu) * ((const float*)rstd.p)[r];
+          const float g = kvm_ldt<YB>(yp, (size_t)r * yld + cb + col);
+          const float mu = mp ? mp[r] : 0.0f;
+          s1 += g * (kvm_ldt<XB>(xp, (size_t)r * xld + cb + col) - mu) * rp[r];
           s2 += g;
         }
       }
+    }
     kvm_sync();
     red[threadIdx.x] = s1; red[KVM_NT + threadIdx.x] = s2;
     kvm_sync();
@@ -288,14 +314,31 @@ static __device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const Kvm
     }
   }
 }
-static __device__ void kvm_op_colsum(const KvmCtx& c, const int32_t* a) {
+// Column sums over R rows for columns [c0,c1): thread = (row group, column), row groups reduced in fixed order through
+// shared memory.  MODE 0: colsum of x; MODE 1: dgamma / dbeta of a norm layer.  One instance per storage type of x (and dy).
+template <int MODE>
+static __device__ void kvm_colreduce(const KvmCtx& c, const KvmBuf& x, const KvmBuf& dy, const KvmBuf& mean, const KvmBuf& rstd, float* o1, float* o2,
+                              int R, int c0, int c1, int acc) {
+  const bool xb = x.dtype == KVM_BF16, yb = MODE == 1 && dy.dtype == KVM_BF16;
+  if (MODE == 0) {
+    if (xb) kvm_colreduce_t<MODE, true, false>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+    else kvm_colreduce_t<MODE, false, false>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+  } else if (xb) {
+    if (yb) kvm_colreduce_t<MODE, true, true>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+    else kvm_colreduce_t<MODE, true, false>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+  } else {
+    if (yb) kvm_colreduce_t<MODE, false, true>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+    else kvm_colreduce_t<MODE, false, false>(c, x, dy, mean, rstd, o1, o2, R, c0, c1, acc);
+  }
+}
+KVM_OP_FN void kvm_op_colsum(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, out, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_F32, out)) return;
   int R = a[2], c0 = a[3], c1 = a[4];
   if (R < 0 || c0 < 0 || c1 < c0 || !kvm_mat_ok(c, x, R, c1) || !kvm_flat_ok(c, out, c1)) { c.fail(KVM_OPE_RANGE, c0, c1); return; }
   kvm_colreduce<0>(c, x, none, none, none, (float*)out.p, nullptr, R, c0, c1, a[5]);
 }
-static __device__ void kvm_op_norm_bwd_params(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_norm_bwd_params(const KvmCtx& c, const int32_t* a) {
   KvmBuf x, dy, mean, rstd, dg, db;
   if (!kvm_buf(c, a[0], KVM_M_FLT, x) || !kvm_buf(c, a[1], KVM_M_FLT, dy) || !kvm_buf(c, a[2], KVM_M_F32, mean, true) || !kvm_buf(c, a[3], KVM_M_F32, rstd) ||
       !kvm_buf(c, a[4], KVM_M_F32, dg) || !kvm_buf(c, a[5], KVM_M_F32, db, true)) return;
@@ -331,14 +374,14 @@ static __device__ void kvm_rope(const KvmCtx& c, const int32_t* a, float sign) {
     kvm_st(out, w1 + half, x1 * s + x2 * co);
   }
 }
-static __device__ void kvm_op_rope_fwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, 1.0f); }
-static __device__ void kvm_op_rope_bwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, -1.0f); }
+KVM_OP_FN void kvm_op_rope_fwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, 1.0f); }
+KVM_OP_FN void kvm_op_rope_bwd(const KvmCtx& c, const int32_t* a) { kvm_rope(c, a, -1.0f); }
 
 // ---- cross entropy: the block walks rows; per row one pass for (max, sum) and one for the gradient -------------------------------------
 // MODE bit 0: forward (rowloss, lse); bit 1: backward (dlogits).
-template <int MODE>
-static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V,
-                       int ignore, float f) {
+template <int MODE, bool LB, bool DB>      // storage types of the logits and of their gradient as template arguments: no type test inside the loops
+static __device__ void kvm_ce_t(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V,
+                         int ignore, float f) {
   float* red = (float*)c.smem;
   const bool vec = (V & 7) == 0 && (lg.ld & 7) == 0 && kvm_vec_ok(lg) && (!(MODE & 2) || ((dl.ld & 7) == 0 && kvm_vec_ok(dl)));
   for (int r = r0; r < r1; ++r) {
@@ -351,7 +394,7 @@ static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& t
       else {
         float m = -INFINITY, s = 0.0f;            // online (max, sum) per thread
         if (vec) for (int k = threadIdx.x * 8; k < V; k += KVM_NT * 8) {
-          float v[8]; kvm_ld8(lg, lo + k, v);
+          float v[8]; kvm_ld8t<LB>(lg.p, lo + k, v);
           float mm = v[0];
 #pragma unroll
           for (int j = 1; j < 8; ++j) mm = fmaxf(mm, v[j]);
@@ -359,7 +402,7 @@ static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& t
 #pragma unroll
           for (int j = 0; j < 8; ++j) s += __expf(v[j] - m);
         } else for (int k = threadIdx.x; k < V; k += KVM_NT) {
-          float v = kvm_ld(lg, lo + k);
+          float v = kvm_ldt<LB>(lg.p, lo + k);
           if (v > m) { s *= __expf(m - v); m = v; }
           s += __expf(v - m);
         }
@@ -373,34 +416,41 @@ static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& t
     if (MODE & 2) {
       const size_t dq = (size_t)r * dl.ld;
       if (vec) for (int k = threadIdx.x * 8; k < V; k += KVM_NT * 8) {
-        float v[8], o[8]; kvm_ld8(lg, lo + k, v);
+        float v[8], o[8]; kvm_ld8t<LB>(lg.p, lo + k, v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = t == ignore ? 0.0f : (__expf(v[j] - lse) - (k + j == t ? 1.0f : 0.0f)) * f;
-        kvm_st8(dl, dq + k, o);
+        kvm_st8t<DB>(dl.p, dq + k, o);
       } else for (int k = threadIdx.x; k < V; k += KVM_NT)
-        kvm_st(dl, dq + k, t == ignore ? 0.0f : (__expf(kvm_ld(lg, lo + k) - lse) - (k == t ? 1.0f : 0.0f)) * f);
+        kvm_st(dl, dq + k, t == ignore ? 0.0f : (__expf(kvm_ldt<LB>(lg.p, lo + k) - lse) - (k == t ? 1.0f : 0.0f)) * f);
     }
   }
+}
+template <int MODE>
+static __device__ void kvm_ce(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V,
+                       int ignore, float f) {
+  const bool lb = lg.dtype == KVM_BF16, db = (MODE & 2) && dl.dtype == KVM_BF16;
+  if (lb) { if (db) kvm_ce_t<MODE, true, true>(c, lg, tg, rl, ls, dl, r0, r1, V, ignore, f); else kvm_ce_t<MODE, true, false>(c, lg, tg, rl, ls, dl, r0, r1, V, ignore, f); }
+  else { if (db) kvm_ce_t<MODE, false, true>(c, lg, tg, rl, ls, dl, r0, r1, V, ignore, f); else kvm_ce_t<MODE, false, false>(c, lg, tg, rl, ls, dl, r0, r1, V, ignore, f); }
 }
 static __device__ bool kvm_ce_args(const KvmCtx& c, const KvmBuf& lg, const KvmBuf& tg, const KvmBuf& rl, const KvmBuf& ls, const KvmBuf& dl, int r0, int r1, int V) {
   if (r0 < 0 || r1 < r0 || V <= 0 || !kvm_mat_ok(c, lg, r1, V) || !kvm_flat_ok(c, tg, r1) || !kvm_flat_ok(c, rl, r1) || !kvm_flat_ok(c, ls, r1) ||
       !kvm_mat_ok(c, dl, r1, V)) { c.fail(KVM_OPE_RANGE, r0, r1); return false; }
   return true;
 }
-static __device__ void kvm_op_softmax_ce_fwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_softmax_ce_fwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, rl, ls, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, rl) || !kvm_buf(c, a[3], KVM_M_F32, ls)) return;
   if (!kvm_ce_args(c, lg, tg, rl, ls, none, a[4], a[5], a[6])) return;
   kvm_ce<1>(c, lg, tg, rl, ls, none, a[4], a[5], a[6], a[7], 0.0f);
 }
-static __device__ void kvm_op_softmax_ce_bwd(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_softmax_ce_bwd(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, ls, loss, dl, none{};
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, ls) || !kvm_buf(c, a[3], KVM_M_F32, loss) ||
       !kvm_buf(c, a[4], KVM_M_FLT, dl)) return;
   if (!kvm_ce_args(c, lg, tg, none, ls, dl, a[5], a[6], a[7]) || !kvm_flat_ok(c, loss, 2)) return;
   kvm_ce<2>(c, lg, tg, none, ls, dl, a[5], a[6], a[7], a[8], __fmul_rn(((const float*)loss.p)[1], kvm_bits_f32(a[9])));
 }
-static __device__ void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, tg, rl, ls, dl;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, rl) || !kvm_buf(c, a[3], KVM_M_F32, ls) ||
       !kvm_buf(c, a[4], KVM_M_FLT, dl)) return;
@@ -409,7 +459,7 @@ static __device__ void kvm_op_softmax_ce_fused(const KvmCtx& c, const int32_t* a
   kvm_ce<3>(c, lg, tg, rl, ls, dl, a[5], a[6], a[7], -1, __fmul_rn((float)(1.0 / (double)a[9]), kvm_bits_f32(a[10])));
 }
 // loss[0] = mean rowloss over non-ignored rows, loss[1] = 1/count (runtime/ref_gpt.py:430-437); double sums, fixed tree.
-static __device__ void kvm_op_softmax_ce_reduce(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_softmax_ce_reduce(const KvmCtx& c, const int32_t* a) {
   KvmBuf rl, tg, loss;
   if (!kvm_buf(c, a[0], KVM_M_F32, rl) || !kvm_buf(c, a[1], KVM_M_I32, tg) || !kvm_buf(c, a[2], KVM_M_F32, loss)) return;
   int N = a[3], ign = a[4];
@@ -469,10 +519,10 @@ static __device__ void kvm_adamw(const KvmCtx& c, const int32_t* a, bool lr_buf)
   }
   for (long long i = e0 + body + threadIdx.x; i < e1; i += KVM_NT) upd(pp[i], kvm_ld(g, i), mp[i], vp[i], pp[i], mp[i], vp[i]);
 }
-static __device__ void kvm_op_adamw(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, false); }
-static __device__ void kvm_op_adamw_lr(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, true); }
+KVM_OP_FN void kvm_op_adamw(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, false); }
+KVM_OP_FN void kvm_op_adamw_lr(const KvmCtx& c, const int32_t* a) { kvm_adamw(c, a, true); }
 
-static __device__ void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
   KvmBuf st, lr;
   if (!kvm_buf(c, a[0], KVM_M_I32, st) || !kvm_buf(c, a[1], KVM_M_F32, lr)) return;
   int kind = a[2], warmup = a[4], total = a[5];
@@ -487,7 +537,7 @@ static __device__ void kvm_op_lr_schedule(const KvmCtx& c, const int32_t* a) {
   }
 }
 
-static __device__ void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a) {
   KvmBuf g, part;
   if (!kvm_buf(c, a[0], KVM_M_FLT, g) || !kvm_buf(c, a[1], KVM_M_F32, part)) return;
   int slot = a[2];
@@ -507,7 +557,7 @@ static __device__ void kvm_op_gradnorm_partial(const KvmCtx& c, const int32_t* a
   s = kvm_block_sum(s, (double*)c.smem);
   if (threadIdx.x == 0) ((float*)part.p)[slot] = (float)s;
 }
-static __device__ void kvm_op_gradnorm_finish(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_gradnorm_finish(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, out;
   if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[2], KVM_M_F32, out)) return;
   int ns = a[1];
@@ -547,7 +597,7 @@ static __device__ void kvm_argmax_rows(const KvmCtx& c, const KvmBuf& lg, const 
     }
   }
 }
-static __device__ void kvm_op_argmax(const KvmCtx& c, const int32_t* a) {
+KVM_OP_FN void kvm_op_argmax(const KvmCtx& c, const int32_t* a) {
   KvmBuf lg, out;
   if (!kvm_buf(c, a[0], KVM_M_FLT, lg) || !kvm_buf(c, a[1], KVM_M_I32, out)) return;
   if (a[2] < 0 || a[3] < a[2] || a[4] <= 0 || !kvm_mat_ok(c, lg, a[3], a[4]) || !kvm_flat_ok(c, out, a[3])) { c.fail(KVM_OPE_RANGE, a[2], a[3]); return; }

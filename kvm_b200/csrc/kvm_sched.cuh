@@ -220,11 +220,12 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
   extern __shared__ __align__(1024) unsigned char kvm_smem[];
   KvmSlot* slots = (KvmSlot*)kvm_smem;                 // the slot ring
   int* ctl = (int*)(kvm_smem + KVM_NSLOT * sizeof(KvmSlot));   // ctl[0] = TMEM base, ctl[1..] scratch
-  static_assert(KVM_NSLOT * sizeof(KvmSlot) + 96 * sizeof(int) <= KVM_EXEC_SMEM_HDR, "header too small");
+  static_assert(KVM_NSLOT * sizeof(KvmSlot) + 96 * sizeof(int) + 288 <= KVM_EXEC_SMEM_HDR, "header too small");      // slots | control words | ... | rope cache (288)
   const int tid = threadIdx.x;
   const bool is_sched = tid >= KVM_NT && tid < KVM_NT + 32;
   const int engine_role = tid == KVM_NT + 32 ? 1 : tid == KVM_NT + 64 ? 2 : 0;      // one thread each: TMA producer, MMA issuer
   if (tid < KVM_NSLOT) { slots[tid].state = 0; slots[tid].task = -1; slots[tid].seq = 0; slots[tid].kind = 0; }
+  if (tid == 0) { ((int*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288))[0] = 0; ((int*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288))[1] = 0; }      // rope cache: no key yet
   unsigned dyn;
   asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   kvm_tc_init(ctl, kvm_smem);                          // TMEM allocation + mbarrier init (whole CTA)
@@ -408,6 +409,7 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
     const int used = used_hdr;
     c.smem = kvm_smem + used; c.smem_bytes = (int)dyn - used;
     c.engine = engine_on ? 1 : 0; c.gemm_seq = 0;
+    c.rope_cache = (float*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288);
     unsigned tiles = 0;
     int cur = 0;
     while (true) {

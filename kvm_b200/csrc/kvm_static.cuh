@@ -21,7 +21,6 @@
 
 #define KVM_ST_SLOTS 4                 // record ring depth (tasks fetched ahead)
 #define KVM_ST_HDR 3072                // header bytes: slots, control words, barriers
-#define KVM_ST_MMA_WARPS 8             // warps of the rows consumer that multiply (each a slice of the chunk's k)
 #define KVM_ST_ARRIVALS 16             // arrivals that free a stage: every compute warp, once it is done with the stage (or has nothing to do with it)
 
 struct KvmStSlot {
@@ -39,7 +38,7 @@ struct KvmStSlot {
   int j0, j1, newrow;         // attention: key range of the split, index of the appended key inside it (-1 none)
   KvmBuf lb[7];               // streamed tasks: the buffer-table entries of the task's buffer arguments (argument j -> lb[j]), looked up once by the front warp
 };
-static_assert(sizeof(KvmStSlot) * KVM_ST_SLOTS + 128 * 4 + 64 <= KVM_ST_HDR, "static header too small");
+static_assert(sizeof(KvmStSlot) * KVM_ST_SLOTS + 128 * 4 + 64 + 288 + 128 <= KVM_ST_HDR, "static header too small");      // slots | control words | ... | rope cache (288) | ring barriers (128)
 
 __device__ __forceinline__ bool kvm_mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -92,7 +91,7 @@ __device__ __forceinline__ bool kvm_ring_wait_warp(const KvmRing& ring, unsigned
 // Stage use `cit + ci` holds rows n0 + ci*R .. of the weight matrix in full (R*K*2 bytes).  All sixteen warps consume: warp = (row r of the
 // stage, part of K); the activation row v = bf16(prologue(x)) is staged once as bf16.  Partial sums are added in part order.
 // Semantics as kvm_op_gemv_bf16 (runtime/ref_extra.py:398-415).  Always consumes its nchunks stage uses, also after an error.
-static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline,
+KVM_OP_FN void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int R, int NC, unsigned long long deadline,
                                      unsigned long long t_task, int* stamp) {
   KvmBuf x, x2, gm, w, out, res;
   const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9];
@@ -111,7 +110,30 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
   kvm_sync();                                              // the previous task is done with the scratch
   if (ok) {
     // ---- prologue: v = bf16(pro(x)) (all 16 warps)
-    if (pro == 1 && K <= 16 * KVM_NT) {
+    if (pro == 1 && K <= 16 * KVM_NT && x.dtype == KVM_F32 && kvm_vec_ok(x) && kvm_vec_ok(gm)) {
+      // float32 row of up to 8192 values: four 16-byte loads of x and of gamma per thread, all in flight together (no storage-type
+      // test between them: with one, every load waits for the one before it), the row stays in registers for the statistics
+      float4 xr[4], gr[4];
+      float q = 0.0f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = (tid + u * KVM_NT) * 4;
+        xr[u] = k < K ? *(const float4*)((const float*)x.p + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        gr[u] = k < K ? *(const float4*)((const float*)gm.p + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q += xr[u].x * xr[u].x + xr[u].y * xr[u].y + xr[u].z * xr[u].z + xr[u].w * xr[u].w;
+      q = kvm_block_sum(q, red);
+      const float rs = 1.0f / sqrtf(q / K + eps);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = (tid + u * KVM_NT) * 4;
+        if (k < K) {
+          *(__nv_bfloat162*)(vs + k) = __floats2bfloat162_rn(xr[u].x * rs * gr[u].x, xr[u].y * rs * gr[u].y);
+          *(__nv_bfloat162*)(vs + k + 2) = __floats2bfloat162_rn(xr[u].z * rs * gr[u].z, xr[u].w * rs * gr[u].w);
+        }
+      }
+    } else if (pro == 1 && K <= 16 * KVM_NT) {
       float xr[16], gr[16], q = 0.0f;
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
@@ -131,6 +153,26 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
       q = kvm_block_sum(q, red);
       const float rs = 1.0f / sqrtf(q / K + eps);
       for (int k = tid; k < K; k += KVM_NT) vs[k] = __float2bfloat16_rn(kvm_ld(x, k) * rs * ((const float*)gm.p)[k]);
+    } else if (x.dtype == KVM_F32 && kvm_vec_ok(x) && (pro != 2 || (x2.dtype == KVM_F32 && kvm_vec_ok(x2)))) {
+      // three 16-byte loads per input and thread in flight per round (a 12288-wide SwiGLU row is two rounds)
+      for (int k0 = 0; k0 < K; k0 += 12 * KVM_NT) {
+        float4 p[3], q[3];
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+          const int k = k0 + (tid + u * KVM_NT) * 4;
+          p[u] = k < K ? *(const float4*)((const float*)x.p + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          q[u] = (pro == 2 && k < K) ? *(const float4*)((const float*)x2.p + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+          const int k = k0 + (tid + u * KVM_NT) * 4;
+          if (k < K) {
+            const float4 v = pro == 2 ? make_float4(kvm_silu(p[u].x) * q[u].x, kvm_silu(p[u].y) * q[u].y, kvm_silu(p[u].z) * q[u].z, kvm_silu(p[u].w) * q[u].w) : p[u];
+            *(__nv_bfloat162*)(vs + k) = __floats2bfloat162_rn(v.x, v.y);
+            *(__nv_bfloat162*)(vs + k + 2) = __floats2bfloat162_rn(v.z, v.w);
+          }
+        }
+      }
     } else {
       for (int k0 = 0; k0 < K; k0 += 8 * KVM_NT) {
         float p[8], q[8];
@@ -155,6 +197,11 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
   {
     const int r = warp / KP, part = warp % KP;
     const int plen = (((K + KP - 1) / KP) + 255) & ~255, kb = part * plen, ke = min(K, kb + plen);
+    // the warp's slice of the activations stays in registers for the whole task (at most 2048 values: eight 16-byte pieces per
+    // lane), so a stage costs one pass over its weights in shared memory and nothing else
+    uint4 xr[8];
+#pragma unroll
+    for (int sg = 0; sg < 8; ++sg) { const int k = kb + sg * 256 + lane * 8; xr[sg] = k < ke ? *(const uint4*)(vs + k) : make_uint4(0, 0, 0, 0); }
     for (int ci = 0; ci < NC; ++ci) {
       const unsigned it = cit + ci;
       unsigned long long tw = 0;
@@ -163,28 +210,24 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
       if (stamp && tid == 0) { const unsigned long long d = kvm_globaltimer() - tw; t_wait += d; if (ci == 0) t_first = d; }
       if (!waited) break;                                  // warp-uniform
       if (ok && r < R && ci * R + r < rows) {
-        const unsigned char* st = kvm_ring_stage(ring, it) + (size_t)r * K * 2;
+        const unsigned char* st = kvm_ring_stage(ring, it) + (size_t)r * K * 2 + (size_t)(kb + lane * 8) * 2;
         float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
-        int k = kb + lane * 8;
-        for (; k + 256 < ke; k += 512) {                   // two 16-byte pieces of the row and of the activations in flight per trip
-          const uint4 wa = *(const uint4*)(st + k * 2), wb = *(const uint4*)(st + (k + 256) * 2);
-          const uint4 xa = *(const uint4*)(vs + k), xb = *(const uint4*)(vs + k + 256);
-          acc0 = fmaf(kvm_bf16lo(xa.x), kvm_bf16lo(wa.x), acc0); acc1 = fmaf(kvm_bf16hi(xa.x), kvm_bf16hi(wa.x), acc1);
-          acc2 = fmaf(kvm_bf16lo(xb.x), kvm_bf16lo(wb.x), acc2); acc3 = fmaf(kvm_bf16hi(xb.x), kvm_bf16hi(wb.x), acc3);
-          acc0 = fmaf(kvm_bf16lo(xa.y), kvm_bf16lo(wa.y), acc0); acc1 = fmaf(kvm_bf16hi(xa.y), kvm_bf16hi(wa.y), acc1);
-          acc2 = fmaf(kvm_bf16lo(xb.y), kvm_bf16lo(wb.y), acc2); acc3 = fmaf(kvm_bf16hi(xb.y), kvm_bf16hi(wb.y), acc3);
-          acc0 = fmaf(kvm_bf16lo(xa.z), kvm_bf16lo(wa.z), acc0); acc1 = fmaf(kvm_bf16hi(xa.z), kvm_bf16hi(wa.z), acc1);
-          acc2 = fmaf(kvm_bf16lo(xb.z), kvm_bf16lo(wb.z), acc2); acc3 = fmaf(kvm_bf16hi(xb.z), kvm_bf16hi(wb.z), acc3);
-          acc0 = fmaf(kvm_bf16lo(xa.w), kvm_bf16lo(wa.w), acc0); acc1 = fmaf(kvm_bf16hi(xa.w), kvm_bf16hi(wa.w), acc1);
-          acc2 = fmaf(kvm_bf16lo(xb.w), kvm_bf16lo(wb.w), acc2); acc3 = fmaf(kvm_bf16hi(xb.w), kvm_bf16hi(wb.w), acc3);
-        }
-        for (; k < ke; k += 256) {
-          const uint4 wv = *(const uint4*)(st + k * 2);
-          const uint4 xv = *(const uint4*)(vs + k);
-          acc0 = fmaf(kvm_bf16lo(xv.x), kvm_bf16lo(wv.x), acc0); acc1 = fmaf(kvm_bf16hi(xv.x), kvm_bf16hi(wv.x), acc1);
-          acc0 = fmaf(kvm_bf16lo(xv.y), kvm_bf16lo(wv.y), acc0); acc1 = fmaf(kvm_bf16hi(xv.y), kvm_bf16hi(wv.y), acc1);
-          acc0 = fmaf(kvm_bf16lo(xv.z), kvm_bf16lo(wv.z), acc0); acc1 = fmaf(kvm_bf16hi(xv.z), kvm_bf16hi(wv.z), acc1);
-          acc0 = fmaf(kvm_bf16lo(xv.w), kvm_bf16lo(wv.w), acc0); acc1 = fmaf(kvm_bf16hi(xv.w), kvm_bf16hi(wv.w), acc1);
+#pragma unroll
+        for (int sg = 0; sg < 8; sg += 2) {
+          if (kb + sg * 256 < ke) {
+            const uint4 wa = *(const uint4*)(st + sg * 512), xa = xr[sg];
+            acc0 = fmaf(kvm_bf16lo(xa.x), kvm_bf16lo(wa.x), acc0); acc1 = fmaf(kvm_bf16hi(xa.x), kvm_bf16hi(wa.x), acc1);
+            acc0 = fmaf(kvm_bf16lo(xa.y), kvm_bf16lo(wa.y), acc0); acc1 = fmaf(kvm_bf16hi(xa.y), kvm_bf16hi(wa.y), acc1);
+            acc0 = fmaf(kvm_bf16lo(xa.z), kvm_bf16lo(wa.z), acc0); acc1 = fmaf(kvm_bf16hi(xa.z), kvm_bf16hi(wa.z), acc1);
+            acc0 = fmaf(kvm_bf16lo(xa.w), kvm_bf16lo(wa.w), acc0); acc1 = fmaf(kvm_bf16hi(xa.w), kvm_bf16hi(wa.w), acc1);
+          }
+          if (kb + (sg + 1) * 256 < ke) {
+            const uint4 wb = *(const uint4*)(st + (sg + 1) * 512), xb = xr[sg + 1];
+            acc2 = fmaf(kvm_bf16lo(xb.x), kvm_bf16lo(wb.x), acc2); acc3 = fmaf(kvm_bf16hi(xb.x), kvm_bf16hi(wb.x), acc3);
+            acc2 = fmaf(kvm_bf16lo(xb.y), kvm_bf16lo(wb.y), acc2); acc3 = fmaf(kvm_bf16hi(xb.y), kvm_bf16hi(wb.y), acc3);
+            acc2 = fmaf(kvm_bf16lo(xb.z), kvm_bf16lo(wb.z), acc2); acc3 = fmaf(kvm_bf16hi(xb.z), kvm_bf16hi(wb.z), acc3);
+            acc2 = fmaf(kvm_bf16lo(xb.w), kvm_bf16lo(wb.w), acc2); acc3 = fmaf(kvm_bf16hi(xb.w), kvm_bf16hi(wb.w), acc3);
+          }
         }
         const float sum = kvm_warp_sum((acc0 + acc1) + (acc2 + acc3));
         if (lane == 0) parts[(ci * R + r) * KP + part] = sum;
@@ -194,8 +237,10 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
     }
   }
   __syncwarp();
-  if (stamp && tid == 0)        // trace detail: prologue | wait for the first stage (both in 0.1 us) | all waits for stages (0.2 us), one byte each
-    stamp[0] = (int)min(255ull, (t_pro - t_task) / 100) | ((int)min(255ull, t_first / 100) << 8) | ((int)min(255ull, t_wait / 200) << 16);
+  if (stamp && tid == 0) {      // trace detail, one byte each in units of 0.2 us: prologue | stage loop (waits included) | waits for stages
+    (void)t_first;
+    stamp[0] = (int)min(255ull, (t_pro - t_task) / 200) | ((int)min(255ull, (kvm_globaltimer() - t_pro) / 200) << 8) | ((int)min(255ull, t_wait / 200) << 16);
+  }
   if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1134);
   kvm_sync();
   if (ok && *(volatile int*)&c.err->code == 0)
@@ -206,124 +251,261 @@ static __device__ void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const Kv
     }
 }
 
-// ---- streamed GEMV for up to eight activation rows (gemv_bf16_rows), consumer side ------------------------------------------------------
-// Tensor cores: D[16 x 8] += A[16 x 16] B[16 x 8] (mma.sync m16n8k16, bf16 operands, float32 accumulate) with A = activations (rows =
-// activation rows, eight of the sixteen used), B = eight weight rows of a stage (columns).  A dot product does not care in which order
-// k is visited, so both operands are read 16 bytes per thread from row-major [row][k] arrays at the SAME k offsets (thread t of a
-// quad takes k = 8t .. 8t+7 of a 32-wide slice for two MMAs) instead of in the instruction's interleaved k layout.
-// Chunks arrive k-chunk outer, row group inner: per k-chunk the prologue'd activations of that k range are staged once (bf16,
-// padded rows), then every row group's stage is multiplied against them by the eight consumer warps (each a slice of the chunk's k);
-// accumulators of up to eight row groups stay in registers over the whole task; at the end the warps' partial sums are added in
-// warp order.  Semantics per row as gemv_bf16 (runtime/ref_extra.py:398-415).
+// ---- streamed GEMV on tensor cores (gemv_bf16 with one activation row, gemv_bf16_rows with up to eight), consumer side --------------
+// D[16 x 8] += A[16 x 16] B[16 x 8] (mma.sync m16n8k16, bf16 operands, float32 accumulate) with A = activations (rows = activation
+// rows, at most eight of the sixteen used), B = the weight rows of a stage (columns).  A dot product does not care in which order k
+// is visited, so both operands are read 16 bytes per thread from row-major [row][k] arrays at the SAME k offsets (thread t of a quad
+// takes k = 8t .. 8t+7 of a 32-wide step, for two MMAs) instead of in the instruction's interleaved k layout.  Steps are taken in
+// pairs: weight rows sit a multiple of 128 bytes apart, so an odd row reads the pair's steps in the other order (and swaps the
+// registers back before the MMAs): the eight lanes of a quarter warp (two rows, four quads) then read eight different 16-byte
+// bank groups.  The activations are staged as bf16 with a row pitch of 64 bytes mod 128 for the same reason.
+//
+// Two stage layouts, chosen by kvm_gemv_mma_layout from the shapes alone (the front warp and the consumers compute the same):
+//   whole rows   a stage holds R <= 8 weight rows in full (KC = K, R*K*2 <= 64 KB, one bulk copy); every stage is a row group of
+//                its own, its sums leave the registers when the stage is done; needs all of the M activation rows staged at once;
+//   k chunks     a stage holds 8 weight rows x KC columns (KC < K, eight copies); stages run k-chunk outer, row group inner, the
+//                accumulators of up to eight row groups stay in registers over the whole task, the activations are staged per k-chunk.
+// All sixteen warps multiply (pairs of steps are dealt round robin); their partial sums are added in warp order at the end.
+// Semantics per activation row as gemv_bf16 (runtime/ref_extra.py:398-415).  Always consumes its nchunks stage uses, also after an error.
+#define KVM_MMA_PARTS_OFF 512
+struct KvmMmaLayout {
+  int R, KC, nkc, ng;       // weight rows and columns per stage, k-chunks, row groups
+  int full_x;               // all k of the activations staged once
+  int pitch;                // bytes per staged activation row
+  int parts_off;            // byte offset of the partial sums [16 warps][ng][M][R] in the scratch
+  int nchunks;
+  bool ok;
+};
+__device__ __forceinline__ KvmMmaLayout kvm_gemv_mma_layout(int rows, int K, int M, int scratch_bytes) {
+  KvmMmaLayout L;
+  L.ok = false;
+  const int row_pitch = K * 2 + 64;
+  // whole rows
+  L.R = K * 2 * 8 <= KVM_ST_STAGE ? 8 : KVM_ST_STAGE / (K * 2);
+  if (L.R >= 1) {
+    L.KC = K; L.nkc = 1; L.ng = (rows + L.R - 1) / L.R; L.full_x = 1; L.pitch = row_pitch;
+    L.parts_off = M * row_pitch + KVM_MMA_PARTS_OFF;
+    if (L.parts_off + 16 * L.ng * M * L.R * 4 <= scratch_bytes) { L.nchunks = L.ng; L.ok = true; return L; }
+  }
+  // k chunks
+  L.R = 8; L.KC = 4096;
+  while (L.KC > 0 && K % L.KC) L.KC -= 256;
+  if (L.KC <= 0 || L.KC >= K) return L;
+  L.nkc = K / L.KC; L.ng = (rows + 7) / 8;
+  if (L.ng > 8) return L;
+  L.full_x = M * row_pitch + KVM_MMA_PARTS_OFF + 16 * L.ng * M * 8 * 4 <= scratch_bytes;
+  L.pitch = L.full_x ? row_pitch : L.KC * 2 + 64;
+  L.parts_off = M * L.pitch + KVM_MMA_PARTS_OFF;
+  if (L.parts_off + 16 * L.ng * M * 8 * 4 > scratch_bytes) return L;
+  L.nchunks = L.nkc * L.ng; L.ok = true;
+  return L;
+}
 __device__ __forceinline__ void kvm_mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
-static __device__ void kvm_gemv_rows_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, const KvmRing& ring, unsigned cit, int KC, unsigned long long deadline) {
+// v[j] = prologue value of 8 consecutive activations starting at column k of row u
+__device__ __forceinline__ void kvm_mma_pro8(int pro, float (&v)[8], const float (&v2)[8], float rs) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = pro == 1 ? v[j] * rs * v2[j] : pro == 2 ? kvm_silu(v[j]) * v2[j] : v[j];
+}
+__device__ __forceinline__ uint4 kvm_pack_bf16x8(const float (&v)[8]) {
+  uint4 pk;
+  __nv_bfloat162* hh = (__nv_bfloat162*)&pk;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) hh[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  return pk;
+}
+// Staging of the activations v = bf16(pro(x)) for the tensor-core consumer, functions of their own (registers of their own).
+struct KvmStageX {
+  KvmBuf x, x2, gm;
+  unsigned char* xs;        // [M][pitch] bytes
+  float* rsq;               // [8] reciprocal RMS per row, from [64] on reduction scratch
+  int r0, M, K, pro, pitch;
+  float eps;
+};
+// One activation row whose prologue loads all fit into registers: every load in flight at once, one pass.  false = not taken.
+KVM_OP_FN bool kvm_stage_one_row(const KvmStageX& s) {
+  const KvmBuf x = s.x, x2 = s.x2, gm = s.gm;
+  const int K = s.K, pro = s.pro, tid = threadIdx.x;
+  if (K > 3 * 8 * KVM_NT || (x.ld & 7) || !kvm_vec_ok(x) || (pro == 2 && ((x2.ld & 7) || !kvm_vec_ok(x2))) || (pro == 1 && !kvm_vec_ok(gm))) return false;
+  float v[3][8], v2[3][8];
+  const size_t xo = (size_t)s.r0 * x.ld, x2o = x2.p ? (size_t)s.r0 * x2.ld : 0;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int k = (tid + j * KVM_NT) * 8;
+    if (k < K) {
+      kvm_ld8(x, xo + k, v[j]);
+      if (pro == 2) kvm_ld8(x2, x2o + k, v2[j]);
+      else if (pro == 1) { *(float4*)v2[j] = *(const float4*)((const float*)gm.p + k); *(float4*)(v2[j] + 4) = *(const float4*)((const float*)gm.p + k + 4); }
+    }
+  }
+  float rs = 0.0f;
+  if (pro == 1) {
+    float q = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) if ((tid + j * KVM_NT) * 8 < K)
+#pragma unroll
+      for (int u = 0; u < 8; ++u) q += v[j][u] * v[j][u];
+    q = kvm_block_sum(q, s.rsq + 64);
+    rs = 1.0f / sqrtf(q / K + s.eps);
+  }
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int k = (tid + j * KVM_NT) * 8;
+    if (k < K) { kvm_mma_pro8(pro, v[j], v2[j], rs); *(uint4*)(s.xs + (size_t)k * 2) = kvm_pack_bf16x8(v[j]); }
+  }
+  return true;
+}
+// RMS statistics of up to eight rows: two warps per activation row.  Whole compute group.
+KVM_OP_FN void kvm_stage_rms(const KvmStageX& s) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, u = warp >> 1, hf = warp & 1, K = s.K;
+  float q = 0.0f;
+  if (u < s.M) for (int k = hf * (K / 2) + lane; k < (hf + 1) * (K / 2); k += 32) { const float v = kvm_ld(s.x, (size_t)(s.r0 + u) * s.x.ld + k); q += v * v; }
+  q = kvm_warp_sum(q);
+  if (lane == 0) s.rsq[64 + warp] = q;
+  kvm_sync();
+  if (tid < 8) s.rsq[tid] = tid < s.M ? 1.0f / sqrtf((s.rsq[64 + 2 * tid] + s.rsq[64 + 2 * tid + 1]) / K + s.eps) : 0.0f;
+  kvm_sync();
+}
+// Columns [kb, kb + kn) of the M rows to column offset 0 of the staged rows (all 16 warps).
+KVM_OP_FN void kvm_stage_rows(const KvmStageX& s, int kb, int kn) {
+  const KvmBuf x = s.x, x2 = s.x2, gm = s.gm;
+  const int pro = s.pro, r0 = s.r0;
+  const bool vec_x = (x.ld & 7) == 0 && kvm_vec_ok(x), vec_x2 = x2.p && (x2.ld & 7) == 0 && kvm_vec_ok(x2), vec_g = gm.p && kvm_vec_ok(gm);
+  for (int e = threadIdx.x; e < s.M * (kn / 8); e += KVM_NT) {
+    const int u = e / (kn / 8), k0 = (e % (kn / 8)) * 8, k = kb + k0;
+    float v[8], v2[8];
+    if (vec_x) kvm_ld8(x, (size_t)(r0 + u) * x.ld + k, v);
+    else for (int j = 0; j < 8; ++j) v[j] = kvm_ld(x, (size_t)(r0 + u) * x.ld + k + j);
+    if (pro == 2) {
+      if (vec_x2) kvm_ld8(x2, (size_t)(r0 + u) * x2.ld + k, v2);
+      else for (int j = 0; j < 8; ++j) v2[j] = kvm_ld(x2, (size_t)(r0 + u) * x2.ld + k + j);
+    } else if (pro == 1) {
+      if (vec_g) { *(float4*)v2 = *(const float4*)((const float*)gm.p + k); *(float4*)(v2 + 4) = *(const float4*)((const float*)gm.p + k + 4); }
+      else for (int j = 0; j < 8; ++j) v2[j] = ((const float*)gm.p)[k + j];
+    }
+    kvm_mma_pro8(pro, v, v2, pro == 1 ? s.rsq[u] : 0.0f);
+    *(uint4*)(s.xs + (size_t)u * s.pitch + (size_t)k0 * 2) = kvm_pack_bf16x8(v);
+  }
+}
+template <bool CHUNKED>      // the k-chunk layout (accumulators of eight row groups live over the task) or the whole-row layout, a function each
+KVM_OP_FN void kvm_gemv_mma_ring_t(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, bool has_rows, const KvmRing& ring, unsigned cit, unsigned long long deadline,
+                                   unsigned long long t_task, int* stamp) {
   KvmBuf x, x2, gm, w, out, res;
-  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9], r0 = a[11], r1 = a[12];
+  const int n0 = a[6], n1 = a[7], K = a[8], pro = a[9], r0 = has_rows ? a[11] : 0, r1 = has_rows ? a[12] : 1;
   const float eps = kvm_bits_f32(a[10]);
   bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, x) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, x2, true) && kvm_buf_local(c, lb, a, 2, KVM_M_F32, gm, true) &&
             kvm_buf_local(c, lb, a, 3, KVM_M_BF16, w) && kvm_buf_local(c, lb, a, 4, KVM_M_FLT, out) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, res, true);
-  const int rows = n1 - n0, ng = (rows + 7) / 8, nkc = K / KC, M = r1 - r0;
-  if (ok && (pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p))) { c.fail(KVM_OPE_SHAPE, K, pro); ok = false; }
+  const int rows = n1 - n0, M = r1 - r0;
+  const KvmMmaLayout L = kvm_gemv_mma_layout(rows, K, M, c.smem_bytes);       // the front warp accepted the same layout
+  const int R = L.R, KC = L.KC, ng = L.ng, nkc = L.nkc, pitch = L.pitch;
+  if (ok && (pro < 0 || pro > 2 || (pro == 1 && !gm.p) || (pro == 2 && !x2.p) || !L.ok || CHUNKED != (L.nkc > 1))) { c.fail(KVM_OPE_SHAPE, K, pro); ok = false; }
   if (ok) ok = kvm_mat_ok(c, x, r1, K) && kvm_mat_ok(c, x2, r1, K) && kvm_flat_ok(c, gm, K) && kvm_mat_ok(c, out, r1, n1) && kvm_mat_ok(c, res, r1, n1);
-  const int pitch = KC * 2 + 16;                          // bytes per staged activation row: 16-byte accesses of the eight rows fall into different banks
-  unsigned char* xs = c.smem;                              // [8][pitch]
-  float* rsq = (float*)(c.smem + 8 * pitch);              // [8] reciprocal RMS per activation row, then [64] reduction scratch
-  float* parts = rsq + 128;                                // [8 warps][ng][8 activation rows][8 weight rows]
+  unsigned char* xs = c.smem;                              // [M][pitch]
+  float* rsq = (float*)(c.smem + M * pitch);               // [8] reciprocal RMS per activation row, from [64] on reduction scratch
+  float* parts = (float*)(c.smem + L.parts_off);           // [16 warps][ng][M][R]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const bool vec_x = ok && (x.ld & 7) == 0 && kvm_vec_ok(x), vec_x2 = ok && x2.p && (x2.ld & 7) == 0 && kvm_vec_ok(x2), vec_g = ok && gm.p && kvm_vec_ok(gm);
   kvm_sync();                                              // the previous task is done with the scratch
-  if (ok && pro == 1) {                                    // RMS statistics: two warps per activation row
-    const int u = warp >> 1, hf = warp & 1;
-    float q = 0.0f;
-    if (u < M) for (int k = hf * (K / 2) + lane; k < (hf + 1) * (K / 2); k += 32) { const float v = kvm_ld(x, (size_t)(r0 + u) * x.ld + k); q += v * v; }
-    q = kvm_warp_sum(q);
-    if (lane == 0) rsq[64 + warp] = q;
-    kvm_sync();
-    if (tid < 8) rsq[tid] = tid < M ? 1.0f / sqrtf((rsq[64 + 2 * tid] + rsq[64 + 2 * tid + 1]) / K + eps) : 0.0f;
-  }
-  float acc[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  struct KvmStageX sx;
+  sx.x = x; sx.x2 = x2; sx.gm = gm; sx.xs = xs; sx.rsq = rsq; sx.r0 = r0; sx.M = M; sx.K = K; sx.pro = pro; sx.pitch = pitch; sx.eps = eps;
+  bool staged = false;
+  if (ok && M == 1 && L.full_x) staged = kvm_stage_one_row(sx);
+  if (ok && !staged && pro == 1) kvm_stage_rms(sx);
+  if (ok && !staged && L.full_x) kvm_stage_rows(sx, 0, K);
+  kvm_sync();
+  unsigned long long t_pro = 0, t_wait = 0, t_first = 0;
+  if (stamp && tid == 0) t_pro = kvm_globaltimer();
   bool waited = true;
-  const int kw = KC / KVM_ST_MMA_WARPS;                                   // k extent of one consumer warp inside a chunk (a multiple of 32)
-  for (int kc = 0; kc < nkc; ++kc) {
-    kvm_sync();                                            // statistics written; the consumers are done with the previous chunk's activations
+  const int npairs = KC / 64;
+  // one stage use: wait for it, multiply it into acc (x columns from xk0 of the staged rows), release it
+  auto consume = [&](unsigned it, float (&acc)[4], int xk0) {
+    unsigned long long tw = 0;
+    if (stamp && tid == 0) tw = kvm_globaltimer();
+    if (waited && !kvm_ring_wait_warp(ring, it, deadline, c.err)) waited = false;
+    if (stamp && tid == 0) { const unsigned long long d = kvm_globaltimer() - tw; t_wait += d; if (it == cit) t_first = d; }
+    if (!waited) return;                                   // warp-uniform; the warp still takes part in every barrier of the task
     if (ok) {
-      // stage v = bf16(pro(x)) of this k range for the M rows, zeros for the unused rows (all 16 warps)
-      for (int e = tid; e < 8 * (KC / 8); e += KVM_NT) {
-        const int u = e / (KC / 8), k0 = (e % (KC / 8)) * 8, k = kc * KC + k0;
-        uint4 pk = make_uint4(0, 0, 0, 0);
-        if (u < M) {
-          float v[8], v2[8];
-          if (vec_x) kvm_ld8(x, (size_t)(r0 + u) * x.ld + k, v);
-          else for (int j = 0; j < 8; ++j) v[j] = kvm_ld(x, (size_t)(r0 + u) * x.ld + k + j);
-          if (pro == 2) {
-            if (vec_x2) kvm_ld8(x2, (size_t)(r0 + u) * x2.ld + k, v2);
-            else for (int j = 0; j < 8; ++j) v2[j] = kvm_ld(x2, (size_t)(r0 + u) * x2.ld + k + j);
-          } else if (pro == 1) {
-            if (vec_g) { *(float4*)v2 = *(const float4*)((const float*)gm.p + k); *(float4*)(v2 + 4) = *(const float4*)((const float*)gm.p + k + 4); }
-            else for (int j = 0; j < 8; ++j) v2[j] = ((const float*)gm.p)[k + j];
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = pro == 1 ? v[j] * rsq[u] * v2[j] : pro == 2 ? kvm_silu(v[j]) * v2[j] : v[j];
-          __nv_bfloat162* hh = (__nv_bfloat162*)&pk;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) hh[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-        }
-        *(uint4*)(xs + (size_t)u * pitch + k0 * 2) = pk;
+      const unsigned char* wrow = kvm_ring_stage(ring, it) + (size_t)g * KC * 2 + t * 16;
+      const unsigned char* xrow = xs + (size_t)g * pitch + (size_t)xk0 * 2 + t * 16;
+      const int odd = g & 1;
+      float acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};                  // the two steps of a pair accumulate side by side
+#pragma unroll 2
+      for (int p = warp; p < npairs; p += KVM_NT / 32) {
+        uint4 b0 = make_uint4(0, 0, 0, 0), b1 = b0, a0 = b0, a1 = b0;
+        if (g < R) { b0 = *(const uint4*)(wrow + (2 * p + odd) * 64); b1 = *(const uint4*)(wrow + (2 * p + 1 - odd) * 64); }
+        if (g < M) { a0 = *(const uint4*)(xrow + (2 * p) * 64); a1 = *(const uint4*)(xrow + (2 * p + 1) * 64); }
+        const uint4 e0 = odd ? b1 : b0, e1 = odd ? b0 : b1;       // weights of step 2p and of step 2p + 1
+        kvm_mma_bf16_16816(acc, a0.x, a0.y, e0.x, e0.y);
+        kvm_mma_bf16_16816(acc2, a1.x, a1.y, e1.x, e1.y);
+        kvm_mma_bf16_16816(acc, a0.z, a0.w, e0.z, e0.w);
+        kvm_mma_bf16_16816(acc2, a1.z, a1.w, e1.z, e1.w);
       }
+      acc[0] += acc2[0]; acc[1] += acc2[1]; acc[2] += acc2[2]; acc[3] += acc2[3];
     }
-    kvm_sync();
-    {
+    __syncwarp();
+    if (lane == 0) kvm_mbar_arrive(kvm_ring_empty(ring, it));
+  };
+  // thread (g, t) holds D[activation row g][weight rows 2t, 2t + 1]
+  auto put_parts = [&](int rg, const float (&acc)[4]) {
+    if (g < M) {
+      float* pp = parts + (((size_t)warp * ng + rg) * M + g) * R;
+      if (2 * t < R) pp[2 * t] = acc[0];
+      if (2 * t + 1 < R) pp[2 * t + 1] = acc[1];
+    }
+  };
+  if (!CHUNKED) {
+    for (int rg = 0; rg < ng; ++rg) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      consume(cit + (unsigned)rg, acc, 0);
+      put_parts(rg, acc);
+    }
+  } else {
+    float acc[8][4];
 #pragma unroll
-      for (int rg = 0; rg < 8; ++rg) {
-        if (rg >= ng) break;
-        const unsigned it = cit + (unsigned)(kc * ng + rg);
-        if (waited && !kvm_ring_wait_warp(ring, it, deadline, c.err)) waited = false;
-        if (!waited) break;                                // warp-uniform; the warp still takes part in every barrier below
-        if (ok && warp < KVM_ST_MMA_WARPS) {               // the other warps only release the stage once it has landed
-          const unsigned char* wrow = kvm_ring_stage(ring, it) + (size_t)g * KC * 2 + (size_t)(warp * kw + t * 8) * 2;
-          const unsigned char* xrow = xs + (size_t)g * pitch + (size_t)(warp * kw + t * 8) * 2;
-#pragma unroll 4
-          for (int kk = 0; kk < kw; kk += 32) {
-            const uint4 bv = *(const uint4*)(wrow + kk * 2);
-            const uint4 av = *(const uint4*)(xrow + kk * 2);
-            kvm_mma_bf16_16816(acc[rg], av.x, av.y, bv.x, bv.y);
-            kvm_mma_bf16_16816(acc[rg], av.z, av.w, bv.z, bv.w);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) kvm_mbar_arrive(kvm_ring_empty(ring, it));
+    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    for (int kc = 0; kc < nkc; ++kc) {
+      if (!L.full_x) {
+        if (kc) kvm_sync();                                // the consumers are done with the previous chunk's activations
+        if (ok) kvm_stage_rows(sx, kc * KC, KC);
+        kvm_sync();
       }
+#pragma unroll
+      for (int rg = 0; rg < 8; ++rg) if (rg < ng) consume(cit + (unsigned)(kc * ng + rg), acc[rg], L.full_x ? kc * KC : 0);
     }
+#pragma unroll
+    for (int rg = 0; rg < 8; ++rg) if (rg < ng) put_parts(rg, acc[rg]);
   }
   __syncwarp();
+  if (stamp && tid == 0) {      // trace detail, one byte each in units of 0.2 us: prologue | stage loop (waits included) | waits for stages
+    (void)t_first;
+    stamp[0] = (int)min(255ull, (t_pro - t_task) / 200) | ((int)min(255ull, (kvm_globaltimer() - t_pro) / 200) << 8) | ((int)min(255ull, t_wait / 200) << 16);
+  }
   if (!waited && *(volatile int*)&c.err->code == 0) kvm_stream_timeout(c, 1301);
-  // partial sums of the eight consumer warps -> shared memory -> added in warp order; thread = (row group, activation row, weight row)
-  if (warp < KVM_ST_MMA_WARPS)
-#pragma unroll
-    for (int rg = 0; rg < 8; ++rg) if (rg < ng) *(float2*)(parts + (((size_t)warp * ng + rg) * 8 + g) * 8 + 2 * t) = make_float2(acc[rg][0], acc[rg][1]);
   kvm_sync();
   if (ok && *(volatile int*)&c.err->code == 0)            // a warp that gave up has recorded the timeout before the barrier
-    for (int e = tid; e < ng * 64; e += KVM_NT) {
-      const int rg = e >> 6, u = (e >> 3) & 7, nn = e & 7, n = n0 + rg * 8 + nn;
-      if (u >= M || n >= n1) continue;
+    for (int e = tid; e < ng * M * R; e += KVM_NT) {
+      const int rg = e / (M * R), u = (e / R) % M, nn = e % R, n = n0 + rg * R + nn;
+      if (n >= n1) continue;
       float sum = 0.0f;
 #pragma unroll
-      for (int wv = 0; wv < KVM_ST_MMA_WARPS; ++wv) sum += parts[(((size_t)wv * ng + rg) * 8 + u) * 8 + nn];
+      for (int wv = 0; wv < KVM_NT / 32; ++wv) sum += parts[(((size_t)wv * ng + rg) * M + u) * R + nn];
       const size_t o = (size_t)(r0 + u) * out.ld + n;
       kvm_st(out, o, res.p ? __fadd_rn(sum, kvm_ld(res, (size_t)(r0 + u) * res.ld + n)) : sum);
     }
 }
 
+__device__ __forceinline__ void kvm_gemv_mma_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, bool has_rows, const KvmRing& ring, unsigned cit, int nkc,
+                                                  unsigned long long deadline, unsigned long long t_task, int* stamp) {
+  if (nkc > 1) kvm_gemv_mma_ring_t<true>(c, a, lb, has_rows, ring, cit, deadline, t_task, stamp);
+  else kvm_gemv_mma_ring_t<false>(c, a, lb, has_rows, ring, cit, deadline, t_task, stamp);
+}
+
 // ---- streamed split attention, consumer side ----------------------------------------------------------------------------------
 // Stage use `cit` holds the split's keys, `cit + 1` its values (the appended row left out).  Semantics as kvm_op_attn_decode_part
 // (runtime/ref_extra.py:421-498); the front warp has validated the geometry before it issued the copies.
-static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, bool qkn, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow,
-                                          unsigned long long deadline) {
+KVM_OP_FN void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb, bool qkn, const KvmRing& ring, unsigned cit, int j0, int j1, int newrow,
+                                          unsigned long long deadline, unsigned long long t_task, int* stamp) {
   KvmBuf q, kc, vc, lens, part, kn, vn, gam{};
   bool ok = kvm_buf_local(c, lb, a, 0, KVM_M_FLT, q) && kvm_buf_local(c, lb, a, 1, KVM_M_FLT, kc) && kvm_buf_local(c, lb, a, 2, KVM_M_FLT, vc) &&
             kvm_buf_local(c, lb, a, 3, KVM_M_I32, lens) && kvm_buf_local(c, lb, a, 4, KVM_M_F32, part) && kvm_buf_local(c, lb, a, 5, KVM_M_FLT, kn, true) &&
@@ -352,21 +534,33 @@ static __device__ void kvm_attn_part_ring(const KvmCtx& c, const int32_t* a, con
     P.q = q; P.kc = kc; P.vc = vc; P.kn = kn; P.vn = vn; P.gam = gam;
     P.b = b; P.kvh = kvh; P.G = G; P.hd = hd; P.fl = fl; P.p0 = p0; P.base = (size_t)(b * Hkv + kvh) * Tmax; P.theta = theta; P.eps = qkn ? kvm_bits_f32(a[19]) : 0.0f;
     P.appends = newrow >= 0;
+    P.rope_cache = c.rope_cache;
     P.qs = (float*)(sm + KVM_AS_OFF_QS); P.inv = (float*)(sm + KVM_AS_OFF_INV); P.kns = (float*)(sm + KVM_AS_OFF_KNEW); P.vns = (float*)(sm + KVM_AS_OFF_VNEW);
     P.rsq = (float*)(sm + KVM_AS_OFF_ML);
-    auto prologue = [&]() { kvm_part_prologue(P); };
+    unsigned long long t_wait = 0;
+    auto prologue = [&]() {
+      kvm_part_prologue(P);
+      if (stamp && threadIdx.x == 0) stamp[0] = (int)min(255ull, (kvm_globaltimer() - t_task) / 100);      // trace detail, byte 0: start to end of the prologue (0.1 us)
+    };
     float* pp = (float*)part.p;
     auto emit = [&](int g, int cc, float M, float Lsum, float A) {
       const size_t row = ((size_t)(b * S + s) * H + kvh * G + g) * part.ld;
       pp[row + cc] = Lsum > 0.0f ? A : 0.0f;
       if (cc == 0) { pp[row + hd] = Lsum > 0.0f ? M : KVM_ATTN_EMPTY_M_STREAM; pp[row + hd + 1] = Lsum; }
     };
-    auto wk = [&]() { return wait_use(cit); };
-    auto wv = [&]() { return wait_use(cit + 1); };
+    auto timed_wait = [&](unsigned it) {
+      const unsigned long long t0 = stamp && threadIdx.x == 0 ? kvm_globaltimer() : 0;
+      const bool r = wait_use(it);
+      if (stamp && threadIdx.x == 0) t_wait += kvm_globaltimer() - t0;
+      return r;
+    };
+    auto wk = [&]() { return timed_wait(cit); };
+    auto wv = [&]() { return timed_wait(cit + 1); };
     if (G <= 1) waited = kvm_attn_part_core<1>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
     else if (G <= 2) waited = kvm_attn_part_core<2>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
     else if (G <= 4) waited = kvm_attn_part_core<4>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
     else waited = kvm_attn_part_core<8>(sm, Ks, Vs, nk, newrow, G, hd, sc, prologue, wk, wv, emit);
+    if (stamp && threadIdx.x == 0) stamp[0] |= (int)min(255ull, t_wait / 100) << 8;       // byte 1: waits for the keys and the values (0.1 us)
   } else {
     waited = wait_use(cit) && wait_use(cit + 1);
   }
@@ -383,26 +577,20 @@ static __device__ void kvm_static_geometry(const KvmDevState& S, KvmStSlot& sl, 
   sl.kind = 0; sl.nchunks = 0; sl.R = 1; sl.j0 = sl.j1 = 0; sl.newrow = -1;
   const int op = sl.desc[0];
   const int32_t* a = sl.args;
-  if (op == 134) {
-    const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8];
-    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || K <= 0 || (K & 255) || K * 2 > KVM_ST_STAGE) return;
+  if (op == 134 || op == 301) {
+    const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8], r0 = op == 301 ? a[11] : 0, r1 = op == 301 ? a[12] : 1;
+    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || K <= 0 || (K & 255) || r0 < 0 || r1 <= r0 || r1 - r0 > 8) return;
     const KvmBuf w = sl.lb[3];
     if (!w.p || w.dtype != KVM_BF16 || (w.ld & 7) || ((uintptr_t)w.p & 15) || n1 > w.rows || K > w.cols) return;
-    int R = KVM_ST_STAGE / (K * 2);
-    if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
-    if (((K * 2 + 127) & ~127) + 256 + ((n1 - n0 + 7) & ~7) * (KVM_ST_ARRIVALS / R) * 4 > scratch_bytes) return;
-    sl.kind = 1; sl.R = R; sl.nchunks = (n1 - n0 + R - 1) / R;
-  } else if (op == 301) {
-    // gemv_bf16_rows: stages hold eight weight rows x KC columns; chunks run k-chunk outer, row group inner (the activations of the
-    // current k-chunk stay in the scratch while every row group passes over them)
-    const int wi = a[3], n0 = a[6], n1 = a[7], K = a[8], r0 = a[11], r1 = a[12];
-    if (wi < 0 || wi >= S.nbufs || n0 < 0 || n1 <= n0 || n1 - n0 > 64 || K <= 0 || (K & 255) || r0 < 0 || r1 <= r0 || r1 - r0 > 8) return;
-    const KvmBuf w = sl.lb[3];
-    if (!w.p || w.dtype != KVM_BF16 || (w.ld & 7) || ((uintptr_t)w.p & 15) || n1 > w.rows || K > w.cols) return;
-    int KC = K;
-    if (KC > 4096) { KC = 4096; while (K % KC) KC -= 256; }
-    if (8 * (KC * 2 + 16) + 8 * 8 * 8 * 8 * 4 + 1024 > scratch_bytes) return;      // activations of one k-chunk + the partial sums of up to eight row groups
-    sl.kind = 3; sl.R = KC; sl.nchunks = (K / KC) * ((n1 - n0 + 7) / 8);
+    // one activation row: the SIMT consumer over stages of whole rows (measured faster than mma.sync fragments at one row: the
+    // legacy tensor path of this part issues an m16n8k16 every few hundred cycles per warp); several rows: the tensor-core consumer
+    if (op == 134 && K * 2 <= KVM_ST_STAGE) {
+      int R = KVM_ST_STAGE / (K * 2);
+      if (R > KVM_ST_ARRIVALS) R = KVM_ST_ARRIVALS;
+      if (((K * 2 + 127) & ~127) + 256 + ((n1 - n0 + 7) & ~7) * (KVM_ST_ARRIVALS / R) * 4 <= scratch_bytes) { sl.kind = 1; sl.R = R; sl.nchunks = (n1 - n0 + R - 1) / R; return; }
+    }
+    const KvmMmaLayout L = kvm_gemv_mma_layout(n1 - n0, K, r1 - r0, scratch_bytes);
+    if (L.ok) { sl.kind = 3; sl.R = L.R; sl.j0 = L.KC; sl.j1 = L.ng; sl.newrow = L.nkc; sl.nchunks = L.nchunks; }      // j0 / j1 / newrow double as KC / row groups / k-chunks
   } else if (op == 135 || op == 300) {
     const int kci = a[1], vci = a[2], li = a[3], b = a[7], kvh = a[8], s = a[9], Sp = a[10], H = a[11], Hkv = a[12], hd = a[13], Tmax = a[14], fl = a[17];
     if (kci < 0 || kci >= S.nbufs || vci < 0 || vci >= S.nbufs || li < 0 || li >= S.nbufs) return;
@@ -426,9 +614,10 @@ static __device__ void kvm_static_issue(const KvmDevState& S, const KvmStSlot& s
   const uint32_t full = kvm_ring_full(ring, it), dst = ring.base_addr + kvm_ring_slot(ring, it) * KVM_ST_STAGE;
   const int32_t* a = sl.args;
   if (sl.kind == 3) {
+    // stage = R weight rows x KC columns; chunk ci = (k-chunk, row group), row group inner
     const KvmBuf w = sl.lb[3];
-    const int n0 = a[6], n1 = a[7], K = a[8], KC = sl.R, ng = (n1 - n0 + 7) / 8;
-    const int kc = ci / ng, rg = ci % ng, r0 = n0 + rg * 8, nr = min(8, n1 - r0);
+    const int n0 = a[6], n1 = a[7], K = a[8], R = sl.R, KC = sl.j0, ng = sl.j1;
+    const int kc = ci / ng, rg = ci % ng, r0 = n0 + rg * R, nr = min(R, n1 - r0);
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w.p + (size_t)kc * KC;
     kvm_mbar_expect_tx(full, (uint32_t)(nr * KC * 2));
     if (KC == K && w.ld == K) kvm_bulk_g2s(dst, wp + (size_t)r0 * w.ld, (uint32_t)(nr * K * 2), full);
@@ -465,7 +654,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
   unsigned dyn;
   asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
   if (tid < KVM_ST_SLOTS) { slots[tid].state = 0; slots[tid].task = -1; }
-  if (tid == 0) { sctl[0] = 0; sctl[1] = 0; }
+  if (tid == 0) { sctl[0] = 0; sctl[1] = 0; ((int*)(kvm_smem + KVM_ST_HDR - 128 - 288))[0] = 0; ((int*)(kvm_smem + KVM_ST_HDR - 128 - 288))[1] = 0; }
   kvm_tc_init(ctl, kvm_smem);
   const unsigned ring_ns = T.ring == 2 ? 2u : 3u;
   const int ring_bytes = (int)ring_ns * KVM_ST_STAGE;
@@ -609,6 +798,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
   } else {
     KvmCtx c;
     c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps; c.pair = -1; c.engine = 0; c.gemm_seq = 0;
+    c.rope_cache = (float*)(kvm_smem + KVM_ST_HDR - 128 - 288);
     c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_ST_HDR) : S.bufs;
     const int used = KVM_ST_HDR + (buf_cache ? cache_bytes : 0);
     c.smem = kvm_smem + used;
@@ -634,11 +824,14 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
       if (tid == 0 && S.trace) { t_task = kvm_globaltimer(); S.t_start[task] = t_task; sctl[3] = 0; }
       const int op = sl.desc[0], kind = sl.kind, nch = sl.nchunks;
       if (kind == 1) kvm_gemv_ring(c, sl.args, sl.lb, ring, cit, sl.R, nch, deadline, t_task, S.trace ? sctl + 3 : nullptr);
-      else if (kind == 3) kvm_gemv_rows_ring(c, sl.args, sl.lb, ring, cit, sl.R, deadline);
-      else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, op == 300, ring, cit, sl.j0, sl.j1, sl.newrow, deadline);
+      else if (kind == 3) kvm_gemv_mma_ring(c, sl.args, sl.lb, op == 301, ring, cit, sl.newrow, deadline, t_task, S.trace ? sctl + 3 : nullptr);
+      else if (kind == 2) kvm_attn_part_ring(c, sl.args, sl.lb, op == 300, ring, cit, sl.j0, sl.j1, sl.newrow, deadline, t_task, S.trace ? sctl + 3 : nullptr);
       else if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       cit += (unsigned)nch;
-      asm volatile("fence.proxy.async;" ::: "memory");
+      // Results that a later bulk copy or TMA load may read (cache rows appended by an attention split, operands of tensor-core ops)
+      // need the writer's generic-to-async proxy fence.  A streamed GEMV writes activations only, which every consumer reads with
+      // plain loads: it skips the fence (it waits for the task's global stores, about a microsecond per task).
+      if (kind != 1 && kind != 3) asm volatile("fence.proxy.async;" ::: "memory");
       kvm_sync();
       if (tid == 0) {
         if (S.trace) { S.t_end[task] = kvm_globaltimer(); S.t_smid[task] = (int)kvm_smid() | (sctl[3] << 8); }     // bits 8.. : detail of a streamed task

@@ -17,9 +17,9 @@ static double kvm_static_cost(const KvmExec* h, const KvmTaskDesc& d, const int3
   auto elems = [&](int e0, int e1) { return (double)(e1 > e0 ? e1 - e0 : 0); };
   switch (d.op_id) {
     case 0: return 0.2;
-    case 134: case 301: return 1.5 + elems(a[6], a[7]) * a[8] * 2.0 / BPU;
-    case 135: case 300: { const double keys = a[10] > 0 ? (double)a[14] / a[10] : a[14]; return 3.0 + 2.0 * keys * a[13] * 2.0 / BPU; }
-    case 136: return 1.0;
+    case 134: case 301: return 8.0 + elems(a[6], a[7]) * a[8] * 2.0 / BPU;     // fixed part measured: prologue and hand-over of a streamed task
+    case 135: case 300: { const double keys = a[10] > 0 ? (double)a[14] / a[10] : a[14]; return 14.0 + 2.0 * keys * a[13] * 2.0 / BPU; }
+    case 136: return 8.0;                     // a few dependent round trips, measured
     case 58: case 57: return 2.0 + elems(a[d.op_id == 58 ? 2 : 3], a[d.op_id == 58 ? 3 : 4]) * a[d.op_id == 58 ? 4 : 5] * 4.0 / BPU;
     case 122: { const double m = std::min(128, a[8] - a[6]), n = std::min(256, a[9] - a[7]); return 5.0 + 2.0 * m * n * a[10] / 8.0e6; }
     case 34: case 114: { const int tm = (a[11] & 64) ? 256 : (a[11] & 32) ? 128 : 64, tn = (a[11] & 64) ? 128 : (a[11] & 32) ? 128 : 64;

@@ -207,7 +207,9 @@ def build_decode_rows(c: DecodeConfig, exact_caches: bool = False) -> Graph:
         rows = max(8, -(-total // slots))
         while sum(-(-n // rows) for n in ns) > slots:
             rows += 1
-        return -(-rows // 8) * 8                 # whole groups of eight weight rows: what one stage of the stream ring holds
+        # whole groups of eight weight rows (what one stage of the stream ring holds), at most seven of them: the static path's
+        # tensor-core consumer keeps the partial sums of a task's row groups for all B activation rows in shared memory
+        return min(-(-rows // 8) * 8, 56)
 
     def gemv(tag, x, w, out, n, k, pro=0, x2=None, gamma=None, res=None, prio=20, rows=None):
         rows = rows or phase_rows([n], k)

@@ -136,8 +136,12 @@ def test_decode_streams_ahead_and_matches_both_the_oracle_and_the_ready_queue(kv
             assert int(ex.read_buffer('u0.lens')[0, 0]) == cfg.ctx + 32
             runs[name] = (toks, {n: ex.read_buffer(n) for n in ('u0.logits', f'u0.l{cfg.layers - 1}.x2', 'u0.l0.kc')})
     assert runs['static'][0] == ref and runs['queue'][0] == ref
+    # The two paths add a dot product's terms in different orders (SIMT partial sums there, tensor-core fragments here), so an
+    # activation that sits on a bf16 rounding boundary may round the other way before it is stored or multiplied: after 32 tokens
+    # the states agree at the level of one bf16 unit (2^-8), not of float32.  Single tasks are held to 2e-5 against the oracle
+    # in the shape tests below.
     for n, a in runs['static'][1].items():
-        assert rel_err(a, runs['queue'][1][n]) <= 2e-5, n
+        assert rel_err(a, runs['queue'][1][n]) <= 4e-3, n
 
 
 @pytest.mark.parametrize('case', [dict(K=4096, N=300, pro=1), dict(K=12288, N=70, pro=2), dict(K=1024, N=37, pro=0), dict(K=2048, N=64, pro=1, ld=2304)])
