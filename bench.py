@@ -113,6 +113,12 @@ def workload_name(model, cfg):
             f'bf16 storage + f32 masters, AdamW lr {cfg.lr} wd {cfg.wd}, seeded weights N(0, {cfg.init_std}), uniform tokens')
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one kvm_exec_kernel launch of the step, from the one-pass ncu captures summarised
+# in profiles/bench_gpt162m_launch_list.md (full size) and profiles/kvm_exec_kernel_gpt162m_2l_ncu_full.md (two-layer cut)
+DECODE_TRAFFIC_RATIO = (2901808000 + 218917888) / 2855e6      # kvm_static_kernel on qwen3_8b_4l: profiles/kvm_static_kernel_decode_4l_ncu.md
+DRAM_TRAFFIC = {'gpt_162m': 24079402496 + 11409903104, 'gpt_162m_2l': 6419808000 + 3092519000}
+
+
 def get_bundle(model, rank, world, stream_steps, over):
     """The one-step training bundle of `model` (generated once per box, cached on local disk)."""
     from kvm_b200.bundle import load_bundle
@@ -310,7 +316,7 @@ def run_ours(args, rank, world, local_rank):
             'e2e': {'value': e2e_value, 'unit': 'steps/s', 'h2d_bytes_per_step': 2 * N * 4, 'd2h_bytes_per_step': 8, 'loss': e2e_loss},
             'gpu_launches': 3 * args.steps,
             'clocks': clk.summary(),
-            'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': None,
+            'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak, 'traffic': DRAM_TRAFFIC.get(args.model),
                          'peak_source': f'{pk_kind} bf16_tflops_sustained', 'flops_per_launch': gemm_fl + attn_fl},
         }
         ex.close()
@@ -318,23 +324,15 @@ def run_ours(args, rank, world, local_rank):
             line['busy'] = trace_split(bundle, local_rank)
         except Exception as e:
             line['busy'] = {'error': str(e)[:300]}
-        if args.decode_tokens > 0 and world == 1:
+        extras = set(args.extras.split(',')) if world == 1 else set()
+        for key, name, fn in (('decode', 'decode', lambda: run_decode(args, local_rank)), ('alone', 'kernels_alone', lambda: run_alone(local_rank)),
+                              ('small', 'small_models', lambda: run_small(local_rank)), ('355m', 'gpt_355m', lambda: run_355m(local_rank))):
+            if key not in extras or (key == 'decode' and args.decode_tokens <= 0):
+                continue
             try:
-                line['decode'] = run_decode(args, local_rank)
+                line[name] = fn()
             except Exception as e:      # the training line stands on its own
-                line['decode'] = {'error': str(e)[:300]}
-            try:
-                line['kernels_alone'] = run_alone(local_rank)
-            except Exception as e:
-                line['kernels_alone'] = {'error': str(e)[:300]}
-            try:
-                line['small_models'] = run_small(local_rank)
-            except Exception as e:
-                line['small_models'] = {'error': str(e)[:300]}
-            try:
-                line['gpt_355m'] = run_355m(local_rank)
-            except Exception as e:
-                line['gpt_355m'] = {'error': str(e)[:300]}
+                line[name] = {'error': str(e)[:300]}
         if cpu:
             line['cpu_baseline'] = {'value': cpu['steps_per_s'], 'unit': 'steps/s', 'cores': os.cpu_count() or 1, 'kind': 'port',
                                     'sample': f"{cpu['tasks']} of {cpu['of_tasks']} tasks of one step, a few of each of its {cpu['kinds']} op kinds, {cpu['seconds']:.1f} s on the numpy oracle; step time = sum over kinds of count x mean task time"}
@@ -548,31 +546,49 @@ def run_decode(args, device):
     pk, kind = peaks()
     gbs = bytes_tok * tok_s / 1e9
     tok = np.zeros(1, np.int32)
+    n_e2e = min(ntok, max(1, cfg.tmax - cfg.ctx - warm - ntok - 8), 64)      # the cache has room for tmax - ctx appended tokens in all
     t0 = time.perf_counter()
-    for _ in range(ntok):
+    for _ in range(n_e2e):
         ex.run()
         ex._check(ex.L.kvm_read_buffer_raw(ex._h, ex.index('u0.tok'), tok.ctypes.data, 4, 0))
-    e2e = ntok / (time.perf_counter() - t0)
+    e2e = n_e2e / (time.perf_counter() - t0)
     out = {'metric': 'decode_tokens_per_s', 'workload': f'{args.decode_model}: {cfg.layers}L hidden {cfg.hidden} {cfg.heads}q/{cfg.kv_heads}kv heads hd{cfg.head_dim} ffn {cfg.ffn} '
-                                                      f'vocab {cfg.vocab}, bf16 weights, batch {cfg.batch}, context {cfg.ctx}, greedy; {len(bundle.tasks)} tasks per token, no QK-norm',
-           'value': tok_s, 'unit': 'tok/s', 'ms_per_token': res.ms / ntok, 'tokens': ntok, 'e2e': {'value': e2e, 'unit': 'tok/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 4},
+                                                      f'vocab {cfg.vocab}, bf16 weights, batch {cfg.batch}, context {cfg.ctx}, greedy; {len(bundle.tasks)} tasks per token, reference op set (the QK-norm variant is timed beside it)',
+           'value': tok_s, 'unit': 'tok/s', 'ms_per_token': res.ms / ntok, 'tokens': ntok, 'e2e': {'value': e2e, 'unit': 'tok/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 4, 'tokens': n_e2e},
            'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'unit': 'GB/s', 'frac': gbs / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
-                        'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': None}, 'last_token': int(tok[0]),
+                        'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs', 'traffic': bytes_tok * DECODE_TRAFFIC_RATIO,
+                        'traffic_note': 'DRAM bytes of the 4-layer cut under ncu (3.12 GB for 2.86 GB algorithmic), scaled by the algorithmic bytes'}, 'last_token': int(tok[0]),
            'path': {'static_schedule': path[0], 'stream_ring': path[1], 'planned_us_per_token': path[2]}}
     ex.close()
-    try:        # the same shape with 8 independent users (one row each, as the reference serves a batch): every user streams the weights again
+    pkh = pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])
+    try:        # Qwen3's per-head QK RMSNorm in front of the rotary embedding (extension op 300; not in the reference op set)
+        cfgq = preset(args.decode_model, qk_norm=True)
+        with Executor(device=device) as exq:
+            exq.load(build_decode(cfgq).to_bundle(check=False))
+            exq.run_steps(warm)
+            rq = exq.run_steps(min(ntok, 32))
+        msq = rq.ms / min(ntok, 32)
+        out['qk_norm'] = {'value': 1e3 / msq, 'unit': 'tok/s', 'ms_per_token': msq, 'roofline_frac': bytes_tok / (msq / 1e3) / 1e9 / pkh}
+    except Exception as e:
+        out['qk_norm'] = {'error': str(e)[:300]}
+    try:        # batch 8, two ways: the users as ROWS of shared activation matrices (extension op 301: one pass over the weights per
+        #         step), and as 8 independent row users (the reference's op set: every user streams the weights again)
+        from kvm_b200.workloads.decode import build_decode_rows
         cfg8 = preset(args.decode_model, batch=8)
-        b8 = build_decode(cfg8).to_bundle(check=False)
-        with Executor(device=device) as ex8:
-            ex8.load(b8)
-            ex8.run_steps(2)
-            r8 = ex8.run_steps(6)
-        ms8 = r8.ms / 6
         ideal = weight_bytes(cfg8) + 8 * kv_bytes(cfg8, cfg8.ctx + 5)
-        out['batch8'] = {'value': 8 / (ms8 / 1e3), 'unit': 'tok/s', 'ms_per_step': ms8, 'tasks_per_step': len(b8.tasks),
-                         'roofline': {'bound': 'hbm', 'achieved': ideal / (ms8 / 1e3) / 1e9, 'unit': 'GB/s', 'peak': pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
-                                      'frac': ideal / (ms8 / 1e3) / 1e9 / pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']), 'bytes_per_step': ideal,
-                                      'note': 'algorithmic bytes count the weights once; the users are independent row tasks here and stream them 8 times'}}
+        out['batch8'] = {}
+        for tag, builder in (('rows', build_decode_rows), ('users', build_decode)):
+            b8 = builder(cfg8).to_bundle(check=False)
+            with Executor(device=device) as ex8:
+                ex8.load(b8)
+                ex8.run_steps(2)
+                r8 = ex8.run_steps(6)
+            ms8 = r8.ms / 6
+            out['batch8'][tag] = {'value': 8 / (ms8 / 1e3), 'unit': 'tok/s', 'ms_per_step': ms8, 'tasks_per_step': len(b8.tasks),
+                                  'roofline': {'bound': 'hbm', 'achieved': ideal / (ms8 / 1e3) / 1e9, 'unit': 'GB/s', 'peak': pkh, 'frac': ideal / (ms8 / 1e3) / 1e9 / pkh,
+                                               'bytes_per_step': ideal}}
+            del b8
+        out['batch8']['note'] = 'algorithmic bytes count the weights once per step and the 8 caches; the independent users stream the weights 8 times'
     except Exception as e:
         out['batch8'] = {'error': str(e)[:300]}
     return out
@@ -724,6 +740,25 @@ def run_alone_more(device, pk):
             else:
                 e.flat(op, [a], [o], N * F, {'x': a, 'out': o}, f'{op}{r}')
         mem(name, g, 4 * N * F * per)
+    # ---- column reductions at the step's granularity (64 columns x all rows per task): bias gradients (colsum of a bf16 [N, F]
+    #      activation gradient) and the norm layers' dgamma / dbeta (x and dy bf16, mean and rstd per row)
+    from kvm_b200.workloads.graph import Graph
+    g = Graph('alone')
+    reps = 3
+    for r in range(reps):
+        x = g.buffer(f'x{r}', N, F, 'bf16', sd(r + 1, 1.0))
+        o = g.buffer(f'o{r}', 1, F)
+        for c0 in range(0, F, cfg.col_chunk):
+            g.task('colsum', {'x': x, 'out': o, 'R': N, 'c0': c0, 'c1': min(c0 + cfg.col_chunk, F), 'acc': 0})
+    mem('colsum', g, reps * N * F * 2)
+    g = Graph('alone')
+    for r in range(reps):
+        x, dy = g.buffer(f'x{r}', N, F, 'bf16', sd(r + 1, 1.0)), g.buffer(f'dy{r}', N, F, 'bf16', sd(r + 11, 1.0))
+        mu, rs = g.buffer(f'mu{r}', 1, N, init=sd(r + 21, 1.0)), g.buffer(f'rs{r}', 1, N, init=sd(r + 31, 1.0))
+        dg, db = g.buffer(f'dg{r}', 1, F), g.buffer(f'db{r}', 1, F)
+        for c0 in range(0, F, cfg.col_chunk):
+            g.task('norm_bwd_params', {'x': x, 'dy': dy, 'mean': mu, 'rstd': rs, 'dgamma': dg, 'dbeta': db, 'R': N, 'd': F, 'c0': c0, 'c1': min(c0 + cfg.col_chunk, F), 'acc': 0})
+    mem('norm_bwd_params', g, reps * N * F * 4)
     return out
 
 
@@ -780,7 +815,8 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--model', default='gpt_162m')
     ap.add_argument('--decode-model', default='qwen3_8b')
-    ap.add_argument('--decode-tokens', type=int, default=32, help='tokens of the decode measurement appended to the line (0 = skip)')
+    ap.add_argument('--decode-tokens', type=int, default=128, help='tokens of the decode measurement appended to the line (0 = skip)')
+    ap.add_argument('--extras', default='decode,alone,small,355m', help='objects appended to the line at one GPU: decode, alone (kernels_alone), small (small_models), 355m; empty for none (profiling runs)')
     ap.add_argument('--cpu-seconds', type=float, default=15.0, help='length of the CPU-oracle sample behind cpu_baseline (0 = skip)')
     ap.add_argument('--cpu-step-limit', type=float, default=240.0, help='--impl reference: time limit of the one real CPU step')
     args = ap.parse_args()

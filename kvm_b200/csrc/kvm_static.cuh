@@ -197,11 +197,6 @@ KVM_OP_FN void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb
   {
     const int r = warp / KP, part = warp % KP;
     const int plen = (((K + KP - 1) / KP) + 255) & ~255, kb = part * plen, ke = min(K, kb + plen);
-    // the warp's slice of the activations stays in registers for the whole task (at most 2048 values: eight 16-byte pieces per
-    // lane), so a stage costs one pass over its weights in shared memory and nothing else
-    uint4 xr[8];
-#pragma unroll
-    for (int sg = 0; sg < 8; ++sg) { const int k = kb + sg * 256 + lane * 8; xr[sg] = k < ke ? *(const uint4*)(vs + k) : make_uint4(0, 0, 0, 0); }
     for (int ci = 0; ci < NC; ++ci) {
       const unsigned it = cit + ci;
       unsigned long long tw = 0;
@@ -210,24 +205,28 @@ KVM_OP_FN void kvm_gemv_ring(const KvmCtx& c, const int32_t* a, const KvmBuf* lb
       if (stamp && tid == 0) { const unsigned long long d = kvm_globaltimer() - tw; t_wait += d; if (ci == 0) t_first = d; }
       if (!waited) break;                                  // warp-uniform
       if (ok && r < R && ci * R + r < rows) {
-        const unsigned char* st = kvm_ring_stage(ring, it) + (size_t)r * K * 2 + (size_t)(kb + lane * 8) * 2;
+        const unsigned char* st = kvm_ring_stage(ring, it) + (size_t)r * K * 2;
         float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
-#pragma unroll
-        for (int sg = 0; sg < 8; sg += 2) {
-          if (kb + sg * 256 < ke) {
-            const uint4 wa = *(const uint4*)(st + sg * 512), xa = xr[sg];
-            acc0 = fmaf(kvm_bf16lo(xa.x), kvm_bf16lo(wa.x), acc0); acc1 = fmaf(kvm_bf16hi(xa.x), kvm_bf16hi(wa.x), acc1);
-            acc0 = fmaf(kvm_bf16lo(xa.y), kvm_bf16lo(wa.y), acc0); acc1 = fmaf(kvm_bf16hi(xa.y), kvm_bf16hi(wa.y), acc1);
-            acc0 = fmaf(kvm_bf16lo(xa.z), kvm_bf16lo(wa.z), acc0); acc1 = fmaf(kvm_bf16hi(xa.z), kvm_bf16hi(wa.z), acc1);
-            acc0 = fmaf(kvm_bf16lo(xa.w), kvm_bf16lo(wa.w), acc0); acc1 = fmaf(kvm_bf16hi(xa.w), kvm_bf16hi(wa.w), acc1);
-          }
-          if (kb + (sg + 1) * 256 < ke) {
-            const uint4 wb = *(const uint4*)(st + (sg + 1) * 512), xb = xr[sg + 1];
-            acc2 = fmaf(kvm_bf16lo(xb.x), kvm_bf16lo(wb.x), acc2); acc3 = fmaf(kvm_bf16hi(xb.x), kvm_bf16hi(wb.x), acc3);
-            acc2 = fmaf(kvm_bf16lo(xb.y), kvm_bf16lo(wb.y), acc2); acc3 = fmaf(kvm_bf16hi(xb.y), kvm_bf16hi(wb.y), acc3);
-            acc2 = fmaf(kvm_bf16lo(xb.z), kvm_bf16lo(wb.z), acc2); acc3 = fmaf(kvm_bf16hi(xb.z), kvm_bf16hi(wb.z), acc3);
-            acc2 = fmaf(kvm_bf16lo(xb.w), kvm_bf16lo(wb.w), acc2); acc3 = fmaf(kvm_bf16hi(xb.w), kvm_bf16hi(wb.w), acc3);
-          }
+        int k = kb + lane * 8;
+        for (; k + 256 < ke; k += 512) {                   // two 16-byte pieces of the row and of the activations in flight per trip
+          const uint4 wa = *(const uint4*)(st + k * 2), wb = *(const uint4*)(st + (k + 256) * 2);
+          const uint4 xa = *(const uint4*)(vs + k), xb = *(const uint4*)(vs + k + 256);
+          acc0 = fmaf(kvm_bf16lo(xa.x), kvm_bf16lo(wa.x), acc0); acc1 = fmaf(kvm_bf16hi(xa.x), kvm_bf16hi(wa.x), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.x), kvm_bf16lo(wb.x), acc2); acc3 = fmaf(kvm_bf16hi(xb.x), kvm_bf16hi(wb.x), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.y), kvm_bf16lo(wa.y), acc0); acc1 = fmaf(kvm_bf16hi(xa.y), kvm_bf16hi(wa.y), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.y), kvm_bf16lo(wb.y), acc2); acc3 = fmaf(kvm_bf16hi(xb.y), kvm_bf16hi(wb.y), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.z), kvm_bf16lo(wa.z), acc0); acc1 = fmaf(kvm_bf16hi(xa.z), kvm_bf16hi(wa.z), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.z), kvm_bf16lo(wb.z), acc2); acc3 = fmaf(kvm_bf16hi(xb.z), kvm_bf16hi(wb.z), acc3);
+          acc0 = fmaf(kvm_bf16lo(xa.w), kvm_bf16lo(wa.w), acc0); acc1 = fmaf(kvm_bf16hi(xa.w), kvm_bf16hi(wa.w), acc1);
+          acc2 = fmaf(kvm_bf16lo(xb.w), kvm_bf16lo(wb.w), acc2); acc3 = fmaf(kvm_bf16hi(xb.w), kvm_bf16hi(wb.w), acc3);
+        }
+        for (; k < ke; k += 256) {
+          const uint4 wv = *(const uint4*)(st + k * 2);
+          const uint4 xv = *(const uint4*)(vs + k);
+          acc0 = fmaf(kvm_bf16lo(xv.x), kvm_bf16lo(wv.x), acc0); acc1 = fmaf(kvm_bf16hi(xv.x), kvm_bf16hi(wv.x), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.y), kvm_bf16lo(wv.y), acc0); acc1 = fmaf(kvm_bf16hi(xv.y), kvm_bf16hi(wv.y), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.z), kvm_bf16lo(wv.z), acc0); acc1 = fmaf(kvm_bf16hi(xv.z), kvm_bf16hi(wv.z), acc1);
+          acc0 = fmaf(kvm_bf16lo(xv.w), kvm_bf16lo(wv.w), acc0); acc1 = fmaf(kvm_bf16hi(xv.w), kvm_bf16hi(wv.w), acc1);
         }
         const float sum = kvm_warp_sum((acc0 + acc1) + (acc2 + acc3));
         if (lane == 0) parts[(ci * R + r) * KP + part] = sum;
