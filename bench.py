@@ -452,31 +452,78 @@ def run_dp(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
-def run_decode_tp(args, rank, world, device):
-    """Tensor-parallel greedy decode of the 8B shape over the `world` GPUs (strong scaling: the same token, weights and cache split
-    over the ranks): 2 * layers + 1 launches of the persistent kernel per token with an NCCL all-reduce of the [1, hidden] partial
-    between them, the LM head split by vocabulary.  Timed with CUDA events around whole tokens, max over ranks."""
+def tp_parity_tokens(rank, world, device, exchange_handles, ntok=6):
+    """The one-launch tensor-parallel form on a small model whose shards are exact slices of the unsharded weights: the greedy tokens
+    over the `world` GPUs must equal the CPU oracle's tokens of the unsharded graph (the checker runs on rank 0's host cores)."""
     import torch
     import torch.distributed as dist
-    from kvm_b200.tp import TensorParallelDecode, pick_token
-    from kvm_b200.workloads.decode import build_decode_tp, kv_bytes, preset, weight_bytes
+    from kvm_b200.tp import TensorParallelDecodeFused, pick_token
+    from kvm_b200.workloads.decode import build_decode, preset
+    cfg = preset('decode_tiny', init_std=0.08, kv_heads=max(2, world))          # 8 query heads: up to 8 ranks
+    if cfg.heads % world or cfg.kv_heads % world or cfg.ffn % world or cfg.vocab % world:
+        return {'skipped': f'decode_tiny does not split over {world} ranks'}
+    logits = torch.zeros(1, cfg.vocab // world, dtype=torch.float32, device='cuda')
+    tok = torch.full((1, 1), 3 % cfg.vocab, dtype=torch.int32, device='cuda')
+    tpd = TensorParallelDecodeFused(cfg, rank, world, device, {'u0.logits': logits.data_ptr(), 'u0.tok': tok.data_ptr()}, exchange_handles, exact=True)
+    got = []
+    for _ in range(ntok):
+        torch.cuda.synchronize(); dist.barrier()
+        tpd.ex.run()
+        val, idx = logits.max(dim=1)
+        allp = torch.zeros(world, 2, dtype=torch.float64, device='cuda')
+        dist.all_gather_into_tensor(allp, torch.stack([val.double(), (idx + rank * logits.shape[1]).double()], dim=1))
+        t = pick_token((float(a), int(b)) for a, b in allp.cpu().numpy())
+        tok.fill_(t)
+        got.append(t)
+    torch.cuda.synchronize(); dist.barrier()
+    tpd.close()
+    ref = None
+    if rank == 0:
+        from oracle.vm_np import VM
+        b = build_decode(cfg).to_bundle()
+        vm, ref = VM(b), []
+        for _ in range(ntok):
+            vm.run()
+            ref.append(int(vm.buffer('u0.tok').a[0, 0]))
+            vm = VM(b, buffers=vm.bufs)
+    return {'model': 'decode_tiny, exact shards', 'tokens': got, 'oracle_tokens': ref, 'match': None if ref is None else got == ref}
+
+
+def run_decode_tp(args, rank, world, device):
+    """Tensor-parallel greedy decode of the 8B shape over the `world` GPUs (strong scaling: the same token, weights and cache split
+    over the ranks), timed with CUDA events around whole tokens, max over ranks.  Default: ONE launch of the persistent kernel per
+    token and rank, the two partial sums per layer are tasks (peer stores into the other ranks' inboxes over NVLink, flag release,
+    bounded wait: extension ops 302 / 303); only the token choice over the vocabulary slices is a host-side all-gather.
+    KVM_B200_TP=segments: 2 * layers + 1 launches per token with an NCCL all-reduce of the [1, hidden] partial between them."""
+    import torch
+    import torch.distributed as dist
+    from kvm_b200.tp import TensorParallelDecode, TensorParallelDecodeFused, pick_token
+    from kvm_b200.workloads.decode import kv_bytes, preset, weight_bytes
     cfg = preset(args.decode_model)
     if cfg.heads % world or cfg.kv_heads % world or cfg.ffn % world or cfg.vocab % world:
         return {'error': f'{args.decode_model} does not split over {world} ranks'}
-    names = [f'u0.l{l}.{n}' for l in range(cfg.layers) for n in ('x1', 'x2')]
+    fused = os.environ.get('KVM_B200_TP', 'fused') != 'segments'
+    names = [] if fused else [f'u0.l{l}.{n}' for l in range(cfg.layers) for n in ('x1', 'x2')]
     bufs = {n: torch.zeros(1, cfg.hidden, dtype=torch.float32, device='cuda') for n in names}
     logits = torch.zeros(1, cfg.vocab // world, dtype=torch.float32, device='cuda')
     tok = torch.full((1, 1), 3, dtype=torch.int32, device='cuda')
     bind = {n: t.data_ptr() for n, t in bufs.items()}
     bind.update({'u0.logits': logits.data_ptr(), 'u0.tok': tok.data_ptr()})
     from kvm_b200.executor import CFG_CHAIN
-    tpd = TensorParallelDecode(cfg, rank, world, device, bind, flags=CFG_CHAIN)
-    comm = {'n': 0}
+
+    def exchange_handles(mine):
+        out = [None] * world
+        dist.all_gather_object(out, mine)
+        return out
+
+    if fused:
+        tpd = TensorParallelDecodeFused(cfg, rank, world, device, bind, exchange_handles, flags=CFG_CHAIN)
+    else:
+        tpd = TensorParallelDecode(cfg, rank, world, device, bind, flags=CFG_CHAIN)
 
     def all_reduce_sum(name):           # first tokens: launches on the handles' own streams, so the host waits for the collective
         dist.all_reduce(bufs[name], op=dist.ReduceOp.SUM)
         torch.cuda.current_stream().synchronize()
-        comm['n'] += 1
 
     def all_reduce_queued(name):        # timed tokens: everything is queued on one stream, stream order is the only synchronisation
         dist.all_reduce(bufs[name], op=dist.ReduceOp.SUM)
@@ -490,28 +537,40 @@ def run_decode_tp(args, rank, world, device):
         tok.fill_(pick_token((float(a), int(b)) for a, b in p))
         torch.cuda.current_stream().synchronize()
 
-    ntok, warm = min(args.decode_tokens, 8), 2
+    parity = None
+    if fused:
+        try:
+            parity = tp_parity_tokens(rank, world, device, exchange_handles)
+        except Exception as e:
+            parity = {'error': str(e)[:200]}
+    step = (lambda: tpd.token(choose)) if fused else (lambda: tpd.token(all_reduce_sum, choose))
+    step_async = (lambda: tpd.token_async(choose)) if fused else (lambda: tpd.token_async(all_reduce_queued, choose))
+    ntok, warm = min(args.decode_tokens, 32 if fused else 8), 2
     for _ in range(warm):
-        tpd.token(all_reduce_sum, choose)
+        torch.cuda.synchronize(); dist.barrier()
+        step()
     tpd.use_stream(torch.cuda.current_stream().cuda_stream)
-    tpd.token_async(all_reduce_queued, choose)
+    step_async()
     dist.barrier(); torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(ntok):
-        tpd.token_async(all_reduce_queued, choose)
+        step_async()
     e1.record(); torch.cuda.synchronize()
-    kern_ms = sum(tpd.finish())         # kernel time of the last token's segments
+    kern_ms = sum(tpd.finish())         # kernel time of the last token's launches
     t = torch.tensor([e0.elapsed_time(e1), kern_ms * ntok], dtype=torch.float64, device='cuda')
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     last = int(tok.item())
+    nlaunch = 3 * len(tpd.handles)
     tpd.close()
     ms_tok = float(t[0]) / ntok
     pk, kind = peaks()
     bytes_tok = weight_bytes(cfg) + kv_bytes(cfg, cfg.ctx + warm + ntok / 2)
     gbs = bytes_tok / (ms_tok / 1e3) / 1e9
+    how = ('one launch per token and rank; the 2 x layers partial sums are tasks: peer stores into the other ranks\' inboxes, flag release, bounded wait'
+           if fused else '2 x layers + 1 launches per token with an NCCL all-reduce of the partial between them')
     return {'metric': 'decode_tokens_per_s', 'value': 1e3 / ms_tok, 'unit': 'tok/s', 'scaling': 'strong', 'n_gpus': world, 'ms_per_token': ms_tok,
-            'kernel_ms_per_token': float(t[1]) / ntok, 'launches_per_token': 3 * len(tpd.handles), 'allreduces_per_token': 2 * cfg.layers, 'tokens': ntok, 'last_token': last,
+            'parity': parity, 'kernel_ms_per_token': float(t[1]) / ntok, 'launches_per_token': nlaunch, 'exchanges_per_token': 2 * cfg.layers, 'exchange': how, 'tokens': ntok, 'last_token': last,
             'workload': f'{args.decode_model} batch 1 context {cfg.ctx}, tensor parallel over {world} GPUs (heads / FFN columns / vocabulary split), seeded shards',
             'roofline': {'bound': 'hbm', 'achieved': gbs, 'unit': 'GB/s', 'peak': world * pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs']),
                          'frac': gbs / (world * pk.get('hbm_gbs', PEAK_FALLBACK['hbm_gbs'])), 'bytes_per_token': bytes_tok, 'peak_source': f'{kind} hbm_gbs x {world} GPUs'}}

@@ -79,6 +79,13 @@ int kvm_add_buffer(KvmExec* h, int32_t rows, int32_t cols, int32_t dtype, const 
 int kvm_bind_buffer(KvmExec* h, void* dev_ptr, int32_t rows, int32_t cols, int32_t ld, int32_t dtype);
 /* Device address of buffer idx (NULL on a bad index). */
 void* kvm_buffer_ptr(KvmExec* h, int32_t idx);
+/* Sharing a buffer with an executor in another process of the same node, for the peer exchange ops (peer_put_signal / peer_wait_sum,
+ * include/kvm_ops.def; the reference takes peer pointers from CUDA P2P / IPC the same way, include/mvm_ops_comm.def:5-9):
+ * the owner exports a 64-byte handle of a buffer it allocated, the peer maps it (kvm_ipc_open) and binds the pointer as a table
+ * entry of its own (kvm_bind_buffer); kvm_ipc_close unmaps it after the peer's executor is destroyed. */
+int kvm_ipc_export(KvmExec* h, int32_t idx, void* handle64);
+int kvm_ipc_open(KvmExec* h, const void* handle64, void** dev_ptr);
+int kvm_ipc_close(KvmExec* h, void* dev_ptr);
 /* Raw host -> device / device -> host copies of [offset, offset+bytes) of a buffer's storage. */
 int kvm_write_buffer(KvmExec* h, int32_t idx, const void* host, size_t bytes, size_t offset);
 int kvm_read_buffer_raw(KvmExec* h, int32_t idx, void* host, size_t bytes, size_t offset);

@@ -47,6 +47,7 @@ struct KvmCtx {
   int* ctl;                   // executor control words in shared memory (ctl[0] = TMEM base address)
   const void* tmaps;          // tensor-map table of the tensor-core tasks
   int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
+  unsigned long long deadline;   // %globaltimer value after which a task that waits for something outside the launch (a peer's flag) gives up
   float* rope_cache;          // shared memory, 66 floats kept over the tasks of a launch: [0] theta bits, [1] head dimension bits, [2..] the inverse frequencies of that pair (or nullptr)
   int engine;                 // 1: the kernel's engine warps run the mainloops of tensor-core GEMM tiles, the op body is their epilogue only
   unsigned gemm_seq;          // with engine: how many tensor-core GEMM tiles this CTA ran before this one (accumulator = gemm_seq & 1)

@@ -7,6 +7,7 @@
 #include "kvm_ops_mm.cuh"
 #include "kvm_ops_attn.cuh"
 #include "kvm_ops_decode.cuh"
+#include "kvm_ops_peer.cuh"
 #include "kvm_gemm_tc.cuh"
 #include "kvm_attn_tc.cuh"
 #include "kvm_state.cuh"
@@ -73,6 +74,8 @@ static __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* a, c
     case 136: kvm_op_attn_decode_merge(c, a); break;
     case 300: kvm_op_attn_decode_part_qkn(c, a); break;
     case 301: kvm_op_gemv_bf16_rows(c, a); break;
+    case 302: kvm_op_peer_put_signal(c, a); break;
+    case 303: kvm_op_peer_wait_sum(c, a); break;
     default: c.fail(KVM_ERR_BAD_OP, op); break;
   }
 }

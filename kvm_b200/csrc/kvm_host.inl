@@ -177,6 +177,34 @@ extern "C" int kvm_bind_buffer(KvmExec* h, void* dev_ptr, int32_t rows, int32_t 
   return (int)h->bufs.size() - 1;
 }
 
+// Sharing a buffer with an executor in another process on the same node (the inbox and flag words of the peer exchange ops):
+// the owner exports a 64-byte handle of the buffer's allocation, the peer maps it and binds the pointer as one of its own
+// table entries (kvm_bind_buffer).  Owned buffers are allocations of their own, so the handle addresses exactly the buffer.
+extern "C" int kvm_ipc_export(KvmExec* h, int32_t idx, void* handle64) {
+  if (!h || !handle64 || idx < 0 || idx >= (int)h->bufs.size()) { if (h) h->error = "kvm_ipc_export: bad argument"; return KVM_E_ARG; }
+  bool owned = false;
+  for (auto& o : h->owned) if (o.p == h->bufs[idx].p) owned = true;
+  if (!owned) { h->error = "kvm_ipc_export: only buffers this executor allocated can be exported"; return KVM_E_ARG; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, h->bufs[idx].p));
+  return 0;
+}
+extern "C" int kvm_ipc_open(KvmExec* h, const void* handle64, void** out) {
+  if (!h || !handle64 || !out) { if (h) h->error = "kvm_ipc_open: bad argument"; return KVM_E_ARG; }
+  cudaSetDevice(h->device);
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle64, sizeof hd);
+  KVM_CUDA(cudaIpcOpenMemHandle(out, hd, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+extern "C" int kvm_ipc_close(KvmExec* h, void* ptr) {
+  if (!h || !ptr) return KVM_E_ARG;
+  cudaSetDevice(h->device);
+  KVM_CUDA(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+
 extern "C" void* kvm_buffer_ptr(KvmExec* h, int32_t idx) { return (h && idx >= 0 && idx < (int)h->bufs.size()) ? h->bufs[idx].p : nullptr; }
 
 static int kvm_buf_span(KvmExec* h, int idx, size_t bytes, size_t offset) {

@@ -410,6 +410,7 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
     c.smem = kvm_smem + used; c.smem_bytes = (int)dyn - used;
     c.engine = engine_on ? 1 : 0; c.gemm_seq = 0;
     c.rope_cache = (float*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288);
+    c.deadline = t_begin + S.timeout_ns - S.timeout_ns / 8;      // a task's own wait gives up (and names itself) before the launch's stall limit does
     unsigned tiles = 0;
     int cur = 0;
     while (true) {

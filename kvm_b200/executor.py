@@ -78,6 +78,9 @@ SYMBOLS = {
     'kvm_task_counts': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_trace': (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     'kvm_trace_detail': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32]),
+    'kvm_ipc_export': (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    'kvm_ipc_open': (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    'kvm_ipc_close': (C.c_int, [C.c_void_p, C.c_void_p]),
     'kvm_launch_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     'kvm_plan_info': (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     'kvm_tc_task_count': (C.c_int, [C.c_void_p]),
@@ -195,6 +198,18 @@ class Executor:
 
     def index(self, buf) -> int:
         return buf if isinstance(buf, int) else self.names[buf]
+
+    def ipc_export(self, buf) -> bytes:
+        """64-byte handle of a buffer this executor allocated, for an executor in another process of the node (kvm_ipc_export)."""
+        h = C.create_string_buffer(64)
+        self._check(self.L.kvm_ipc_export(self._h, self.index(buf), h))
+        return h.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Device pointer of a peer's exported buffer mapped into this process (kvm_ipc_open)."""
+        p = C.c_void_p()
+        self._check(self.L.kvm_ipc_open(self._h, C.c_char_p(handle), C.byref(p)))
+        return p.value
 
     def buffer_ptr(self, buf) -> int:
         return self.L.kvm_buffer_ptr(self._h, self.index(buf))

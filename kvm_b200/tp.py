@@ -5,7 +5,9 @@ collective (NCCL through torch.distributed in bench.py).  The LM head is sharded
 token of its slice and the best proposal wins (lowest index on ties, as `argmax` does).
 
 This is what the reference plans with its tensor-parallel partitioner and in-kernel comm ops (`runtime/partition.py`,
-include/mvm_ops_comm.def); here the exchange is a library collective between launches.
+include/mvm_ops_comm.def).  Two forms: `TensorParallelDecode` (the exchange is a library collective between launches) and
+`TensorParallelDecodeFused` (ONE launch per token and rank: the sums are tasks that store the partial into the peers' inboxes
+over NVLink, release a flag word and wait, bounded, for the peers' flags; extension ops 302 / 303).
 """
 from __future__ import annotations
 
@@ -85,3 +87,57 @@ class TensorParallelDecode:
     def close(self):
         for ex in reversed(self.handles):
             ex.close()
+
+
+class TensorParallelDecodeFused:
+    """One executor per rank, one launch per token: the partial sums over the ranks are tasks of the graph (peer_put_signal /
+    peer_wait_sum).  `exchange_handles(handles: dict) -> list[dict]` is the caller's all-gather of small Python objects over the
+    ranks (torch.distributed.all_gather_object in bench.py): every rank exports its inbox and flag buffers, maps the peers' and
+    binds them as the graph's `tp.peer{p}.*` buffers.  Only the token choice (one proposal per rank) stays with the caller."""
+
+    def __init__(self, cfg: DecodeConfig, rank: int, world: int, device: int, bind: dict, exchange_handles, exact: bool = False, **exec_kw):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        g, _, _ = build_decode_tp(cfg, rank, world, exact, fused=True)
+        self.bundle = b = g.to_bundle(check=False)
+        self.ex = ex = Executor(device=device, **exec_kw)
+        self._mapped = []
+        peers = None
+        for spec in b.buffers:
+            name = spec['name']
+            if name.startswith('tp.peer'):
+                if peers is None:            # this rank's inbox and flag words exist by now (they are the first buffers of the graph)
+                    mine = {'inbox': ex.ipc_export('tp.inbox'), 'flag': ex.ipc_export('tp.flag')}
+                    peers = exchange_handles(mine)
+                p, what = int(name.split('.')[1][4:]), name.split('.')[2]
+                ptr = ex.ipc_open(peers[p][what])
+                self._mapped.append(ptr)
+                ex.bind_buffer(ptr, spec['rows'], spec['cols'], spec['dtype'], name=name)
+            elif name in bind:
+                ex.bind_buffer(bind[name], spec['rows'], spec['cols'], spec['dtype'], name=name)
+            else:
+                ex.add_bundle_buffer(b, spec)
+        ex.submit(b.tasks, b.succ, b.args)
+        ex.bundle = b
+        self.handles = [ex]
+
+    def token(self, choose):
+        """One decode step: one launch, then the caller's token choice over the ranks' logits slices."""
+        ms = self.ex.run().ms
+        choose()
+        return ms
+
+    def use_stream(self, cuda_stream: int):
+        self.ex.set_stream(cuda_stream)
+
+    def token_async(self, choose):
+        self.ex.start()
+        choose()
+
+    def finish(self):
+        return [self.ex.finish().ms]
+
+    def close(self):
+        for ptr in self._mapped:
+            self.ex.L.kvm_ipc_close(self.ex._h, ptr)
+        self._mapped = []
+        self.ex.close()

@@ -284,7 +284,7 @@ def build_decode_rows(c: DecodeConfig, exact_caches: bool = False) -> Graph:
     return g
 
 
-def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False):
+def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False, fused: bool = False):
     """Rank `rank`'s share of the one-token graph under tensor parallelism over `world` ranks, batch 1.
 
     q / k / v / gate / up are sharded by output rows (heads, FFN columns), the o and down projections by input columns, the
@@ -294,6 +294,14 @@ def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False)
     buffer to sum over the ranks after segment i (None after the last one, whose `logits` hold the rank's vocabulary slice).
     exact=True takes every shard as a slice of the full model's seeded weights (small configurations, parity tests);
     otherwise the shards are seeded on their own (same shapes and traffic, a different random model).
+
+    fused=True keeps the token in ONE graph (one launch per token and rank): the sums over the ranks become tasks.  The o / down
+    projection writes its partial to a buffer of its own; one peer_put_signal task per peer stores it into that peer's inbox row
+    (site, this rank) and releases the flag word (site, this rank) with version lens + 1, and a peer_wait_sum task waits for the
+    other ranks' flags and adds the partials in rank order (extension ops 302 / 303, include/kvm_ops.def).  The first buffers of
+    the graph are `tp.inbox` [sites * world, hidden] and `tp.flag` [1, sites * world] (this rank's, written by the peers) and, per
+    peer p, `tp.peer{p}.inbox` / `tp.peer{p}.flag`: the host binds those to the peers' memory before the first run.  cuts and
+    exchanges then describe a single segment.
     """
     from .. import initgen
     P = world
@@ -322,6 +330,21 @@ def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False)
             n1 = min(n0 + rows, n)
             g.task('gemv_bf16', {'x': x, 'x2': x2, 'gamma': gamma, 'w': w, 'out': out, 'res': res, 'n0': n0, 'n1': n1, 'K': k, 'pro': pro, 'eps': c.eps},
                    [x, x2, gamma, (w, (n0, n1)), (res, (0, 1), (n0, n1)) if res else None], [(out, (0, 1), (n0, n1))], prio, f'{tag}.{i}')
+
+    sites = 2 * c.layers
+    if fused:
+        inbox, flag = g.buffer('tp.inbox', sites * P, d), g.buffer('tp.flag', 1, sites * P, 'i32')
+        peers = {p: (g.buffer(f'tp.peer{p}.inbox', sites * P, d), g.buffer(f'tp.peer{p}.flag', 1, sites * P, 'i32')) for p in range(P) if p != rank}
+
+    def exchange(site, partial, out, prio, tag):
+        """out = sum over the ranks of their `partial`, inside the launch."""
+        row0 = site * P
+        for p, (pin, pfl) in peers.items():
+            g.task('peer_put_signal', {'src': partial, 'dst': pin, 'src_off': 0, 'dst_off': (row0 + rank) * d, 'n': d, 'flag': pfl, 'var': row0 + rank, 'ver': 1,
+                                       'seq': lens, 'stride': 1}, [partial, lens], [(pin, (row0 + rank, row0 + rank + 1)), (pfl, (0, 1), (row0 + rank, row0 + rank + 1))],
+                   prio, f'{tag}.put{p}')
+        g.task('peer_wait_sum', {'partial': partial, 'inbox': inbox, 'flag': flag, 'out': out, 'res': None, 'n': d, 'row0': row0, 'rank': rank, 'world': P, 'ver': 1,
+                                 'seq': lens, 'stride': 1}, [partial, lens, (inbox, (row0, row0 + P)), (flag, (0, 1), (row0, row0 + P))], [out], prio, f'{tag}.sum')
 
     W('embed', V, d)
     g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})
@@ -366,15 +389,25 @@ def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False)
             g.task('attn_decode_merge', {'part': part, 'o': o, 'b': 0, 'h0': kvh * G, 'h1': (kvh + 1) * G, 'S': S, 'H': Hl, 'hd': hd},
                    [part], [(o, (0, 1), (kvh * G * hd, (kvh + 1) * G * hd))], prio, f'{tl}merge.{kvh}')
         x1 = g.buffer(tl + 'x1', 1, d)               # partial sum of the o projection (+ residual on rank 0); summed over the ranks after the segment
-        gemv(tl + 'o', o, wo, x1, d, Hl * hd, 0, res=x if rank == 0 else None, prio=prio)
-        cuts.append(len(g.tasks)); exchanges.append(x1)
+        if fused:
+            x1p = g.buffer(tl + 'x1p', 1, d)
+            gemv(tl + 'o', o, wo, x1p, d, Hl * hd, 0, res=x if rank == 0 else None, prio=prio)
+            exchange(2 * l, x1p, x1, prio, tl + 'x1')
+        else:
+            gemv(tl + 'o', o, wo, x1, d, Hl * hd, 0, res=x if rank == 0 else None, prio=prio)
+            cuts.append(len(g.tasks)); exchanges.append(x1)
         gate, up = g.buffer(tl + 'gate', 1, Fl), g.buffer(tl + 'up', 1, Fl)
         rgu = max(8, -(-2 * Fl // c.workers))
         gemv(tl + 'gate', x1, wg, gate, Fl, d, 1, gamma=ln2, prio=prio, rows=rgu)
         gemv(tl + 'up', x1, wu, up, Fl, d, 1, gamma=ln2, prio=prio, rows=rgu)
         xn = g.buffer(tl + 'x2', 1, d)
-        gemv(tl + 'down', gate, wd, xn, d, Fl, 2, x2=up, res=x1 if rank == 0 else None, prio=prio)
-        cuts.append(len(g.tasks)); exchanges.append(xn)
+        if fused:
+            xnp = g.buffer(tl + 'x2p', 1, d)
+            gemv(tl + 'down', gate, wd, xnp, d, Fl, 2, x2=up, res=x1 if rank == 0 else None, prio=prio)
+            exchange(2 * l + 1, xnp, xn, prio, tl + 'x2')
+        else:
+            gemv(tl + 'down', gate, wd, xn, d, Fl, 2, x2=up, res=x1 if rank == 0 else None, prio=prio)
+            cuts.append(len(g.tasks)); exchanges.append(xn)
         x = xn
     logits = g.buffer('u0.logits', 1, Vl)
     gemv('u0.head', x, 'wb.head', logits, Vl, d, 1, gamma='w.lnf', prio=1, rows=max(8, -(-Vl // (2 * c.workers))))

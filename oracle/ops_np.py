@@ -663,6 +663,42 @@ def gemv_bf16_rows(b, a, **kw):
         gemv_bf16(row, a, **kw)
 
 
+# ---- exchange between executors (extension ops 302 / 303) ---------------------------------------------------------------------------
+# Restated from the reference's put_signal and inbox versions (include/mvm_ops_comm.def:5-11, include/mvm_dist.cuh:73-77, CPU
+# model dist/commops.py): a peer buffer is simply another buffer of the table (in a CPU test: an array shared with the other
+# rank's VM), the flag word is written after the data.  PEER_WAIT is how long peer_wait_sum polls before it gives up.
+PEER_WAIT = 20.0
+
+
+def _seq_ver(b, a):
+    return a['ver'] + (int(b['seq'].a.flat[0]) * a['stride'] if b.get('seq') is not None else 0)
+
+
+def peer_put_signal(b, a, **kw):
+    n = a['n']
+    _need(n > 0 and a['src_off'] >= 0 and a['src_off'] + n <= b['src'].a.size and a['dst_off'] >= 0 and a['dst_off'] + n <= b['dst'].a.size, 'peer_put_signal: range')
+    _need(0 <= a['var'] < b['flag'].a.size, 'peer_put_signal: flag index')
+    b['dst'].a.reshape(-1)[a['dst_off']:a['dst_off'] + n] = b['src'].a.reshape(-1)[a['src_off']:a['src_off'] + n]
+    b['flag'].a.reshape(-1)[a['var']] = _seq_ver(b, a)          # after the data (release)
+
+
+def peer_wait_sum(b, a, **kw):
+    import time
+    n, row0, rank, world = a['n'], a['row0'], a['rank'], a['world']
+    _need(n > 0 and 1 <= world <= 32 and 0 <= rank < world and row0 >= 0, 'peer_wait_sum: arguments')
+    _need(row0 + world <= b['flag'].a.size and row0 + world <= b['inbox'].rows and n <= b['inbox'].cols, 'peer_wait_sum: range')
+    eff, flag = _seq_ver(b, a), b['flag'].a.reshape(-1)
+    t0 = time.monotonic()
+    while any(flag[row0 + p] < eff for p in range(world) if p != rank):
+        _need(time.monotonic() - t0 < PEER_WAIT, 'peer_wait_sum: timeout')
+        time.sleep(0.0005)
+    v = None if b.get('res') is None else b['res'].a.reshape(-1)[:n].astype(np.float32)
+    for p in range(world):
+        t = (b['partial'].a.reshape(-1)[:n] if p == rank else b['inbox'].a[row0 + p, :n]).astype(np.float32)
+        v = t.copy() if v is None else (v + t).astype(np.float32)
+    b['out'].a.reshape(-1)[:n] = v
+
+
 # ---- loss -------------------------------------------------------------------------------------------------------------------
 def softmax_ce_fwd(b, a, **kw):
     lg, tg, rl, ls = b['logits'], b['tgt'], b['rowloss'], b['lse']

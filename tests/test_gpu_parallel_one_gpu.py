@@ -118,3 +118,62 @@ def test_two_data_parallel_ranks_equal_gradient_accumulation(kvm_lib):
     assert moved
     for dp in dps:
         dp.close()
+
+
+# ---- the exchange ops of the one-launch tensor-parallel form (peer_put_signal 302, peer_wait_sum 303) on one GPU ------------------------
+# No second kernel runs here (two kernels that wait for one another must not share a GPU): the "peer" is host code that fills this
+# rank's inbox and flag word before the launch, or never does.
+def _exchange_graph(n=4096, seq0=40):
+    from kvm_b200.workloads.graph import Graph
+    rng = np.random.default_rng(5)
+    g = Graph('xchg')
+    g.data('partial', rng.standard_normal((1, n)).astype(np.float32))
+    g.data('res', rng.standard_normal((1, n)).astype(np.float32))
+    g.buffer('inbox', 2 * 2, n), g.buffer('flag', 1, 2 * 2, 'i32')
+    g.buffer('peer.inbox', 2 * 2, n), g.buffer('peer.flag', 1, 2 * 2, 'i32')      # stand-ins for the peer's memory
+    g.data('seq', np.array([[seq0]], np.int32), 'i32')
+    g.buffer('out', 1, n)
+    site, rank, world = 1, 0, 2
+    row0 = site * world
+    g.task('peer_put_signal', {'src': 'partial', 'dst': 'peer.inbox', 'src_off': 0, 'dst_off': (row0 + rank) * n, 'n': n, 'flag': 'peer.flag', 'var': row0 + rank,
+                               'ver': 1, 'seq': 'seq', 'stride': 1}, ['partial', 'seq'], ['peer.inbox', 'peer.flag'])
+    g.task('peer_wait_sum', {'partial': 'partial', 'inbox': 'inbox', 'flag': 'flag', 'out': 'out', 'res': 'res', 'n': n, 'row0': row0, 'rank': rank, 'world': world,
+                             'ver': 1, 'seq': 'seq', 'stride': 1}, ['partial', 'seq', 'inbox', 'flag', 'res'], ['out'])
+    return g.to_bundle(), n, row0, seq0
+
+
+@pytest.mark.parametrize('flags', ['static', 'queue'])
+def test_exchange_ops_deliver_and_sum_in_rank_order(kvm_lib, flags):
+    from kvm_b200.executor import CFG_DYNAMIC, CFG_STATIC, Executor
+    from oracle.vm_np import VM
+    b, n, row0, seq0 = _exchange_graph()
+    theirs = np.random.default_rng(6).standard_normal((1, n)).astype(np.float32)
+    vm = VM(b)
+    vm.buffer('inbox').a[row0 + 1] = theirs[0]
+    vm.buffer('flag').a[0, row0 + 1] = seq0 + 1
+    vm.run()
+    with Executor(flags=CFG_STATIC if flags == 'static' else CFG_DYNAMIC) as ex:
+        ex.load(b)
+        ex.write_buffer('inbox', theirs, offset_elems=(row0 + 1) * n)                  # what the peer's put would have stored ...
+        ex.write_buffer('flag', np.array([seq0 + 1], np.int32), offset_elems=row0 + 1)    # ... and released
+        res = ex.run()
+        assert res.status == 0 and res.done == 2
+        assert np.array_equal(ex.read_buffer('out'), vm.buffer('out').a)              # same order of additions: bit-equal
+        assert np.array_equal(ex.read_buffer('peer.inbox'), vm.buffer('peer.inbox').a)
+        assert ex.read_buffer('peer.flag').tolist() == vm.buffer('peer.flag').a.tolist() and ex.read_buffer('peer.flag')[0, row0] == seq0 + 1
+
+
+def test_exchange_wait_runs_out_when_the_peer_never_signals(kvm_lib):
+    """Failure detection without a fault: nothing sets the flag, the bounded wait ends after the launch timeout, the launch returns
+    KVM_ERR_TIMEOUT for that task and the handle stays usable."""
+    from kvm_b200 import abi
+    from kvm_b200.executor import Executor
+    b, n, row0, seq0 = _exchange_graph()
+    with Executor(timeout_ms=300) as ex:
+        ex.load(b)
+        res = ex.run(check=False)
+        assert abi.err_name(res.status) == 'TIMEOUT' and res.err_task == 1, (res.status, res.err_task)
+        assert ex.read_buffer('peer.flag')[0, row0] == seq0 + 1                        # the put itself was delivered
+        ex.write_buffer('flag', np.array([seq0 + 1], np.int32), offset_elems=row0 + 1)    # the peer arrives after all
+        res = ex.run(check=False)
+        assert res.status == 0 and res.done == 2

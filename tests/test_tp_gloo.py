@@ -76,3 +76,52 @@ def test_two_ranks_reproduce_the_unsharded_tokens():
 
 def test_pick_token_prefers_the_lowest_index_on_ties():
     assert pick_token([(1.0, 7), (2.0, 9), (2.0, 3)]) == 3
+
+
+def test_fused_exchange_graphs_reproduce_the_unsharded_tokens():
+    """The one-launch form: each rank's whole token is one graph whose partial sums are peer_put_signal / peer_wait_sum tasks.
+    Two oracle VMs run as threads of this process; a rank's `tp.peer{p}.*` buffers are the other rank's `tp.inbox` / `tp.flag`
+    arrays (what the GPU runner maps over CUDA IPC), so a put lands in the peer's memory and its wait really waits for it."""
+    import threading
+    ref_toks, ref_logits = _reference_tokens()
+    c = preset('decode_tiny', **CFG)
+    world, Vl = 2, c.vocab // 2
+    bundles = [build_decode_tp(c, r, world, exact=True, fused=True)[0].to_bundle() for r in range(world)]
+    assert [s['name'] for s in bundles[0].buffers[:4]] == ['tp.inbox', 'tp.flag', 'tp.peer1.inbox', 'tp.peer1.flag']
+    vms = [VM(b) for b in bundles]
+    index = lambda b, name: next(i for i, spec in enumerate(b.buffers) if spec['name'] == name)
+    for r in range(world):                                  # bind the peer views: the same Buf objects, hence the same arrays
+        for p in range(world):
+            if p != r:
+                vms[r].bufs[index(bundles[r], f'tp.peer{p}.inbox')] = vms[p].buffer('tp.inbox')
+                vms[r].bufs[index(bundles[r], f'tp.peer{p}.flag')] = vms[p].buffer('tp.flag')
+    toks = []
+    for _ in range(NTOK):
+        errs = []
+
+        def run(vm):
+            try:
+                vm.run()
+            except Exception as e:      # surfaces in the asserting thread
+                errs.append(e)
+        th = [threading.Thread(target=run, args=(vm,)) for vm in vms]
+        for t in th:
+            t.start()
+        for t in th:
+            t.join(timeout=120)
+        assert not errs, errs
+        props = []
+        for r, vm in enumerate(vms):
+            lg = vm.buffer('u0.logits').a[0]
+            props.append((float(lg.max()), r * Vl + int(lg.argmax())))
+        tok = pick_token(props)
+        toks.append(tok)
+        vms = [VM(b, buffers=vm.bufs) for b, vm in zip(bundles, vms)]
+        for vm in vms:
+            vm.buffer('u0.tok').a[0, 0] = tok
+    assert toks == ref_toks, (toks, ref_toks)
+    logits = np.concatenate([vm.buffer('u0.logits').a.ravel() for vm in vms])
+    assert np.allclose(logits, ref_logits.ravel(), rtol=2e-3, atol=2e-3)
+    # the replicas of the summed hidden state are bit-equal: every rank adds the partials in rank order
+    last = f'u0.l{c.layers - 1}.x2'
+    assert np.array_equal(vms[0].buffer(last).a, vms[1].buffer(last).a)
