@@ -47,6 +47,14 @@ struct KvmCtx {
   int* ctl;                   // executor control words in shared memory (ctl[0] = TMEM base address)
   const void* tmaps;          // tensor-map table of the tensor-core tasks
   int pair;                   // >= 0: the task runs together with this partner task (two stacked GEMM tiles), else -1
+  // Yielding (ready-queue kernel only, else yield_word == nullptr): a task that would only wait for something outside the launch
+  // (a peer's flag) while other tasks are queued may set *yield_word = 1 and return WITHOUT having written anything; the worker
+  // then puts it back at the end of its queue instead of finishing it.  yield_count: per-task attempts word (bounds the re-queues),
+  // q_head / q_tail: the ready queue's ticket words of the four classes.
+  int* yield_word;
+  int* yield_count;
+  const unsigned* q_head;
+  const unsigned* q_tail;
   unsigned long long deadline;   // %globaltimer value after which a task that waits for something outside the launch (a peer's flag) gives up
   float* rope_cache;          // shared memory, 66 floats kept over the tasks of a launch: [0] theta bits, [1] head dimension bits, [2..] the inverse frequencies of that pair (or nullptr)
   int engine;                 // 1: the kernel's engine warps run the mainloops of tensor-core GEMM tiles, the op body is their epilogue only

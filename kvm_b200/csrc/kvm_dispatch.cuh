@@ -76,6 +76,7 @@ static __device__ void kvm_dispatch(const KvmCtx& c, int op, const int32_t* a, c
     case 301: kvm_op_gemv_bf16_rows(c, a); break;
     case 302: kvm_op_peer_put_signal(c, a); break;
     case 303: kvm_op_peer_wait_sum(c, a); break;
+    case 304: kvm_op_peer_wait(c, a); break;
     default: c.fail(KVM_ERR_BAD_OP, op); break;
   }
 }

@@ -31,6 +31,7 @@
 #define KVM_CTL_PROD_IT 1
 #define KVM_CTL_MMA_IT 2
 #define KVM_CTL_ACC_PH 3
+#define KVM_CTL_YIELD 5          // ready-queue kernel: set by a task that wants to be put back into the queue instead of finished
 #define KVM_CTL_BAR 8          // 8-byte aligned: full[4], empty[4], acc_full at ctl[8 + 2*i]
 #define KVM_CTL_ABAR 9          // second barrier set (attention, paired GEMM tiles): indices 9.. in the ctl barrier array
 #define KVM_CTL_ACNT 64         // completed-phase counts of the second set (ints)

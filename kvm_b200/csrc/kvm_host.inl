@@ -472,10 +472,16 @@ extern "C" int kvm_clear_tasks(KvmExec* h) {
   return 0;
 }
 
+// Cells per class of the ready ring: every task is pushed once, a task that may yield (a wait for a peer's flag) up to six times more.
+static int kvm_ring_cap(const KvmExec* h) {
+  size_t extra = 0;
+  for (const KvmTaskDesc& t : h->tasks) if (t.op_id == 303 || t.op_id == 304) extra += 6;
+  return (int)(h->tasks.size() + extra);
+}
 static KvmDevState kvm_dev_state(KvmExec* h) {
   KvmDevState S{};
   S.tasks = h->d_tasks; S.succ = h->d_succ; S.args = h->d_args; S.nt = (int)h->tasks.size();
-  S.indeg = h->d_indeg; S.exec_count = h->d_exec; S.ring = h->d_ring;
+  S.indeg = h->d_indeg; S.exec_count = h->d_exec; S.ring = h->d_ring; S.ring_cap = kvm_ring_cap(h);
   S.head = (unsigned*)h->d_ctl + 8; S.tail = (unsigned*)h->d_ctl + 12; S.done = h->d_ctl + 2;      // head[4], tail[4]: 16-byte aligned, one sector
   S.bufs = h->d_bufs; S.nbufs = (int)h->bufs.size();
   S.versions = h->d_versions; S.nvars = h->nvars; S.ver_base = h->d_ver_base; S.ver_off = h->d_ver_off; S.park_head = h->d_park_head; S.park_next = h->d_park_next;
@@ -533,7 +539,7 @@ static int kvm_prepare(KvmExec* h, bool keep_error = false) {
     KVM_CUDA(cudaMalloc(&h->d_args, (h->args.size() + 1) * 4));
     KVM_CUDA(cudaMalloc(&h->d_aux, nt * sizeof(int4)));
     KVM_CUDA(cudaMalloc(&h->d_tmaps, (h->tmaps.size() + 1) * sizeof(CUtensorMap)));
-    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, nt * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_claim, nt * 4));
+    KVM_CUDA(cudaMalloc(&h->d_indeg, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_exec, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_ring, (size_t)kvm_ring_cap(h) * 4 * KVM_NCLASS)); KVM_CUDA(cudaMalloc(&h->d_park_next, nt * 4)); KVM_CUDA(cudaMalloc(&h->d_claim, nt * 4));
     if (h->cfg.trace) { KVM_CUDA(cudaMalloc(&h->d_tstart, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tend, nt * 8)); KVM_CUDA(cudaMalloc(&h->d_tsmid, nt * 4)); }
     KVM_CUDA(cudaMemcpyAsync(h->d_tasks, h->tasks.data(), nt * sizeof(KvmTaskDesc), cudaMemcpyHostToDevice, h->stream));
     if (!h->succ.empty()) {

@@ -37,43 +37,94 @@ KVM_OP_FN void kvm_op_peer_put_signal(const KvmCtx& c, const int32_t* a) {
   }
 }
 
+#define KVM_MAX_YIELDS 6
+// Bounded wait of warp 0 for flag[row0 + i] >= eff, i < count (count <= 32; lane i polls word i, `skip` is left out).  *ok (shared
+// memory) = 1: every flag came; 0: give up.  On expiry of the launch's deadline the lane whose flag is missing records
+// KVM_ERR_TIMEOUT.  Where the executor allows it (KvmCtx::yield_word) and other tasks are queued, the wait ends early with a yield:
+// the task has written nothing and runs again later, so a flag that is late costs a trip through the queue, not a stalled worker.
+__device__ __forceinline__ void kvm_peer_poll(const KvmCtx& c, const KvmBuf& flag, int row0, int count, int skip, int eff, int* ok) {
+  if (threadIdx.x < 32) {
+    const int p = threadIdx.x;
+    bool met = !(p < count && p != skip);
+    unsigned spins = 0;
+    int verdict = 0;                               // 1 all flags, 2 timeout / error elsewhere, 3 yield
+    while (verdict == 0) {
+      if (!met && kvm_ld_acquire_sys((const int*)flag.p + row0 + p) >= eff) met = true;
+      if (__all_sync(0xffffffffu, met)) { verdict = 1; break; }
+      if ((++spins & 63u) == 0) {
+        int v = 0;
+        if (threadIdx.x == 0) {
+          if (kvm_globaltimer() > c.deadline || *(volatile const int*)&c.err->code != 0) v = 2;
+          else if (c.yield_word && (spins & 255u) == 0) {
+            unsigned h[4], t[4];
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "l"(c.q_head) : "memory");
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]) : "l"(c.q_tail) : "memory");
+            const bool queued = t[0] > h[0] || t[1] > h[1] || t[2] > h[2] || t[3] > h[3];
+            if (queued && atomicAdd(c.yield_count, 1) < KVM_MAX_YIELDS) v = 3;
+          }
+        }
+        verdict = __shfl_sync(0xffffffffu, v, 0);
+      }
+    }
+    if (verdict == 2 && !met) c.fail_any(KVM_ERR_TIMEOUT, row0 + p, eff);        // the peer's flag never came (first error wins)
+    if (threadIdx.x == 0) { *ok = verdict == 1 ? 1 : 0; if (verdict == 3) *c.yield_word = 1; }
+  }
+}
+
 // peer_wait_sum (303)
 KVM_OP_FN void kvm_op_peer_wait_sum(const KvmCtx& c, const int32_t* a) {
   KvmBuf part, inbox, flag, out, res, seq;
   if (!kvm_buf(c, a[0], KVM_M_F32, part) || !kvm_buf(c, a[1], KVM_M_F32, inbox) || !kvm_buf(c, a[2], KVM_M_I32, flag) || !kvm_buf(c, a[3], KVM_M_F32, out) ||
       !kvm_buf(c, a[4], KVM_M_F32, res, true) || !kvm_buf(c, a[10], KVM_M_I32, seq, true)) return;
-  const int n = a[5], row0 = a[6], rank = a[7], world = a[8], ver = a[9], stride = a[11];
+  const int n = a[5], row0 = a[6], rank = a[7], world = a[8], ver = a[9], stride = a[11], po = a[12], oo = a[13];
   if (n <= 0 || world < 1 || world > 32 || rank < 0 || rank >= world || row0 < 0) { c.fail(KVM_OPE_RANGE, n, world); return; }
-  if (!kvm_span_ok(c, part, 0, n) || !kvm_span_ok(c, out, 0, n) || (res.p && !kvm_span_ok(c, res, 0, n)) || !kvm_span_ok(c, flag, row0, world) ||
+  if (!kvm_span_ok(c, part, po, n) || !kvm_span_ok(c, out, oo, n) || (res.p && !kvm_span_ok(c, res, 0, n)) || !kvm_span_ok(c, flag, row0, world) ||
       !kvm_mat_ok(c, inbox, (long long)row0 + world, n)) return;
   int* ok = (int*)c.smem;
   kvm_sync();                                   // the previous task is done with the scratch
-  if (threadIdx.x < 32) {
-    const int eff = ver + (seq.p ? ((const int*)seq.p)[0] * stride : 0);
-    const int p = threadIdx.x;
-    bool met = !(p < world && p != rank);
-    unsigned spins = 0;
-    bool alive = true;
-    while (alive) {
-      if (!met && kvm_ld_acquire_sys((const int*)flag.p + row0 + p) >= eff) met = true;
-      if (__all_sync(0xffffffffu, met)) break;
-      if ((++spins & 255u) == 0 && (kvm_globaltimer() > c.deadline || *(volatile const int*)&c.err->code != 0)) alive = false;
-      alive = __all_sync(0xffffffffu, alive);
-    }
-    if (!alive && !met) c.fail_any(KVM_ERR_TIMEOUT, row0 + p, eff);        // the peer's flag never came (first error wins)
-    if (threadIdx.x == 0) *ok = alive ? 1 : 0;
-  }
+  kvm_peer_poll(c, flag, row0, world, rank, ver + (seq.p ? ((const int*)seq.p)[0] * stride : 0), ok);
   kvm_sync();                                   // the acquiring warp's loads happen before everyone's reads of the inbox
   if (*ok == 0) return;
+  // inbox rows are read from L2 (what the peer wrote, never a stale L1 line of the last run); rank order, one rounded add each
   const float* ib = (const float*)inbox.p;
-  for (int i = threadIdx.x; i < n; i += KVM_NT) {
-    float v = res.p ? ((const float*)res.p)[i] : 0.0f;
-    bool first = !res.p;
-    for (int p = 0; p < world; ++p) {
-      const float t = p == rank ? ((const float*)part.p)[i] : __ldcg(ib + (size_t)(row0 + p) * inbox.ld + i);     // L2: what the peer wrote, never a stale L1 line of the last run
-      v = first ? t : __fadd_rn(v, t);
-      first = false;
+  const float* pp = (const float*)part.p + po;
+  float* op = (float*)out.p + oo;
+  const float* rp = (const float*)res.p;
+  if (!(n & 3) && !(inbox.ld & 3) && !(((uintptr_t)pp | (uintptr_t)op | (uintptr_t)ib | (uintptr_t)rp) & 15)) {
+    for (int i = threadIdx.x; i < n / 4; i += KVM_NT) {
+      float4 v = rp ? ((const float4*)rp)[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      bool first = !rp;
+      for (int p = 0; p < world; ++p) {
+        const float4 t = p == rank ? ((const float4*)pp)[i] : __ldcg((const float4*)(ib + (size_t)(row0 + p) * inbox.ld) + i);
+        v = first ? t : make_float4(__fadd_rn(v.x, t.x), __fadd_rn(v.y, t.y), __fadd_rn(v.z, t.z), __fadd_rn(v.w, t.w));
+        first = false;
+      }
+      ((float4*)op)[i] = v;
     }
-    ((float*)out.p)[i] = v;
+  } else {
+    for (int i = threadIdx.x; i < n; i += KVM_NT) {
+      float v = rp ? rp[i] : 0.0f;
+      bool first = !rp;
+      for (int p = 0; p < world; ++p) {
+        const float t = p == rank ? pp[i] : __ldcg(ib + (size_t)(row0 + p) * inbox.ld + i);
+        v = first ? t : __fadd_rn(v, t);
+        first = false;
+      }
+      op[i] = v;
+    }
   }
+}
+
+// peer_wait (304)
+KVM_OP_FN void kvm_op_peer_wait(const KvmCtx& c, const int32_t* a) {
+  KvmBuf flag, seq;
+  if (!kvm_buf(c, a[0], KVM_M_I32, flag) || !kvm_buf(c, a[4], KVM_M_I32, seq, true)) return;
+  const int row0 = a[1], count = a[2], ver = a[3], stride = a[5];
+  if (row0 < 0 || count < 1 || count > 32 || !kvm_span_ok(c, flag, row0, count)) { if (count < 1 || count > 32 || row0 < 0) c.fail(KVM_OPE_RANGE, row0, count); return; }
+  int* ok = (int*)c.smem;
+  kvm_sync();
+  kvm_peer_poll(c, flag, row0, count, -1, ver + (seq.p ? ((const int*)seq.p)[0] * stride : 0), ok);
+  kvm_sync();
+  // The data that came with the flags is in L2; lines of it that this SM still holds in L1 from an earlier run are dropped by the
+  // acquire above (system scope), so the tasks released by this one read what the peers stored.
 }

@@ -33,8 +33,8 @@ struct KvmSlot {
 __device__ __forceinline__ void kvm_push_ready(const KvmDevState& S, int task) {
   const int c = kvm_class_of(S.tasks[task].priority);
   unsigned t = atomicAdd(&S.tail[c], 1u);
-  if (t >= (unsigned)S.nt) { kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, task, (int)t); return; }
-  kvm_st_release(&S.ring[(size_t)c * S.nt + t], task + 1);
+  if (t >= (unsigned)S.ring_cap) { kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, task, (int)t); return; }
+  kvm_st_release(&S.ring[(size_t)c * S.ring_cap + t], task + 1);
 }
 // Pop, highest class first.  Tickets are taken with atomicAdd (no compare-and-swap convoy when many workers are idle) but only
 // where head < tail was just seen; a ticket that lost that race and points past the tail is HELD: the worker keeps polling its
@@ -62,8 +62,8 @@ __device__ __forceinline__ int kvm_try_pop(const KvmDevState& S, int (&held)[KVM
   for (int c = KVM_NCLASS - 1; c >= 0; --c)
     if (held[c] < 0 && h[c] < t[c]) {
       const unsigned tk = atomicAdd(&S.head[c], 1u);
-      if (tk >= (unsigned)S.nt) continue;
-      const int cell = (int)((size_t)c * S.nt + tk);
+      if (tk >= (unsigned)S.ring_cap) continue;
+      const int cell = (int)((size_t)c * S.ring_cap + tk);
       const int v = kvm_ld_acquire(&S.ring[cell]);
       if (v > 0) return v - 1;
       held[c] = cell;                      // its pusher is one store away, or the race was lost: look again next pass
@@ -124,10 +124,11 @@ __global__ void kvm_arm_kernel(KvmDevState S) {
     S.indeg[i] = S.tasks[i].indegree;
     S.exec_count[i] = 0;
     S.claim[i] = 0;
-#pragma unroll
-    for (int c = 0; c < KVM_NCLASS; ++c) S.ring[(size_t)c * S.nt + i] = 0;
     S.park_next[i] = -1;
   }
+  for (int j = i; j < S.ring_cap; j += gridDim.x * blockDim.x)       // a class's ring holds every task once, plus the re-queues of tasks that may yield
+#pragma unroll
+    for (int c = 0; c < KVM_NCLASS; ++c) S.ring[(size_t)c * S.ring_cap + j] = 0;
   if (i < S.nvars) { S.park_head[i] = -1; S.ver_off[i] = S.versions[i] - S.ver_base[i]; }
 }
 __global__ void kvm_roots_kernel(KvmDevState S) {
@@ -204,8 +205,8 @@ static __device__ int kvm_finish_task(const KvmDevState& S, int task, int so, in
 #pragma unroll
       for (int u = 0; u < KVM_REL_U; ++u)
         if (kind[u] == c) {
-          if (t >= (unsigned)S.nt) kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, s[u], (int)t);
-          else kvm_st_relaxed(&S.ring[(size_t)c * S.nt + t], s[u] + 1);
+          if (t >= (unsigned)S.ring_cap) kvm_dev_fail(S, KVM_ERR_QUEUE_OVERFLOW, s[u], (int)t);
+          else kvm_st_relaxed(&S.ring[(size_t)c * S.ring_cap + t], s[u] + 1);
           ++t;
         }
     }
@@ -225,6 +226,7 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
   const bool is_sched = tid >= KVM_NT && tid < KVM_NT + 32;
   const int engine_role = tid == KVM_NT + 32 ? 1 : tid == KVM_NT + 64 ? 2 : 0;      // one thread each: TMA producer, MMA issuer
   if (tid < KVM_NSLOT) { slots[tid].state = 0; slots[tid].task = -1; slots[tid].seq = 0; slots[tid].kind = 0; }
+  if (tid == 0) ctl[KVM_CTL_YIELD] = 0;
   if (tid == 0) { ((int*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288))[0] = 0; ((int*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288))[1] = 0; }      // rope cache: no key yet
   unsigned dyn;
   asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
@@ -257,7 +259,20 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
     unsigned polls = 0;
     while (true) {
       bool progressed = false;
-      // 1. a finished task?
+      // 1. a task that yielded: back to the end of its class's queue, nothing released, the exactly-once witness taken back
+      if (inflight > 0 && kvm_ld_volatile_shared(&slots[drain].state) == 3) {
+        __syncwarp();
+        if (lane == 0) {
+          const int t = slots[drain].task;
+          atomicSub(&S.exec_count[t], 1);
+          __threadfence();
+          kvm_push_ready(S, t);
+          slots[drain].state = 0;
+        }
+        __syncwarp();
+        drain = (drain + 1) % KVM_NSLOT; --inflight; progressed = true;
+      }
+      // 1b. a finished task?
       if (inflight > 0 && kvm_ld_volatile_shared(&slots[drain].state) == 2) {
         __syncwarp();
         const int32_t* dd = slots[drain].desc;
@@ -410,6 +425,7 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
     c.smem = kvm_smem + used; c.smem_bytes = (int)dyn - used;
     c.engine = engine_on ? 1 : 0; c.gemm_seq = 0;
     c.rope_cache = (float*)(kvm_smem + KVM_EXEC_SMEM_HDR - 288);
+    c.yield_word = ctl + KVM_CTL_YIELD; c.q_head = S.head; c.q_tail = S.tail;
     c.deadline = t_begin + S.timeout_ns - S.timeout_ns / 8;      // a task's own wait gives up (and names itself) before the launch's stall limit does
     unsigned tiles = 0;
     int cur = 0;
@@ -444,6 +460,7 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
       const int op = sl.desc[0];
       const bool tile = sl.kind == 1;
       c.gemm_seq = tiles;
+      c.yield_count = S.claim + task;           // the claim word of a task that is not a stacked GEMM tile is free: it counts the task's yields
       if (op != 0 && go == 1) kvm_dispatch(c, op, sl.args, sl.aux);
       if (tile) ++tiles;
       // this task's generic-proxy writes (global results, shared scratch) ordered before any later TMA access to them
@@ -452,7 +469,9 @@ __global__ void __launch_bounds__(KVM_EXEC_THREADS, 1) kvm_exec_kernel(KvmDevSta
       if (tid == 0) {
         if (S.trace) { S.t_end[task] = kvm_globaltimer(); if (c.pair >= 0) S.t_end[c.pair] = S.t_end[task]; }
         __threadfence();
-        sl.state = 2;
+        const int y = ctl[KVM_CTL_YIELD];
+        ctl[KVM_CTL_YIELD] = 0;
+        sl.state = y ? 3 : 2;                    // 3: the task wrote nothing and wants to run again later
       }
       cur = (cur + 1) % KVM_NSLOT;
     }

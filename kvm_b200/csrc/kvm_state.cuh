@@ -35,6 +35,7 @@ struct KvmDevState {
   int buf_cache;              // 1: copy the buffer table into shared memory at launch (off for graphs of streaming GEMVs, which want the space)
   int pair_depth;             // tiles are stacked only while at least this many tasks are queued (wide phases; narrow ones keep their parallelism)
   int* claim;                 // per task: 0 free, 1 taken (tensor-core GEMM tiles that may run stacked with a partner tile)
+  int ring_cap;               // cells per class of the ready ring: nt, plus the bounded re-queues of tasks that may yield (peer waits)
   int engine;                 // 1: the ready-queue kernel's engine warps run the mainloops of the tensor-core GEMM tiles (overlapped with the previous tile's epilogue)
 };
 #define KVM_REC_WORDS 48

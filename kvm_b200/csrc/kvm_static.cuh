@@ -798,6 +798,7 @@ __global__ void __launch_bounds__(KVM_NT + 32, 1) kvm_static_kernel(KvmStaticSta
     KvmCtx c;
     c.nbufs = S.nbufs; c.err = S.err; c.cfg_flags = S.cfg_flags; c.ctl = ctl; c.tmaps = S.tmaps; c.pair = -1; c.engine = 0; c.gemm_seq = 0;
     c.rope_cache = (float*)(kvm_smem + KVM_ST_HDR - 128 - 288);
+    c.yield_word = nullptr; c.yield_count = nullptr; c.q_head = c.q_tail = nullptr;      // program order: a waiting task waits in place
     c.deadline = deadline - S.timeout_ns / 8;      // a task's own wait gives up (and names itself) before the launch's stall limit does
     c.bufs = buf_cache ? (const KvmBuf*)(kvm_smem + KVM_ST_HDR) : S.bufs;
     const int used = KVM_ST_HDR + (buf_cache ? cache_bytes : 0);

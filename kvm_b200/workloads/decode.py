@@ -344,7 +344,7 @@ def build_decode_tp(c: DecodeConfig, rank: int, world: int, exact: bool = False,
                                        'seq': lens, 'stride': 1}, [partial, lens], [(pin, (row0 + rank, row0 + rank + 1)), (pfl, (0, 1), (row0 + rank, row0 + rank + 1))],
                    prio, f'{tag}.put{p}')
         g.task('peer_wait_sum', {'partial': partial, 'inbox': inbox, 'flag': flag, 'out': out, 'res': None, 'n': d, 'row0': row0, 'rank': rank, 'world': P, 'ver': 1,
-                                 'seq': lens, 'stride': 1}, [partial, lens, (inbox, (row0, row0 + P)), (flag, (0, 1), (row0, row0 + P))], [out], prio, f'{tag}.sum')
+                                 'seq': lens, 'stride': 1, 'p_off': 0, 'o_off': 0}, [partial, lens, (inbox, (row0, row0 + P)), (flag, (0, 1), (row0, row0 + P))], [out], prio, f'{tag}.sum')
 
     W('embed', V, d)
     g.buffer('w.lnf', 1, d, init={'kind': 'fill', 'value': 1.0})

@@ -87,9 +87,55 @@ def token_stream(cfg: GPTConfig, steps: int, rank: int = 0, world: int = 1):
     return mine[:, :, :-1].reshape(-1).copy(), mine[:, :, 1:].reshape(-1).copy()
 
 
+def param_shapes(c: GPTConfig):
+    """(name, rows, cols, fill or None, is a GEMM operand) of every parameter, in declaration order."""
+    d = c.d_model
+    out = [('wte', c.vocab, d, None, False), ('wpe', c.seq, d, None, False)]
+    for l in range(c.layers):
+        p = f'h{l}.'
+        out += [(p + 'ln1.g', 1, d, 1.0, False), (p + 'ln1.b', 1, d, 0.0, False)]
+        for n in 'qkv':
+            out += [(p + f'attn.{n}.w', d, d, None, True), (p + f'attn.{n}.b', 1, d, 0.0, False)]
+        out += [(p + 'attn.o.w', d, d, None, True), (p + 'attn.o.b', 1, d, 0.0, False)]
+        out += [(p + 'ln2.g', 1, d, 1.0, False), (p + 'ln2.b', 1, d, 0.0, False)]
+        out += [(p + 'fc.w', d, c.d_ff, None, True), (p + 'fc.b', 1, c.d_ff, 0.0, False)]
+        out += [(p + 'proj.w', c.d_ff, d, None, True), (p + 'proj.b', 1, d, 0.0, False)]
+    out += [('lnf.g', 1, d, 1.0, False), ('lnf.b', 1, d, 0.0, False)]
+    if not c.tied:
+        out.append(('head.w', d, c.vocab, None, True))
+    return out
+
+
+def dp_exchange_layout(c: GPTConfig, world: int):
+    """Layout of the in-launch gradient exchange of data parallelism over `world` ranks, the same on every rank: the gradient arena
+    ({parameter: element offset}, 64-element aligned, and its length), the exchange chunks [(parameter, e0, e1)] (the optimizer's
+    own flat chunks: chunk k is summed by rank k % world), the inbox row length and the number of chunks a rank owns at most."""
+    tmp = Graph('layout')
+    off, arena, chunks = 0, {}, []
+    for name, rows, cols, _, _ in param_shapes(c):
+        tmp.buffer('w.' + name, rows, cols)
+        arena[name] = off
+        off += -(-rows * cols // 64) * 64
+        chunks += [(name, e0, e1) for e0, e1 in tmp.flat_chunks('w.' + name, c.flat_chunk)]
+    width = -(-max(e1 - e0 for _, e0, e1 in chunks) // 4) * 4
+    return arena, off, chunks, width, -(-len(chunks) // world)
+
+
 class _Emit:
-    def __init__(self, cfg: GPTConfig, steps: int, rank=0, world=1, stream_steps=None):
+    def __init__(self, cfg: GPTConfig, steps: int, rank=0, world=1, stream_steps=None, dp_fused=False):
         self.c, self.g = cfg, Graph('train')
+        self.rank, self.world, self.dp_fused = rank, world, bool(dp_fused) and world > 1
+        if self.dp_fused:
+            # Buffers of the in-launch gradient exchange come first, so that a runner has this rank's exported ones before it binds
+            # the peers' (kvm_b200/dp.py): the arena every gradient buffer is a slice of, the inbox the peers store their partial
+            # chunks into (row = owned chunk * world + sending rank), its flag words, the flag words of the summed chunks coming back.
+            _, n_arena, chunks, width, owned = dp_exchange_layout(cfg, world)
+            gb = self.g.buffer
+            gb('dp.arena', 1, n_arena), gb('dp.inbox', owned * world, width), gb('dp.flag', 1, owned * world, 'i32'), gb('dp.gflag', 1, len(chunks), 'i32')
+            for p in range(world):
+                if p != rank:
+                    gb(f'dp.peer{p}.arena', 1, n_arena), gb(f'dp.peer{p}.inbox', owned * world, width)
+                    gb(f'dp.peer{p}.flag', 1, owned * world, 'i32'), gb(f'dp.peer{p}.gflag', 1, len(chunks), 'i32')
         self.g.join_threshold = cfg.join_threshold
         self.bf = cfg.precision == 'bf16'
         self.act = 'bf16' if self.bf else 'f32'
@@ -103,21 +149,9 @@ class _Emit:
         g.buffer('opt_step', 1, 1, 'i32')
         g.buffer('clip_coef', 1, 2, init={'kind': 'fill', 'value': 1.0})
         g.buffer('version_token', 1, 1)      # one cell that chains the publishers of `weights` (post(s-1) -> pre(s) -> post(s))
-        self.param('wte', c.vocab, d)
-        self.param('wpe', c.seq, d)
-        for l in range(c.layers):
-            p = f'h{l}.'
-            self.param(p + 'ln1.g', 1, d, 1.0), self.param(p + 'ln1.b', 1, d, 0.0)
-            for n in 'qkv':
-                self.param(p + f'attn.{n}.w', d, d, mat=True), self.param(p + f'attn.{n}.b', 1, d, 0.0)
-            self.param(p + 'attn.o.w', d, d, mat=True), self.param(p + 'attn.o.b', 1, d, 0.0)
-            self.param(p + 'ln2.g', 1, d, 1.0), self.param(p + 'ln2.b', 1, d, 0.0)
-            self.param(p + 'fc.w', d, c.d_ff, mat=True), self.param(p + 'fc.b', 1, c.d_ff, 0.0)
-            self.param(p + 'proj.w', c.d_ff, d, mat=True), self.param(p + 'proj.b', 1, d, 0.0)
-        self.param('lnf.g', 1, d, 1.0), self.param('lnf.b', 1, d, 0.0)
-        if not c.tied:
-            self.param('head.w', d, c.vocab, mat=True)
-        elif self.bf:
+        for name, rows, cols, fill, mat in param_shapes(c):
+            self.param(name, rows, cols, fill, mat)
+        if c.tied and self.bf:
             g.buffer('wb.wte', c.vocab, d, 'bf16')
         for s in range(steps):
             self.step(s)
@@ -319,7 +353,8 @@ class _Emit:
         rowloss, lse_ce, dlog = B('rowloss', N, 1), B('lse_ce', N, 1), B('dlogits', N, V, act)
         self._rowwise = {logits}
         self.rows('softmax_ce_fused', tag + 'ce', N, c.ce_rows,
-                  {'logits': logits, 'tgt': tgt, 'rowloss': rowloss, 'lse': lse_ce, 'dlogits': dlog, 'V': V, 'ignore': -1, 'N': N, 'scale': 1.0},
+                  {'logits': logits, 'tgt': tgt, 'rowloss': rowloss, 'lse': lse_ce, 'dlogits': dlog, 'V': V, 'ignore': -1, 'N': N,
+                   'scale': 1.0 / self.world if self.dp_fused else 1.0},      # fused data parallelism: the mean over the ranks is folded into the loss gradient
                   [logits], [dlog], vec_r=[tgt], vec_w=[rowloss, lse_ce])
         loss = B(f'loss.{s}', 1, 2)
         g.task('softmax_ce_reduce', {'rowloss': rowloss, 'tgt': tgt, 'loss': loss, 'N': N, 'ignore': -1}, [rowloss, tgt], [loss], 0, tag + 'loss')
@@ -384,6 +419,8 @@ class _Emit:
         for name, (rows, cols, _) in self.params.items():
             for e0, e1 in g.flat_chunks('w.' + name, c.flat_chunk):
                 chunks.append((name, e0, e1))
+        if self.dp_fused:
+            self.dp_exchange(tag, chunks)
         partial = B('gn_partial', 1, len(chunks))
         for slot, (name, e0, e1) in enumerate(chunks):
             g.task('gradnorm_partial', {'g': 'g.' + name, 'partial': partial, 'slot': slot, 'e0': e0, 'e1': e1},
@@ -404,7 +441,42 @@ class _Emit:
         g.task('noop', {}, [], ['version_token'], 1, tag + 'barrier.post', publishes='weights', after=ups)
 
 
-def build_training(cfg: GPTConfig, steps: int = 1, rank: int = 0, world: int = 1, stream_steps: int | None = None) -> Graph:
+    def dp_exchange(self, tag, chunks):
+        """The gradient all-reduce (mean) of data parallelism as tasks of the step, between the backward and the optimizer: chunk k of
+        the gradients is owned by rank k % world.  Every other rank stores its chunk into the owner's inbox and releases a flag
+        (peer_put_signal); the owner waits for the world - 1 flags, adds the partials in rank order in place (peer_wait_sum) and
+        stores the sum into every peer's gradient arena, releasing that peer's flag of the chunk; a non-owner waits for that flag
+        (peer_wait) before anything reads the chunk.  Versions are the optimizer step counter + 1.  The 1 / world of the mean is in
+        the loss gradient already.  The tasks are ordinary low-priority tasks: they run while the backward still has work."""
+        g, P, rank = self.g, self.world, self.rank
+        arena, _, layout_chunks, width, owned = dp_exchange_layout(self.c, P)
+        assert layout_chunks == chunks
+        seq = {'seq': 'opt_step', 'stride': 1, 'ver': 1}
+        sends, recvs = [], []
+        for k, (name, e0, e1) in enumerate(chunks):
+            gbuf, n = 'g.' + name, e1 - e0
+            region = (gbuf, *g.region_of(gbuf, e0, e1))
+            owner, j = k % P, k // P
+            if owner == rank:
+                g.task('peer_wait_sum', {'partial': gbuf, 'inbox': 'dp.inbox', 'flag': 'dp.flag', 'out': gbuf, 'res': None, 'n': n, 'row0': j * P, 'rank': rank,
+                                         'world': P, **seq, 'p_off': e0, 'o_off': e0}, [region, 'opt_step'], [region], 2, f'{tag}dp.sum.{k}')
+                for p in range(P):
+                    if p != rank:
+                        g.task('peer_put_signal', {'src': gbuf, 'dst': f'dp.peer{p}.arena', 'src_off': e0, 'dst_off': arena[name] + e0, 'n': n,
+                                                   'flag': f'dp.peer{p}.gflag', 'var': k, **seq}, [region, 'opt_step'], [], 2, f'{tag}dp.bcast.{k}.{p}')
+            else:
+                sends.append(g.task('peer_put_signal', {'src': gbuf, 'dst': f'dp.peer{owner}.inbox', 'src_off': e0, 'dst_off': (j * P + rank) * width, 'n': n,
+                                                        'flag': f'dp.peer{owner}.flag', 'var': j * P + rank, **seq}, [region, 'opt_step'], [], 2, f'{tag}dp.send.{k}'))
+                recvs.append((k, region))
+        # A wait occupies its worker until the flag comes.  The waits for the sums coming back are therefore held until this rank has
+        # sent its last chunk (the backward is over then, and most sums have arrived long before): they cost a poll each, not a stall.
+        sent = g.task('noop', {}, [], [], 2, f'{tag}dp.sent', after=sends) if sends else None
+        for k, region in recvs:
+            g.task('peer_wait', {'flag': 'dp.gflag', 'row0': k, 'count': 1, **seq}, [region, 'opt_step'], [region], 2, f'{tag}dp.recv.{k}', after=[sent])
+
+
+def build_training(cfg: GPTConfig, steps: int = 1, rank: int = 0, world: int = 1, stream_steps: int | None = None, dp_fused: bool = False) -> Graph:
     """`steps` optimizer steps unrolled in one graph; the token stream holds `stream_steps` (default `steps`) windows, so a
-    one-step graph can be re-run `stream_steps` times (the device step counter selects the window)."""
-    return _Emit(cfg, steps, rank, world, stream_steps).g
+    one-step graph can be re-run `stream_steps` times (the device step counter selects the window).  dp_fused: with world > 1 the
+    gradient all-reduce is part of the graph (`_Emit.dp_exchange`), one launch per step and rank."""
+    return _Emit(cfg, steps, rank, world, stream_steps, dp_fused).g

@@ -692,11 +692,24 @@ def peer_wait_sum(b, a, **kw):
     while any(flag[row0 + p] < eff for p in range(world) if p != rank):
         _need(time.monotonic() - t0 < PEER_WAIT, 'peer_wait_sum: timeout')
         time.sleep(0.0005)
+    po, oo = a.get('p_off', 0), a.get('o_off', 0)
+    _need(po >= 0 and po + n <= b['partial'].a.size and oo >= 0 and oo + n <= b['out'].a.size, 'peer_wait_sum: offsets')
     v = None if b.get('res') is None else b['res'].a.reshape(-1)[:n].astype(np.float32)
     for p in range(world):
-        t = (b['partial'].a.reshape(-1)[:n] if p == rank else b['inbox'].a[row0 + p, :n]).astype(np.float32)
+        t = (b['partial'].a.reshape(-1)[po:po + n] if p == rank else b['inbox'].a[row0 + p, :n]).astype(np.float32)
         v = t.copy() if v is None else (v + t).astype(np.float32)
-    b['out'].a.reshape(-1)[:n] = v
+    b['out'].a.reshape(-1)[oo:oo + n] = v
+
+
+def peer_wait(b, a, **kw):
+    import time
+    row0, count = a['row0'], a['count']
+    _need(row0 >= 0 and 1 <= count <= 32 and row0 + count <= b['flag'].a.size, 'peer_wait: range')
+    eff, flag = _seq_ver(b, a), b['flag'].a.reshape(-1)
+    t0 = time.monotonic()
+    while any(flag[row0 + i] < eff for i in range(count)):
+        _need(time.monotonic() - t0 < PEER_WAIT, 'peer_wait: timeout')
+        time.sleep(0.0005)
 
 
 # ---- loss -------------------------------------------------------------------------------------------------------------------

@@ -138,7 +138,7 @@ def _exchange_graph(n=4096, seq0=40):
     g.task('peer_put_signal', {'src': 'partial', 'dst': 'peer.inbox', 'src_off': 0, 'dst_off': (row0 + rank) * n, 'n': n, 'flag': 'peer.flag', 'var': row0 + rank,
                                'ver': 1, 'seq': 'seq', 'stride': 1}, ['partial', 'seq'], ['peer.inbox', 'peer.flag'])
     g.task('peer_wait_sum', {'partial': 'partial', 'inbox': 'inbox', 'flag': 'flag', 'out': 'out', 'res': 'res', 'n': n, 'row0': row0, 'rank': rank, 'world': world,
-                             'ver': 1, 'seq': 'seq', 'stride': 1}, ['partial', 'seq', 'inbox', 'flag', 'res'], ['out'])
+                             'ver': 1, 'seq': 'seq', 'stride': 1, 'p_off': 0, 'o_off': 0}, ['partial', 'seq', 'inbox', 'flag', 'res'], ['out'])
     return g.to_bundle(), n, row0, seq0
 
 
