@@ -92,21 +92,25 @@ def test_two_ranks_equal_gradient_accumulation():
     assert any(fresh.buffer(k).a.tobytes() != got[0][k] for k in got[0])
 
 
-def test_fused_exchange_graphs_equal_gradient_accumulation():
-    """The one-launch form: the all-reduce is tasks of each rank's graph (peer_put_signal / peer_wait_sum / peer_wait).  Two oracle
-    VMs run as threads; a rank's `dp.peer{p}.*` buffers are the other rank's arrays and every gradient buffer is a view into the
-    rank's arena (what the GPU runner sets up with CUDA IPC and kvm_bind_buffer).  With two ranks the result is bit-identical to
-    averaging the two microbatch gradients (the 1 / 2 folded into the loss gradient is an exact scaling)."""
+import pytest
+
+
+@pytest.mark.parametrize('world', [2, 4])
+def test_fused_exchange_graphs_equal_gradient_accumulation(world):
+    """The one-launch form: the all-reduce is tasks of each rank's graph (peer_put_signal / peer_wait_sum / peer_wait).  The oracle
+    VMs of the ranks run as threads; a rank's `dp.peer{p}.*` buffers are the other rank's arrays and every gradient buffer is a view
+    into the rank's arena (what the GPU runner sets up with CUDA IPC and kvm_bind_buffer).  With 2 or 4 ranks the result is
+    bit-identical to summing the microbatch gradients in rank order and scaling by 1 / world (the 1 / world folded into the loss
+    gradient is an exact scaling by a power of two)."""
     import threading
     from kvm_b200.workloads.gpt import dp_exchange_layout
     from oracle.ops_np import Buf
     cfg = preset('gpt_micro')
-    world = 2
     bundles = [build_training(cfg, 1, rank=r, world=world, stream_steps=2, dp_fused=True).to_bundle() for r in range(world)]
     arena, n_arena, chunks, width, owned = dp_exchange_layout(cfg, world)
     index = lambda b, name: next(i for i, spec in enumerate(b.buffers) if spec['name'] == name)
     vms = [VM(b) for b in bundles]
-    for r, (vm, b) in enumerate(zip(vms, bundles)):
+    for vm, b in zip(vms, bundles):
         flat = vm.buffer('dp.arena').a.reshape(-1)
         for name, off in arena.items():
             i = index(b, 'g.' + name)
@@ -134,9 +138,10 @@ def test_fused_exchange_graphs_equal_gradient_accumulation():
         vms = [VM(b, buffers=vm.bufs) for b, vm in zip(bundles, vms)]
     wnames = [s['name'] for s in bundles[0].buffers if s['name'].startswith('w.')]
     for k in wnames:
-        assert np.array_equal(vms[0].buffer(k).a, vms[1].buffer(k).a), f'replicas diverged on {k}'
-    # reference: the two-launch form with the average taken on the host
-    gs = [build_training(cfg, 1, rank=r, world=2, stream_steps=2) for r in range(2)]
+        for r in range(1, world):
+            assert np.array_equal(vms[0].buffer(k).a, vms[r].buffer(k).a), f'replicas diverged on {k}'
+    # reference: the two-launch form with the mean taken on the host, partials added in rank order
+    gs = [build_training(cfg, 1, rank=r, world=world, stream_steps=2) for r in range(world)]
     halves = [g.to_bundles_split(g.split_at) for g in gs]
     lay, n = grad_arena_layout(halves[0][0])
     ref = [VM(h[0]) for h in halves]
@@ -144,7 +149,10 @@ def test_fused_exchange_graphs_equal_gradient_accumulation():
         for vm in ref:
             vm.run()
         for idx in lay:
-            avg = (ref[0].bufs[idx].a + ref[1].bufs[idx].a) * np.float32(0.5)
+            acc = ref[0].bufs[idx].a.copy()
+            for r in range(1, world):
+                acc = (acc + ref[r].bufs[idx].a).astype(np.float32)
+            avg = acc * np.float32(1.0 / world)
             for vm in ref:
                 vm.bufs[idx].a[:] = avg
         nxt = []
