@@ -27,9 +27,9 @@ struct KvmStSlot {
   int task;
   int state;                  // 0 free, 1 fetched, 2 ready, 3 leave
   int go;
-  int kind;                   // 0 generic op, 1 streamed gemv, 2 streamed split attention
+  int kind;                   // 0 generic op, 1 streamed gemv (one activation row, SIMT consumer), 2 streamed split attention, 3 streamed gemv on tensor cores (rows)
   int nchunks;                // stage uses of this task
-  int R;                      // gemv: weight rows per stage
+  int R;                      // gemv: weight rows per stage (kind 3 keeps its chunk columns / row groups / k-chunks in j0 / j1 / newrow)
   int wait_off, wait_cnt;
   int32_t desc[16];
   int32_t args[KVM_MAX_ARGS];
