@@ -126,6 +126,10 @@ int kvm_variable_id(KvmExec* h, const char* name);
 /* MvmExec::start (mvm_exec.cu:724-738): launch the persistent kernel over the resident program (every batch submitted since
  * the last kvm_clear_tasks, see kvm_submit).  kvm_finish (mvm_exec.cu:1513-1539): wait, copy counters back.  kvm_run = both. */
 int kvm_start(KvmExec* h);
+/* MvmExec::close (mvm_exec.cu:1513-1520: no more batches will be admitted to the running launch).  Here every batch is resident
+ * before the launch, so there is nothing to close: kept for callers written against start / close / finish; returns 0, or
+ * KVM_E_STATE when no run was started. */
+int kvm_close(KvmExec* h);
 /* Run on the caller's CUDA stream (a cudaStream_t) from now on, so that launches order with the caller's own work - collectives
  * between segments of a tensor-parallel token - without host synchronisation.  No counterpart in the reference (its executor
  * owns one non-blocking stream, mvm_exec.cu:546).  The stream is not destroyed by kvm_destroy. */

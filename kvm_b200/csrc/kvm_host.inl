@@ -648,6 +648,12 @@ extern "C" int kvm_start(KvmExec* h) {
   return 0;
 }
 
+extern "C" int kvm_close(KvmExec* h) {
+  if (!h) return KVM_E_ARG;
+  if (!h->started) { h->error = "kvm_close: nothing started"; return KVM_E_STATE; }
+  return 0;          // every batch was resident before the launch: nothing to close
+}
+
 extern "C" int kvm_finish(KvmExec* h, KvmResult* res) {
   if (!h) return KVM_E_ARG;
   if (!h->started) { h->error = "kvm_finish: nothing started"; return KVM_E_STATE; }

@@ -69,6 +69,7 @@ SYMBOLS = {
     'kvm_buffer_index': (C.c_int, [C.c_void_p, C.c_char_p]),
     'kvm_variable_id': (C.c_int, [C.c_void_p, C.c_char_p]),
     'kvm_start': (C.c_int, [C.c_void_p]),
+    'kvm_close': (C.c_int, [C.c_void_p]),
     'kvm_set_stream': (C.c_int, [C.c_void_p, C.c_void_p]),
     'kvm_finish': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
     'kvm_run': (C.c_int, [C.c_void_p, C.POINTER(KvmResult)]),
