@@ -87,3 +87,16 @@ def test_tensor_parallel_exchange_sites(world):
         assert sorted(a['row0'] for _, a in sums) == [s * world for s in range(sites)]
         for _, a in puts:
             assert a['var'] % world == rank and a['dst_off'] == a['var'] * cfg.hidden and a['n'] == cfg.hidden
+
+
+def test_c_validator_accepts_the_exchange_ops_and_rejects_a_short_argument_list():
+    """The C library's host check (no GPU) knows the extension ops' arities from the same registry file."""
+    from kvm_b200.executor import validate_batch
+    b = build_training(preset('gpt_micro'), 1, rank=1, world=2, stream_steps=2, dp_fused=True).to_bundle()
+    assert validate_batch(b.tasks, b.succ, b.args, len(b.buffers)) == ''
+    t = b.tasks.copy()
+    i = int(np.nonzero(t['op_id'] == OPS['peer_wait_sum'].id)[0][0])
+    t['args_words'][i] -= 2            # the offsets are missing: an older caller's 12-word form
+    assert 'arg' in validate_batch(t, b.succ, b.args, len(b.buffers)).lower()
+    d = build_decode_tp(decode_preset('decode_tiny'), 0, 2, fused=True)[0].to_bundle()
+    assert validate_batch(d.tasks, d.succ, d.args, len(d.buffers)) == ''
