@@ -51,11 +51,11 @@ __device__ __forceinline__ void kvm_peer_poll(const KvmCtx& c, const KvmBuf& fla
     while (verdict == 0) {
       if (!met && kvm_ld_acquire_sys((const int*)flag.p + row0 + p) >= eff) met = true;
       if (__all_sync(0xffffffffu, met)) { verdict = 1; break; }
-      if ((++spins & 63u) == 0) {
+      if ((++spins & 15u) == 0) {                     // a poll is a system-scope load of about a microsecond: look around every 16th
         int v = 0;
         if (threadIdx.x == 0) {
           if (kvm_globaltimer() > c.deadline || *(volatile const int*)&c.err->code != 0) v = 2;
-          else if (c.yield_word && (spins & 255u) == 0) {
+          else if (c.yield_word) {
             unsigned h[4], t[4];
             asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "l"(c.q_head) : "memory");
             asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]) : "l"(c.q_tail) : "memory");
