@@ -260,3 +260,19 @@ def test_corrupted_bundles_are_rejected_on_the_host(kvm_lib):
         elif changed and which == 1:
             raise AssertionError(f'trial {trial}: a rewired successor was accepted')
     assert rejected > 150
+
+
+def test_command_line_runner_usage_and_registry_without_a_gpu(kvm_lib):
+    """The kvm_exec tool (reference CLI contract: exit 2 on usage errors) and the registry it was built with, arities included."""
+    import subprocess
+    from kvm_b200 import abi, build
+    cli = build.build_cli()
+    assert subprocess.run([str(cli)], capture_output=True).returncode == 2
+    assert subprocess.run([str(cli), '--no-such-flag', 'x'], capture_output=True).returncode == 2
+    r = subprocess.run([str(cli), '--check-ops'], capture_output=True, text=True)
+    rows = [line.split() for line in r.stdout.splitlines()]
+    assert r.returncode == 0
+    assert {int(w[0]): (w[1], int(w[3])) for w in rows} == {o.id: (o.name, len(o.args)) for o in abi.load_ops().values()}
+    # a bundle directory cannot run here: the tool says why on stderr and exits 1 without a result line
+    r = subprocess.run([str(cli), '/nonexistent/bundle'], capture_output=True, text=True)
+    assert r.returncode == 1 and r.stdout == '' and r.stderr
